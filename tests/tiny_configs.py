@@ -1,0 +1,52 @@
+"""Tiny configurations of the architecture for tests.  They differ in every size and
+option: head counts and groups, head size, widths that are no power of two, number of
+layers, vocabulary, the norms' eps, the rotary base, tied or untied output matrix, number
+of MTP heads, page size, window, layer order."""
+from __future__ import annotations
+
+import os
+import tempfile
+
+import torch
+
+TINY_A = dict(architecture="gqa_mtp_transformer", vocab_size=256, hidden_size=64, num_layers=2, num_heads=4,
+              num_kv_heads=2, head_dim=16, ffn_hidden=192, rms_norm_eps=1e-5, rope_theta=10000.0,
+              max_context=128, tie_word_embeddings=True, num_mtp_heads=1)
+TINY_A_PAGE = 16
+
+TINY_B = dict(architecture="gqa_mtp_transformer", vocab_size=512, hidden_size=128, num_layers=3, num_heads=4,
+              num_kv_heads=1, head_dim=32, ffn_hidden=352, rms_norm_eps=1e-6, rope_theta=500000.0,
+              max_context=256, tie_word_embeddings=False, num_mtp_heads=2)
+TINY_B_PAGE = 8
+
+# odd sizes: width 120 with 6 heads of 48 (so H*hd != width), 3 query heads per kv head,
+# vocabulary 301, a window of 24 keys on all layers but layer 0, layer 1 run twice
+TINY_C = dict(architecture="gqa_mtp_transformer", vocab_size=301, hidden_size=120, num_layers=2, num_heads=6,
+              num_kv_heads=2, head_dim=48, ffn_hidden=200, rms_norm_eps=3e-6, rope_theta=25000.0,
+              max_context=192, tie_word_embeddings=True, num_mtp_heads=1, sliding_window=24,
+              full_attention_layers=[0], layer_order=[0, 1, 1])
+TINY_C_PAGE = 4
+
+# a layer that reads another layer's keys and values
+TINY_D = dict(architecture="gqa_mtp_transformer", vocab_size=200, hidden_size=48, num_layers=3, num_heads=3,
+              num_kv_heads=3, head_dim=16, ffn_hidden=80, rms_norm_eps=1e-5, rope_theta=10000.0,
+              max_context=96, tie_word_embeddings=False, num_mtp_heads=0, layer_order=[0, 1, 2],
+              cache_source=[None, None, 1])
+TINY_D_PAGE = 16
+
+ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
+       "D": (TINY_D, TINY_D_PAGE, 3)}
+
+
+def make_model_folder(cfg_dict: dict, seed: int, folder: str, std: float = 0.02) -> str:
+    """Write config.json + model.safetensors with the engine's random-weights mode."""
+    from tiny_inference_server_b200.registry import config_from_dict
+    from tiny_inference_server_b200.weights import write_random_model
+
+    cfg = config_from_dict(dict(cfg_dict))
+    return write_random_model(folder, cfg, seed, std=std)
+
+
+def random_prompts(vocab: int, lengths, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]

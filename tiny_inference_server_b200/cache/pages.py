@@ -1,0 +1,197 @@
+"""Pages of keys and values.
+
+Upstream keeps one pool tensor for all layers, a deque of free page ids and a python
+list of page ids per request (``block_table.py:31-86``).  Here the planes (one per
+cached layer) are first grouped by what they need — kv heads, head size, and whether
+they keep every key or a window of them — and every group has pages of its own: a pool
+tensor ``[planes, pages, 2, kv_heads, page_size, head_dim]``, a free list, and one
+block table per request slot.  A page id addresses the same page in every plane of its
+group, as upstream's does in every layer.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..parts.base import KVSpec
+
+
+class CacheError(RuntimeError):
+    """Misuse of the cache manager (double free, unknown slot, pool exhausted)."""
+
+
+class OutOfPages(CacheError):
+    """A group has fewer free pages than an extension needs.  Nothing was allocated."""
+
+
+class PagePool:
+    """Free list over page ids 0..num_pages-1 (FIFO, as upstream's deque:
+    ``block_table.py:44,57-63``), with the checks upstream does not make: a page is never
+    handed out twice, freed twice, or freed without having been handed out."""
+
+    def __init__(self, num_pages: int):
+        if num_pages <= 0:
+            raise CacheError(f"a pool needs at least one page, got {num_pages}")
+        self.num_pages = num_pages
+        self._free = deque(range(num_pages))
+        self._held = [False] * num_pages
+
+    @property
+    def free(self) -> int:
+        return len(self._free)
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise OutOfPages("no free page")
+        p = self._free.popleft()
+        if self._held[p]:
+            raise CacheError(f"page {p} was on the free list while held")
+        self._held[p] = True
+        return p
+
+    def release(self, page: int) -> None:
+        if not (0 <= page < self.num_pages):
+            raise CacheError(f"page id {page} is outside the pool (0..{self.num_pages - 1})")
+        if not self._held[page]:
+            raise CacheError(f"page {page} freed twice (or never allocated)")
+        self._held[page] = False
+        self._free.append(page)
+
+    def shuffle(self, rng) -> None:
+        """Scatter the free list (tests: pages of a request are not contiguous)."""
+        items = list(self._free)
+        rng.shuffle(items)
+        self._free = deque(items)
+
+    def check(self) -> None:
+        """Every page is either held or exactly once on the free list."""
+        on_list = [0] * self.num_pages
+        for p in self._free:
+            on_list[p] += 1
+        for p in range(self.num_pages):
+            if on_list[p] + (1 if self._held[p] else 0) != 1:
+                raise CacheError(f"page {p}: on free list {on_list[p]} times, held={self._held[p]}")
+
+
+@dataclass
+class PlaneRef:
+    """Where the cache of one schedule entry lives."""
+    group: int
+    index: int        # plane inside the group's pool
+
+
+class CacheGroup:
+    """Planes with the same needs: one pool of pages, one block table per slot."""
+
+    def __init__(self, gid: int, kv_heads: int, head_dim: int, window: Optional[int], lags: Sequence[int],
+                 page_size: int, num_pages: int, max_slots: int, max_positions: int, dtype: torch.dtype,
+                 device: torch.device):
+        self.gid = gid
+        self.kv_heads = kv_heads
+        self.head_dim = head_dim
+        self.window = window
+        self.lags = list(lags)                    # per plane: how far it is filled behind the trunk
+        self.max_lag = max(self.lags) if self.lags else 0
+        self.page_size = page_size
+        self.num_planes = len(self.lags)
+        self.pool = PagePool(num_pages)
+        self.max_pages_per_slot = (max_positions + page_size - 1) // page_size
+        # zeros, not empty: an unwritten tail of a page must not hold NaN patterns
+        # (upstream's reason too, block_table.py:40-41)
+        self.pages = torch.zeros((self.num_planes, num_pages, 2, kv_heads, page_size, head_dim),
+                                 dtype=dtype, device=device)
+        self.table_host = torch.full((max_slots, self.max_pages_per_slot), -1, dtype=torch.int32)
+        self.table_dev = torch.full((max_slots, self.max_pages_per_slot), -1, dtype=torch.int32, device=device)
+        # per slot: first logical page still held, and one past the last
+        self.first = [0] * max_slots
+        self.end = [0] * max_slots
+        self.pending: List[tuple] = []            # (slot, logical page, page id) not yet on the device
+
+    @property
+    def bytes_per_token(self) -> int:
+        return 2 * self.num_planes * self.kv_heads * self.head_dim * self.pages.element_size()
+
+    def plane(self, index: int) -> torch.Tensor:
+        return self.pages[index]
+
+    # ---- planning ---------------------------------------------------------------------
+    def dead_before(self, start_pos: int) -> int:
+        """First logical page that a step feeding positions from ``start_pos`` on can still
+        read.  Without a window every page stays.  With a window W the plane that lags most
+        reads keys from (start_pos - lag) - W + 1 on."""
+        if self.window is None:
+            return 0
+        lowest = start_pos - self.max_lag - self.window + 1
+        return max(0, lowest) // self.page_size
+
+    def pages_to_grow(self, slot: int, new_len: int) -> int:
+        need_end = (new_len + self.page_size - 1) // self.page_size
+        return max(0, need_end - self.end[slot])
+
+    def pages_freed_by(self, slot: int, start_pos: int) -> int:
+        return max(0, min(self.dead_before(start_pos), self.end[slot]) - self.first[slot])
+
+    # ---- mutation ---------------------------------------------------------------------
+    def trim(self, slot: int, start_pos: int) -> int:
+        """Give back pages wholly behind the window of a step that starts at ``start_pos``."""
+        upto = min(self.dead_before(start_pos), self.end[slot])
+        n = 0
+        for lp in range(self.first[slot], upto):
+            page = int(self.table_host[slot, lp])
+            self.pool.release(page)
+            self.table_host[slot, lp] = -1
+            self.pending.append((slot, lp, -1))
+            n += 1
+        self.first[slot] = max(self.first[slot], upto)
+        return n
+
+    def grow(self, slot: int, new_len: int) -> None:
+        need_end = (new_len + self.page_size - 1) // self.page_size
+        if need_end > self.max_pages_per_slot:
+            raise CacheError(f"{new_len} tokens exceed the block table ({self.max_pages_per_slot} pages "
+                             f"of {self.page_size})")
+        if need_end - self.end[slot] > self.pool.free:
+            raise OutOfPages(f"group {self.gid}: need {need_end - self.end[slot]} pages, {self.pool.free} free")
+        for lp in range(self.end[slot], need_end):
+            page = self.pool.allocate()
+            self.table_host[slot, lp] = page
+            self.pending.append((slot, lp, page))
+        self.end[slot] = max(self.end[slot], need_end)
+
+    def release_slot(self, slot: int) -> None:
+        for lp in range(self.first[slot], self.end[slot]):
+            page = int(self.table_host[slot, lp])
+            self.pool.release(page)
+            self.table_host[slot, lp] = -1
+            self.pending.append((slot, lp, -1))
+        self.first[slot] = 0
+        self.end[slot] = 0
+
+    def held(self, slot: int) -> int:
+        return self.end[slot] - self.first[slot]
+
+    def take_pending(self) -> List[tuple]:
+        p, self.pending = self.pending, []
+        return p
+
+
+def group_planes(specs: Sequence[Optional[KVSpec]]):
+    """Group the kv specs of the schedule entries: returns ([group key], [PlaneRef or None]).
+    Entries with equal (kv_heads, head_dim, window) share a group."""
+    keys: List[tuple] = []
+    lags: Dict[tuple, List[int]] = {}
+    refs: List[Optional[PlaneRef]] = []
+    for s in specs:
+        if s is None:
+            refs.append(None)
+            continue
+        k = s.group_key()
+        if k not in lags:
+            keys.append(k)
+            lags[k] = []
+        refs.append(PlaneRef(keys.index(k), len(lags[k])))
+        lags[k].append(s.lag)
+    return keys, lags, refs

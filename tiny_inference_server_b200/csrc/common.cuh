@@ -1,0 +1,74 @@
+// Shared device helpers: storage types, 32-bit conversions, block reductions.
+//
+// Every kernel of this library computes in 32-bit floating point; T is only the type
+// in which activations, weights and cache pages are stored (float or bfloat16).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define TIS_API extern "C" __attribute__((visibility("default")))
+
+// Error codes returned by the extern "C" launchers (0 = launched).
+enum TisStatus : int {
+    TIS_OK = 0,
+    TIS_BAD_SIZE = 1,      // a size the kernel refuses (message in tis_last_error())
+    TIS_BAD_DTYPE = 2,
+    TIS_CUDA_ERROR = 3,
+};
+
+void tis_set_error(const char* fmt, ...);
+int tis_check_launch(const char* what);
+
+enum TisDtype : int { TIS_F32 = 0, TIS_BF16 = 1 };
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum / max for blockDim.x a multiple of 32 (<= 1024); `red` holds 33 floats.
+// All threads get the result.  Two calls need no barrier in between from the caller.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // `red` may still be read from an earlier call
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+// Dispatch on the storage dtype inside a launcher.
+#define TIS_DISPATCH_DTYPE(dtype, T, ...)                                   \
+    do {                                                                    \
+        if ((dtype) == TIS_F32) { typedef float T; __VA_ARGS__; }           \
+        else if ((dtype) == TIS_BF16) { typedef bf16 T; __VA_ARGS__; }      \
+        else { tis_set_error("unknown dtype code %d", (int)(dtype)); return TIS_BAD_DTYPE; } \
+    } while (0)

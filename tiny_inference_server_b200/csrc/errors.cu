@@ -1,0 +1,28 @@
+// Last-error text of the library (per host thread) and the launch check.
+#include "common.cuh"
+#include <cstdarg>
+#include <cstdio>
+
+static thread_local char g_err[512] = "";
+
+void tis_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int tis_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        tis_set_error("%s: %s", what, cudaGetErrorString(e));
+        return TIS_CUDA_ERROR;
+    }
+    return TIS_OK;
+}
+
+TIS_API const char* tis_last_error() { return g_err; }
+
+// Version of the launcher interface; the Python side refuses a library built from
+// other sources than its own.
+TIS_API int tis_abi_version() { return 1; }

@@ -1,0 +1,260 @@
+// Row-wise kernels: embedding gather, fused residual-add + RMSNorm, rotary position
+// encoding fused with the write of keys and values into cache pages, SwiGLU gating,
+// and the input of a multi-token-prediction head.
+//
+// One CTA per row of the step.  A row whose request slot is negative is padding: it
+// writes nothing into the cache and its outputs are never read.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------------
+// embedding: residual[r, :] = table[token[r], :]   (the 32-bit residual stream starts here)
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                  float* __restrict__ out, int d) {
+    const int r = blockIdx.x;
+    const T* src = table + (size_t)tokens[r] * d;
+    float* dst = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, float* out, int n, int d,
+                           cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    TIS_DISPATCH_DTYPE(dtype, T,
+        embed_rows_kernel<T><<<n, 256, 0, stream>>>((const T*)table, tokens, out, d));
+    return tis_check_launch("embed_rows");
+}
+
+// ----------------------------------------------------------------------------------
+// residual += delta ; out = residual * sqrt(d) / (||residual||_2 + eps) * scale
+// (eps is added to the L2 norm itself: main_models_new.py:38-42 of the upstream project)
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict__ delta,
+                                   const float* __restrict__ scale, float eps, T* __restrict__ out, int d) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = res[base + i];
+        if (delta != nullptr) {
+            v += to_f32(delta[base + i]);
+            res[base + i] = v;
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = sqrtf((float)d) / (sqrtf(ss) + eps);
+    if (out != nullptr)
+        for (int i = threadIdx.x; i < d; i += blockDim.x) out[base + i] = from_f32<T>(row[i] * inv * scale[i]);
+}
+
+TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const float* scale, float eps,
+                            void* out, int n, int d, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if ((size_t)d * sizeof(float) > 96 * 1024) {
+        tis_set_error("add_rmsnorm: width %d too large (one row must fit 96 KB of shared memory)", d);
+        return TIS_BAD_SIZE;
+    }
+    const int threads = d >= 2048 ? 512 : 256;
+    const size_t smem = (size_t)d * sizeof(float);
+    TIS_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<T><<<n, threads, smem, stream>>>(residual, (const T*)delta, scale, eps, (T*)out, d);
+    });
+    return tis_check_launch("add_rmsnorm");
+}
+
+// ----------------------------------------------------------------------------------
+// rotary position encoding of q and k, and the write of k, v into the row's page.
+//
+// qkv row layout: [H*hd queries | KVH*hd keys | KVH*hd values] (keys before values, as
+// the upstream kv_proj: main_models_new.py:104-106).  q is rotated in place.
+// plane layout: [page][2 (k, v)][KVH][page_size][hd].
+// pairing: half-split (i, i + rot/2) as upstream rotate_half (main_models_new.py:71-73),
+// or interleaved (2i, 2i+1); only the first `rot` entries of a head are rotated.
+// cos/sin tables: [positions][rot/2] float.
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                     const int* __restrict__ row_slot, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, T* __restrict__ plane,
+                                     const int* __restrict__ block_table, int bt_stride, int num_pages,
+                                     int H, int KVH, int hd, int rot, int interleaved, int page_size,
+                                     int write_kv, int* __restrict__ fault) {
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = positions[r];
+    T* row = qkv + (size_t)r * row_stride;
+    const int half = rot >> 1;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+
+    // queries, in place
+    for (int w = threadIdx.x; w < H * half; w += blockDim.x) {
+        const int h = w / half, i = w - h * half;
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        T* x = row + (size_t)h * hd;
+        const float x1 = to_f32(x[a]), x2 = to_f32(x[b]);
+        const float c = cs[i], s = sn[i];
+        x[a] = from_f32<T>(x1 * c - x2 * s);
+        x[b] = from_f32<T>(x2 * c + x1 * s);
+    }
+    if (!write_kv) return;
+
+    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicExch(fault, 1);
+        return;
+    }
+    const int in_page = pos % page_size;
+    T* kdst = plane + ((size_t)page * 2 * KVH * page_size + in_page) * hd;      // + h*page_size*hd
+    T* vdst = kdst + (size_t)KVH * page_size * hd;
+    const T* ksrc = row + (size_t)H * hd;
+    const T* vsrc = ksrc + (size_t)KVH * hd;
+    for (int w = threadIdx.x; w < KVH * half; w += blockDim.x) {
+        const int h = w / half, i = w - h * half;
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float x1 = to_f32(ksrc[h * hd + a]), x2 = to_f32(ksrc[h * hd + b]);
+        const float c = cs[i], s = sn[i];
+        T* o = kdst + (size_t)h * page_size * hd;
+        o[a] = from_f32<T>(x1 * c - x2 * s);
+        o[b] = from_f32<T>(x2 * c + x1 * s);
+    }
+    if (rot < hd) {
+        const int rest = hd - rot;
+        for (int w = threadIdx.x; w < KVH * rest; w += blockDim.x) {
+            const int h = w / rest, i = rot + (w - h * rest);
+            kdst[(size_t)h * page_size * hd + i] = ksrc[h * hd + i];
+        }
+    }
+    for (int w = threadIdx.x; w < KVH * hd; w += blockDim.x) {
+        const int h = w / hd, i = w - h * hd;
+        vdst[(size_t)h * page_size * hd + i] = vsrc[w];
+    }
+}
+
+TIS_API int tis_rope_kv_write(int dtype, void* qkv, int row_stride, const int* positions, const int* row_slot,
+                              const float* cos_t, const float* sin_t, void* plane, const int* block_table,
+                              int bt_stride, int num_pages, int n, int H, int KVH, int hd, int rot,
+                              int interleaved, int page_size, int write_kv, int* fault, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if (rot % 2 || rot > hd || rot < 0) {
+        tis_set_error("rope_kv_write: rotary size %d must be even and at most the head size %d", rot, hd);
+        return TIS_BAD_SIZE;
+    }
+    TIS_DISPATCH_DTYPE(dtype, T,
+        rope_kv_write_kernel<T><<<n, 256, 0, stream>>>((T*)qkv, row_stride, positions, row_slot, cos_t, sin_t,
+                                                        (T*)plane, block_table, bt_stride, num_pages, H, KVH, hd,
+                                                        rot, interleaved, page_size, write_kv, fault));
+    return tis_check_launch("rope_kv_write");
+}
+
+// ----------------------------------------------------------------------------------
+// SwiGLU gating: out[r, j] = silu(gu[r, j]) * gu[r, F + j]   (main_models_new.py:51)
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / F;
+        const int j = (int)(idx - r * F);
+        const float g = to_f32(gu[r * 2 * F + j]);
+        const float u = to_f32(gu[r * 2 * F + F + j]);
+        out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    const size_t total = (size_t)n * F;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TIS_DISPATCH_DTYPE(dtype, T,
+        swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)out, F, total));
+    return tis_check_launch("swiglu");
+}
+
+// ----------------------------------------------------------------------------------
+// residual += delta  (when no norm follows)
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ res, const T* __restrict__ delta, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        res[idx] += to_f32(delta[idx]);
+}
+
+TIS_API int tis_residual_add(int dtype, float* residual, const void* delta, int n, int d, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    const size_t total = (size_t)n * d;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TIS_DISPATCH_DTYPE(dtype, T,
+        residual_add_kernel<T><<<(int)blocks, 256, 0, stream>>>(residual, (const T*)delta, total));
+    return tis_check_launch("residual_add");
+}
+
+// ----------------------------------------------------------------------------------
+// Input of an MTP head (main_models_new.py:164): out[r] = [ h_prev of the row before r |
+// rmsnorm(table[token[r]]) ].  The row before the first row of a request in this step
+// is the row saved in the request's state slot by the step before; the first row's
+// CTA then saves h_prev[last row of the request in this step] there for the next step.
+// ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void mtp_input_kernel(const T* __restrict__ h_prev, T* __restrict__ state,
+                                 const int* __restrict__ row_slot, const int* __restrict__ row_last,
+                                 const int* __restrict__ tokens, const T* __restrict__ table,
+                                 const float* __restrict__ scale, float eps, T* __restrict__ out, int d) {
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    T* o = out + (size_t)r * 2 * d;
+    const bool first = (r == 0) || (row_slot[r - 1] != slot);
+    if (first) {
+        T* st = state + (size_t)slot * d;
+        const T* keep = h_prev + (size_t)row_last[r] * d;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            o[i] = st[i];
+            st[i] = keep[i];
+        }
+    } else {
+        const T* src = h_prev + (size_t)(r - 1) * d;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = src[i];
+    }
+    const T* e = table + (size_t)tokens[r] * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = to_f32(e[i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = sqrtf((float)d) / (sqrtf(ss) + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[d + i] = from_f32<T>(row[i] * inv * scale[i]);
+}
+
+TIS_API int tis_mtp_input(int dtype, const void* h_prev, void* state, const int* row_slot, const int* row_last,
+                          const int* tokens, const void* table, const float* scale, float eps, void* out,
+                          int n, int d, cudaStream_t stream) {
+    if (n <= 0) return TIS_OK;
+    if ((size_t)d * sizeof(float) > 96 * 1024) {
+        tis_set_error("mtp_input: width %d too large (one row must fit 96 KB of shared memory)", d);
+        return TIS_BAD_SIZE;
+    }
+    const size_t smem = (size_t)d * sizeof(float);
+    TIS_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(mtp_input_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mtp_input_kernel<T><<<n, 256, smem, stream>>>((const T*)h_prev, (T*)state, row_slot, row_last, tokens,
+                                                       (const T*)table, scale, eps, (T*)out, d);
+    });
+    return tis_check_launch("mtp_input");
+}

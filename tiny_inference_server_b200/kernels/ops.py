@@ -1,0 +1,202 @@
+"""The device operations of the engine: thin wrappers over the ``extern "C"`` launchers
+of the CUDA library.  There is one implementation of each operation and no fallback:
+without a CUDA device, nvcc-built library and sm_100-class GPU the first call raises.
+
+Conventions: tensors are contiguous CUDA tensors; ``T`` is the compute dtype (bfloat16
+or float32); the residual stream, norm scales, rotary tables and logits are float32;
+integer metadata is int32.  Launches go to torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lib = None
+ABI_VERSION = 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library():
+    """Load (building at the first call) the CUDA library; raise if that is impossible."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this engine runs on hand-written sm_100a kernels only and has no "
+                          "CPU path")
+    major, _minor = torch.cuda.get_device_capability()
+    if major != 10:
+        raise KernelError(f"the kernels are built for sm_100a (B200); this device is sm_{major}{_minor}")
+    path = _build.build()
+    lib = ctypes.CDLL(path)
+    lib.tis_last_error.restype = ctypes.c_char_p
+    lib.tis_abi_version.restype = ctypes.c_int
+    if lib.tis_abi_version() != ABI_VERSION:
+        raise KernelError(f"{path}: launcher interface {lib.tis_abi_version()}, expected {ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def is_loaded() -> bool:
+    return _lib is not None
+
+
+def _check(status: int, lib) -> None:
+    if status != 0:
+        raise KernelError(lib.tis_last_error().decode())
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"unsupported dtype {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f(x: float):
+    return ctypes.c_float(x)
+
+
+# ---------------------------------------------------------------------------------------
+# matrix products (library GEMMs, as upstream uses for every projection:
+# main_models_new.py:20,29,226)
+# ---------------------------------------------------------------------------------------
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32."""
+    if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
+    if out is None:
+        return torch.mm(a, w)
+    return torch.mm(a, w, out=out)
+
+
+def gemm_f32_out(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``a (n, K) @ w (K, N)`` with a float32 result whatever the dtype of the operands."""
+    if a.dtype == torch.float32:
+        return gemm(a, w)
+    return torch.mm(a, w, out_dtype=torch.float32)
+
+
+# ---------------------------------------------------------------------------------------
+# row-wise kernels
+# ---------------------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = float(table[tokens[r]]); out is the float32 residual stream (n, d)."""
+    lib = library()
+    n, d = out.shape
+    _check(lib.tis_embed_rows(_dt(table), _p(table), _p(tokens), _p(out), n, d, _stream()), lib)
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], scale: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """residual += delta (when given), then out = residual*sqrt(d)/(||residual||+eps)*scale."""
+    lib = library()
+    n, d = residual.shape
+    ref = out if out is not None else delta
+    _check(lib.tis_add_rmsnorm(_dt(ref), _p(residual), _p(delta), _p(scale), _f(eps), _p(out), n, d, _stream()), lib)
+    return out
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    lib = library()
+    n, d = residual.shape
+    _check(lib.tis_residual_add(_dt(delta), _p(residual), _p(delta), n, d, _stream()), lib)
+    return residual
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Tensor, cos: torch.Tensor,
+                  sin: torch.Tensor, plane: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+                  num_heads: int, kv_heads: int, head_dim: int, page_size: int, fault: torch.Tensor,
+                  interleaved: bool = False, write_kv: bool = True) -> None:
+    """Rotate the queries of ``qkv`` (n, (H+2*KVH)*hd) in place; rotate the keys and write
+    keys and values of every row into its page of ``plane`` [pages, 2, KVH, page, hd]."""
+    lib = library()
+    n = qkv.shape[0]
+    rot = 2 * cos.shape[1]
+    write = bool(write_kv and plane is not None)
+    _check(lib.tis_rope_kv_write(
+        _dt(qkv), _p(qkv), qkv.stride(0), _p(positions), _p(row_slot), _p(cos), _p(sin),
+        _p(plane if write else None), _p(block_table if write else None),
+        block_table.stride(0) if write else 0, plane.shape[0] if write else 0,
+        n, num_heads, kv_heads, head_dim, rot, int(interleaved), page_size, int(write), _p(fault), _stream()), lib)
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor,
+                    positions: torch.Tensor, row_slot: torch.Tensor, num_heads: int, kv_heads: int,
+                    head_dim: int, page_size: int, window: Optional[int], fault: torch.Tensor,
+                    step=None) -> torch.Tensor:
+    """Causal attention of the step's rows over the cache.  ``q`` is (n, >= H*hd) with the
+    queries first in each row (row stride free); ``out`` is (n, H*hd).  The row at position
+    p of slot s sees keys max(0, p-window+1)..p of ``plane`` through ``block_table[s]``."""
+    lib = library()
+    n = q.shape[0]
+    scale = 1.0 / math.sqrt(head_dim)
+    _check(lib.tis_paged_attention_simt(
+        _dt(q), _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table), block_table.stride(0),
+        plane.shape[0], _p(positions), _p(row_slot), n, num_heads, kv_heads, head_dim, page_size,
+        int(window or 0), _f(scale), _p(fault), _stream()), lib)
+    return out
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, j] = silu(gu[r, j]) * gu[r, F + j]."""
+    lib = library()
+    n, f = out.shape
+    _check(lib.tis_swiglu(_dt(gu), _p(gu), _p(out), n, f, _stream()), lib)
+    return out
+
+
+def mtp_input(h_prev: torch.Tensor, state: torch.Tensor, row_slot: torch.Tensor, row_last: torch.Tensor,
+              tokens: torch.Tensor, table: torch.Tensor, scale: torch.Tensor, eps: float,
+              out: torch.Tensor) -> torch.Tensor:
+    """out[r] = [h_prev of the row before r (the slot's saved row for a request's first row) |
+    rmsnorm(table[tokens[r]])]; saves h_prev[row_last[r]] into the slot for the next step."""
+    lib = library()
+    n, d = h_prev.shape
+    _check(lib.tis_mtp_input(_dt(h_prev), _p(h_prev), _p(state), _p(row_slot), _p(row_last), _p(tokens),
+                             _p(table), _p(scale), _f(eps), _p(out), n, d, _stream()), lib)
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------
+
+def sample_rows(logits: torch.Tensor, temps: torch.Tensor, top_ks: torch.Tensor, top_ps: torch.Tensor,
+                penalties: torch.Tensor, slots: Optional[torch.Tensor], seen_bitmap: Optional[torch.Tensor],
+                seeds: torch.Tensor, counters: torch.Tensor, out_tokens: torch.Tensor,
+                probs_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 ``logits`` (k, V); see csrc/sampling.cu for the order of
+    the transformations.  ``seen_bitmap`` (slots, ceil(V/32)) int32 gets the drawn token's bit."""
+    lib = library()
+    k, v = logits.shape
+    words = seen_bitmap.shape[1] if seen_bitmap is not None else 0
+    _check(lib.tis_sample_rows(_p(logits), k, v, _p(temps), _p(top_ks), _p(top_ps), _p(penalties), _p(slots),
+                               _p(seen_bitmap), words, _p(seeds), _p(counters), _p(out_tokens), _p(probs_out),
+                               _stream()), lib)
+    return out_tokens
+
+
+def bitmap_set(bitmap_row: torch.Tensor, tokens: torch.Tensor) -> None:
+    lib = library()
+    _check(lib.tis_bitmap_set(_p(bitmap_row), _p(tokens), tokens.numel(), _stream()), lib)

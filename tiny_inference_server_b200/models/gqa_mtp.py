@@ -1,0 +1,165 @@
+"""The bias-free pre-norm GQA decoder with multi-token-prediction heads
+(upstream ``Transformer``, main_models_new.py:174-226), put together from parts.
+
+Tensor names are upstream's ``named_parameters()``::
+
+    embedding.weight                                   (V, d)
+    transformer_block_list.{l}.att.q_proj.weight       (d, H*hd)
+    transformer_block_list.{l}.att.kv_proj.weight      (d, 2*KVH*hd)
+    transformer_block_list.{l}.att.rms_norm_att.scale  (d,)
+    transformer_block_list.{l}.att.linear_proj.weight  (H*hd, d)
+    transformer_block_list.{l}.ffn.swig.linear1.weight (d, F)     gate
+    transformer_block_list.{l}.ffn.swig.linear2.weight (d, F)     up
+    transformer_block_list.{l}.ffn.fc.weight           (F, d)
+    transformer_block_list.{l}.rms_norm_ffn.scale      (d,)
+    rms_out.scale                                      (d,)
+    mtp_heads_list.{i}.proj.weight                     (2d, d)
+    mtp_heads_list.{i}.rms_embed.scale                 (d,)
+    mtp_heads_list.{i}.rms_out.scale                   (d,)
+    mtp_heads_list.{i}.trans_block.<the eight of a block>
+    lm_head.weight                                     (V, d)     only when tie_word_embeddings is false
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.model_config import GqaMtpConfig
+from ..kernels import ops
+from ..parts.base import BuildContext, Part, StateSpec, WeightSpec
+from ..parts.block import Block
+from ..parts.embedding import Embedding, LMHead
+from ..parts.stream import ResidualStream
+from ..registry import part, register_architecture
+from .base import Model, ScheduleEntry, StepOutput
+
+
+def _make_block(cfg: GqaMtpConfig, prefix: str, layer_index: int, lag: int, mixer_type: str, ffn_type: str,
+                position) -> Block:
+    """One block of the architecture; every size and constant comes from ``cfg``."""
+    norm_cls = part("norm", cfg.norm_type)
+    mixer_cls = part("mixer", mixer_type)
+    ffn_cls = part("ffn", ffn_type)
+    if mixer_type == "gqa":
+        mixer = mixer_cls(cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, position,
+                          window=cfg.window_of(layer_index), lag=lag, prefix=prefix + "att.")
+    else:
+        mixer = mixer_cls.from_config(cfg, prefix=prefix + "att.", layer_index=layer_index, lag=lag)
+    if ffn_type == "swiglu":
+        ffn = ffn_cls(cfg.hidden_size, cfg.ffn_hidden, prefix=prefix + "ffn.")
+    else:
+        ffn = ffn_cls.from_config(cfg, prefix=prefix + "ffn.", layer_index=layer_index)
+    return Block(
+        norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "att.rms_norm_att."),
+        mixer,
+        norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_norm_ffn."),
+        ffn,
+        prefix=prefix,
+    )
+
+
+class MtpHead(Part):
+    """Head i (upstream ``mtp_head``, main_models_new.py:155-171): at position p it takes the
+    previous stage's normalised output at p and the embedding of token p+1+i,
+    ``u = cat[h, rms_embed(e)] @ proj``, runs one block at position p over its own cache,
+    and normalises: ``g = rms_out(u)``.  It runs 1+i positions behind the trunk."""
+
+    def __init__(self, cfg: GqaMtpConfig, index: int, embedding: Embedding, position):
+        prefix = f"mtp_heads_list.{index}."
+        super().__init__(prefix)
+        norm_cls = part("norm", cfg.norm_type)
+        self.index = index
+        self.lag = 1 + index
+        self.width = cfg.hidden_size
+        self.embedding = embedding
+        self.rms_embed = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_embed.")
+        self.rms_out = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_out.")
+        self.block = _make_block(cfg, prefix + "trans_block.", cfg.num_layers + index, self.lag, "gqa", "swiglu",
+                                 position)
+        self.w_proj: Optional[torch.Tensor] = None
+
+    def children(self):
+        return (self.rms_embed, self.rms_out, self.block)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"proj.weight": WeightSpec((2 * self.width, self.width))}
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        self.w_proj = tensors[self.prefix + "proj.weight"].to(device=ctx.device, dtype=ctx.dtype).contiguous()
+
+    def forward(self, h_prev: torch.Tensor, pending_rows: torch.Tensor, step, entry: ScheduleEntry) -> torch.Tensor:
+        """``h_prev``: the previous stage's output at this step's rows; ``pending_rows``
+        ``[slots, width]``: per request, that stage's output at the last position fed."""
+        n = h_prev.shape[0]
+        trunk = step.stage(0)
+        cat = torch.empty((n, 2 * self.width), dtype=h_prev.dtype, device=h_prev.device)
+        ops.mtp_input(h_prev, pending_rows, trunk.row_slot, trunk.row_last, trunk.tokens, self.embedding.table,
+                      self.rms_embed.scale, self.rms_embed.eps, cat)
+        u = ops.gemm(cat, self.w_proj)
+        stream = ResidualStream(torch.zeros((n, self.width), dtype=torch.float32, device=h_prev.device))
+        stream.add(u)
+        self.block.forward(stream, step.stage(self.lag), entry.binding)
+        return stream.normed(self.rms_out)
+
+
+class GqaMtpModel(Model):
+    def __init__(self, cfg: GqaMtpConfig):
+        super().__init__()
+        self.config = cfg
+        self.vocab_size = cfg.vocab_size
+        self.max_positions = cfg.max_context
+        pos_cls = part("position", cfg.position_type)
+        self.position = pos_cls(cfg.head_dim, cfg.rope_theta, cfg.max_context)
+        self.embedding = Embedding(cfg.vocab_size, cfg.hidden_size)
+        mixers = cfg.mixer_types or ["gqa"] * cfg.num_layers
+        ffns = cfg.ffn_types or ["swiglu"] * cfg.num_layers
+        self.blocks: List[Block] = [
+            _make_block(cfg, f"transformer_block_list.{l}.", l, 0, mixers[l], ffns[l], self.position)
+            for l in range(cfg.num_layers)
+        ]
+        norm_cls = part("norm", cfg.norm_type)
+        self.rms_out = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix="rms_out.")
+        self.heads: List[MtpHead] = [MtpHead(cfg, i, self.embedding, self.position)
+                                     for i in range(cfg.num_mtp_heads)]
+        self.lm_head = LMHead(cfg.vocab_size, cfg.hidden_size, self.embedding if cfg.tie_word_embeddings else None)
+        # the order in which layers run is data
+        self.entries = [ScheduleEntry(self.blocks[l], source=src) for (l, src) in cfg.schedule()]
+        self.n_trunk_entries = len(self.entries)
+        self.entries += [ScheduleEntry(h.block) for h in self.heads]
+        self._pending: List[torch.Tensor] = []
+
+    def top_parts(self):
+        return [self.embedding, self.position, *self.blocks, self.rms_out, *self.heads, self.lm_head]
+
+    def extra_states(self, ctx: BuildContext) -> Dict[str, StateSpec]:
+        # per MTP head: the previous stage's output row at the last position fed
+        return {f"mtp_pending{i}": StateSpec((self.config.hidden_size,), ctx.dtype)
+                for i in range(len(self.heads))}
+
+    def bind(self, cache) -> None:
+        super().bind(cache)
+        self._pending = [cache.states[f"mtp_pending{i}"] for i in range(len(self.heads))]
+
+    def forward(self, step, want_rows: torch.Tensor, aux: bool = False) -> StepOutput:
+        """Trunk over the step's rows, then (``aux``) the MTP heads in order, each fed by the
+        stage before it (server.py:328-359 upstream); logits only at the wanted rows."""
+        stream = ResidualStream(self.embedding.forward(step.tokens))
+        for e in self.entries[: self.n_trunk_entries]:
+            e.block.forward(stream, step, e.binding)
+        h = stream.normed(self.rms_out)
+        out = StepOutput(main=self.lm_head.forward(h.index_select(0, want_rows)))
+        if aux:
+            prev = h
+            for i, head in enumerate(self.heads):
+                prev = head.forward(prev, self._pending[i], step, self.entries[self.n_trunk_entries + i])
+                out.aux.append(self.lm_head.forward(prev.index_select(0, want_rows)))
+                out.aux_valid.append(step.stage(head.lag).row_slot.index_select(0, want_rows) >= 0)
+        return out
+
+
+def build(cfg: GqaMtpConfig) -> GqaMtpModel:
+    return GqaMtpModel(cfg)
+
+
+register_architecture(GqaMtpConfig.architecture, GqaMtpConfig, build)

@@ -1,0 +1,48 @@
+"""Feed-forward parts."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from ..registry import register_part
+from .base import BuildContext, FeedForward, WeightSpec
+
+
+class SwiGLU(FeedForward):
+    """``(silu(x W1) * (x W2)) W3`` (upstream ``swiglu`` and ``ffn_router``,
+    main_models_new.py:44-60); weights ``(in, out)``: W1 gate and W2 up ``(width, hidden)``,
+    W3 ``(hidden, width)``.  On the device gate and up are one matrix ``(width, 2*hidden)``."""
+
+    def __init__(self, width: int, hidden: int, prefix: str = "", names: Optional[Dict[str, str]] = None):
+        super().__init__(prefix)
+        self.width = width
+        self.hidden = hidden
+        self.names = {"gate": "swig.linear1.weight", "up": "swig.linear2.weight", "down": "fc.weight"}
+        if names:
+            self.names.update(names)
+        self.w_gate_up = None
+        self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {
+            self.names["gate"]: WeightSpec((self.width, self.hidden)),
+            self.names["up"]: WeightSpec((self.width, self.hidden)),
+            self.names["down"]: WeightSpec((self.hidden, self.width)),
+        }
+
+    def load(self, tensors, ctx: BuildContext) -> None:
+        gate = tensors[self.prefix + self.names["gate"]]
+        up = tensors[self.prefix + self.names["up"]]
+        self.w_gate_up = torch.cat([gate, up], dim=1).to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.w_down = tensors[self.prefix + self.names["down"]].to(device=ctx.device, dtype=ctx.dtype).contiguous()
+
+    def forward(self, x: torch.Tensor, step=None) -> torch.Tensor:
+        gu = ops.gemm(x, self.w_gate_up)
+        h = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
+        ops.swiglu(gu, h)
+        return ops.gemm(h, self.w_down)
+
+
+register_part("ffn", "swiglu", SwiGLU)
