@@ -1,0 +1,326 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (tests/kernel_refs.py), in
+float32 and bfloat16, at sizes other than the engine's tiny models: widths and
+vocabularies that are no power of two, head sizes in steps of 16, odd numbers of heads
+and groups, scattered pages, padding rows."""
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _ops():
+    from tiny_inference_server_b200.kernels import ops
+    ops.library()
+    return ops
+
+
+def _tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+def _rand(shape, dtype, gen, scale=1.0):
+    return (torch.randn(shape, generator=gen, dtype=torch.float32) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,d,V", [(5, 72, 301), (33, 1536, 1000), (2, 8200, 77)])
+def test_embed_rows(dtype, n, d, V):
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    table = _rand((V, d), dtype, g)
+    tokens = torch.randint(0, V, (n,), generator=g, dtype=torch.int32)
+    want = ref.embed_rows(table, tokens, torch.empty(n, d))
+    got = ops.embed_rows(table.cuda(), tokens.cuda(), torch.empty(n, d, device="cuda"))
+    torch.testing.assert_close(got.cpu(), want, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,d", [(1, 48), (7, 120), (19, 1536), (3, 4100), (2, 16384)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_add_rmsnorm(dtype, n, d, with_delta):
+    ops = _ops()
+    g = torch.Generator().manual_seed(1)
+    res = torch.randn(n, d, generator=g) * 3
+    delta = _rand((n, d), dtype, g) if with_delta else None
+    scale = 1 + 0.1 * torch.randn(d, generator=g)
+    eps = 1e-3
+    res_ref = res.clone()
+    want = ref.add_rmsnorm(res_ref, delta, scale, eps, torch.empty(n, d, dtype=dtype))
+    res_dev = res.cuda()
+    got = ops.add_rmsnorm(res_dev, None if delta is None else delta.cuda(), scale.cuda(), eps,
+                          torch.empty(n, d, dtype=dtype, device="cuda"))
+    torch.testing.assert_close(res_dev.cpu(), res_ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
+
+
+def test_add_rmsnorm_eps_is_added_to_the_norm():
+    """With a large eps the two forms of RMSNorm differ; the kernel follows
+    x*sqrt(d)/(||x||+eps), not x*rsqrt(mean(x^2)+eps)."""
+    ops = _ops()
+    d = 64
+    x = torch.full((1, d), 0.5)
+    scale = torch.ones(d)
+    eps = 2.0
+    got = ops.add_rmsnorm(x.cuda(), None, scale.cuda(), eps, torch.empty(1, d, device="cuda")).cpu()
+    want = x * math.sqrt(d) / (x.norm() + eps)
+    other = x * torch.rsqrt((x * x).mean() + eps)
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+    assert (got - other).abs().max() > 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,F", [(3, 200), (17, 4096), (1, 10)])
+def test_swiglu(dtype, n, F):
+    ops = _ops()
+    g = torch.Generator().manual_seed(2)
+    gu = _rand((n, 2 * F), dtype, g, 2.0)
+    want = ref.swiglu(gu, torch.empty(n, F, dtype=dtype))
+    got = ops.swiglu(gu.cuda(), torch.empty(n, F, dtype=dtype, device="cuda"))
+    torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_residual_add(dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    res = torch.randn(9, 130, generator=g)
+    delta = _rand((9, 130), dtype, g)
+    want = res + delta.float()
+    got = ops.residual_add(res.cuda(), delta.cuda())
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-6, atol=1e-6)
+
+
+def _scattered_tables(n_slots, max_pages, num_pages, gen):
+    perm = torch.randperm(num_pages, generator=gen)
+    table = torch.full((n_slots, max_pages), -1, dtype=torch.int32)
+    k = 0
+    for s in range(n_slots):
+        for p in range(max_pages):
+            if k < num_pages:
+                table[s, p] = perm[k]
+                k += 1
+    return table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,hd,page,rot,inter", [(4, 2, 16, 16, None, False), (6, 2, 48, 4, None, False),
+                                                      (5, 5, 32, 8, 16, False), (3, 1, 64, 32, None, True),
+                                                      (12, 3, 128, 16, None, False)])
+def test_rope_kv_write(dtype, H, KVH, hd, page, rot, inter):
+    ops = _ops()
+    g = torch.Generator().manual_seed(4)
+    n, slots, max_pages = 11, 3, 6
+    num_pages = slots * max_pages
+    rot = rot or hd
+    table = _scattered_tables(slots, max_pages, num_pages, g)
+    qkv = _rand((n, (H + 2 * KVH) * hd), dtype, g)
+    positions = torch.tensor([0, 1, 2, 3, page - 1, page, page * 2 - 1, page * 2, 5, 0, 9], dtype=torch.int32)
+    row_slot = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1, 2, -1, 2], dtype=torch.int32)
+    ang = torch.outer(torch.arange(80, dtype=torch.float64), 10000.0 ** (-2.0 * torch.arange(rot // 2) / rot))
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    plane = torch.zeros(num_pages, 2, KVH, page, hd, dtype=dtype)
+    fault = torch.zeros(4, dtype=torch.int32)
+    qkv_ref, plane_ref = qkv.clone(), plane.clone()
+    ref.rope_kv_write(qkv_ref, positions, row_slot, cos, sin, plane_ref, table, H, KVH, hd, page, fault,
+                      interleaved=inter)
+    qkv_dev, plane_dev, fault_dev = qkv.cuda(), plane.cuda(), fault.cuda()
+    ops.rope_kv_write(qkv_dev, positions.cuda(), row_slot.cuda(), cos.cuda(), sin.cuda(), plane_dev, table.cuda(),
+                      H, KVH, hd, page, fault_dev, interleaved=inter)
+    tol = dict(rtol=1e-6, atol=1e-6) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    valid = row_slot >= 0
+    torch.testing.assert_close(qkv_dev.cpu()[valid].float(), qkv_ref[valid].float(), **tol)
+    torch.testing.assert_close(plane_dev.cpu().float(), plane_ref.float(), **tol)
+    assert int(fault_dev[0]) == 0
+    # the padding row wrote nothing and was not rotated
+    assert torch.equal(qkv_dev.cpu()[9], qkv[9])
+
+
+def test_rope_kv_write_reports_bad_page():
+    ops = _ops()
+    H, KVH, hd, page = 2, 1, 16, 4
+    qkv = torch.randn(1, (H + 2 * KVH) * hd).cuda()
+    table = torch.tensor([[99]], dtype=torch.int32).cuda()          # outside a pool of 2 pages
+    plane = torch.zeros(2, 2, KVH, page, hd).cuda()
+    fault = torch.zeros(4, dtype=torch.int32).cuda()
+    cos = torch.ones(8, hd // 2).cuda()
+    sin = torch.zeros(8, hd // 2).cuda()
+    ops.rope_kv_write(qkv, torch.zeros(1, dtype=torch.int32).cuda(), torch.zeros(1, dtype=torch.int32).cuda(),
+                      cos, sin, plane, table, H, KVH, hd, page, fault)
+    assert int(fault[0]) != 0
+    assert float(plane.abs().sum()) == 0.0
+
+
+def _fill_cache(dtype, slots_len, KVH, hd, page, gen, scale=1.0):
+    """Random keys and values for each slot, written into scattered pages."""
+    max_pages = max((L + page - 1) // page for L in slots_len) + 1
+    num_pages = len(slots_len) * max_pages + 3
+    table = _scattered_tables(len(slots_len), max_pages, num_pages, gen)
+    plane = torch.zeros(num_pages, 2, KVH, page, hd, dtype=dtype)
+    for s, L in enumerate(slots_len):
+        k = _rand((L, KVH, hd), dtype, gen, scale)
+        v = _rand((L, KVH, hd), dtype, gen)
+        for t in range(L):
+            pg = int(table[s, t // page])
+            plane[pg, 0, :, t % page] = k[t]
+            plane[pg, 1, :, t % page] = v[t]
+    return plane, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KVH,hd,page,window", [(4, 2, 16, 16, None), (6, 2, 48, 4, None), (8, 2, 64, 16, None),
+                                                  (5, 5, 32, 8, 20), (12, 3, 128, 16, None), (3, 1, 80, 32, 37),
+                                                  (7, 7, 256, 16, None), (16, 1, 112, 8, None)])
+def test_paged_attention(dtype, H, KVH, hd, page, window):
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    lens = [37, 300, 1, 130]
+    plane, table = _fill_cache(dtype, lens, KVH, hd, page, g)
+    # rows: decode rows at the end of each slot, a chunk of rows inside slot 1, a padding row
+    rows = [(0, 36), (1, 299), (2, 0), (3, 129)] + [(1, p) for p in range(120, 140)] + [(-1, 0), (3, 64), (3, 15),
+                                                                                         (3, 16), (0, 0)]
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    stride = (H + 2 * KVH) * hd
+    q = _rand((n, stride), dtype, g)
+    fault = torch.zeros(4, dtype=torch.int32)
+    want = ref.paged_attention(q, torch.empty(n, H * hd, dtype=dtype), plane, table, positions, row_slot, H, KVH, hd,
+                               page, window, fault)
+    fault_dev = fault.cuda()
+    got = ops.paged_attention(q.cuda(), torch.empty(n, H * hd, dtype=dtype, device="cuda"), plane.cuda(),
+                              table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault_dev)
+    tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tol)
+    assert int(fault_dev[0]) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_a_far_key(dtype):
+    """One key among hundreds, at a page's first slot far back, is made to stand out: its
+    value must dominate the output.  A kernel that skips a page, or reads a neighbour's,
+    fails here although random inputs would hide it."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(6)
+    H, KVH, hd, page = 4, 2, 32, 16
+    L = 700
+    plane, table = _fill_cache(dtype, [L], KVH, hd, page, g, scale=0.1)
+    n = 3
+    q = _rand((n, (H + 2 * KVH) * hd), dtype, g, 0.1)
+    for far in (0, 16 * 7, 16 * 30 + 15):
+        pl = plane.clone()
+        pg = int(table[0, far // page])
+        marker = torch.zeros(hd)
+        marker[3] = 30.0
+        pl[pg, 0, :, far % page] = marker.to(dtype)          # key: large along one axis
+        pl[pg, 1, :, far % page] = torch.full((hd,), 5.0).to(dtype)   # value: easy to recognise
+        qq = q.clone()
+        qq[:, : H * hd] = 0
+        for h in range(H):
+            qq[:, h * hd + 3] = 30.0                         # every query looks along that axis
+        positions = torch.tensor([L - 1, L - 2, far], dtype=torch.int32)
+        row_slot = torch.zeros(n, dtype=torch.int32)
+        fault = torch.zeros(4, dtype=torch.int32).cuda()
+        got = ops.paged_attention(qq.cuda(), torch.empty(n, H * hd, dtype=dtype, device="cuda"), pl.cuda(),
+                                  table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, None, fault)
+        assert (got.float() - 5.0).abs().max() < 0.05, f"far key at {far} not found"
+        want = ref.paged_attention(qq, torch.empty(n, H * hd, dtype=dtype), pl, table, positions, row_slot, H, KVH,
+                                   hd, page, None, torch.zeros(4, dtype=torch.int32))
+        torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_window_edge(dtype):
+    """The key just outside the window is made to stand out and must be ignored; the key
+    just inside must be seen."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(7)
+    H, KVH, hd, page, W = 2, 1, 16, 8, 24
+    L = 100
+    base, table = _fill_cache(dtype, [L], KVH, hd, page, g, scale=0.05)
+    pos = 90
+    for key_pos, seen in ((pos - W, False), (pos - W + 1, True)):
+        pl = base.clone()
+        pg = int(table[0, key_pos // page])
+        marker = torch.zeros(hd)
+        marker[0] = 40.0
+        pl[pg, 0, 0, key_pos % page] = marker.to(dtype)
+        pl[pg, 1, 0, key_pos % page] = torch.full((hd,), 9.0).to(dtype)
+        q = torch.zeros(1, (H + 2 * KVH) * hd)
+        q[0, 0] = 40.0
+        q[0, hd] = 40.0
+        q = q.to(dtype)
+        fault = torch.zeros(4, dtype=torch.int32).cuda()
+        got = ops.paged_attention(q.cuda(), torch.empty(1, H * hd, dtype=dtype, device="cuda"), pl.cuda(),
+                                  table.cuda(), torch.tensor([pos], dtype=torch.int32).cuda(),
+                                  torch.zeros(1, dtype=torch.int32).cuda(), H, KVH, hd, page, W, fault)
+        if seen:
+            assert (got.float() - 9.0).abs().max() < 0.1
+        else:
+            assert got.float().abs().max() < 1.0
+
+
+def test_paged_attention_refuses_bad_head_size():
+    ops = _ops()
+    from tiny_inference_server_b200.kernels.ops import KernelError
+    z = torch.zeros(1, 3 * 24, device="cuda")
+    with pytest.raises(KernelError):
+        ops.paged_attention(z, torch.zeros(1, 24, device="cuda"), torch.zeros(1, 2, 1, 4, 24, device="cuda"),
+                            torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
+                            torch.zeros(1, dtype=torch.int32, device="cuda"),
+                            torch.zeros(1, dtype=torch.int32, device="cuda"), 1, 1, 24, 4, None,
+                            torch.zeros(4, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mtp_input(dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(8)
+    n, d, V, slots = 9, 72, 50, 4
+    h_prev = _rand((n, d), dtype, g)
+    state = _rand((slots, d), dtype, g)
+    row_slot = torch.tensor([2, 2, 2, 0, 3, 3, -1, 1, 1], dtype=torch.int32)
+    row_last = torch.tensor([2, 2, 2, 3, 5, 5, 6, 8, 8], dtype=torch.int32)
+    tokens = torch.randint(0, V, (n,), generator=g, dtype=torch.int32)
+    table = _rand((V, d), dtype, g)
+    scale = 1 + 0.1 * torch.randn(d, generator=g)
+    state_ref = state.clone()
+    want = ref.mtp_input(h_prev, state_ref, row_slot, row_last, tokens, table, scale, 1e-5,
+                         torch.zeros(n, 2 * d, dtype=dtype))
+    state_dev = state.cuda()
+    got = ops.mtp_input(h_prev.cuda(), state_dev, row_slot.cuda(), row_last.cuda(), tokens.cuda(), table.cuda(),
+                        scale.cuda(), 1e-5, torch.zeros(n, 2 * d, dtype=dtype, device="cuda"))
+    torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
+    torch.testing.assert_close(state_dev.cpu().float(), state_ref.float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,K,N", [(1, 64, 48), (7, 120, 301), (64, 1536, 2304), (130, 200, 120)])
+def test_gemm(dtype, n, K, N):
+    ops = _ops()
+    g = torch.Generator().manual_seed(9)
+    a = _rand((n, K), dtype, g)
+    w = _rand((K, N), dtype, g, 0.05)
+    want = a.double() @ w.double()
+    got = ops.gemm(a.cuda(), w.cuda())
+    assert got.dtype == dtype
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.cpu().double(), want, **tol)
+    got32 = ops.gemm_f32_out(a.cuda(), w.cuda())
+    assert got32.dtype == torch.float32
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(got32.cpu().double(), want, **tol)
+
+
+def test_float32_products_are_not_tf32():
+    """A product whose exact value needs more than TF32's 10 mantissa bits."""
+    ops = _ops()
+    a = torch.full((4, 256), 1.0 + 2.0 ** -12).cuda()
+    w = torch.full((256, 8), 1.0).cuda()
+    got = ops.gemm(a, w).cpu()
+    assert abs(float(got[0, 0]) - 256 * (1.0 + 2.0 ** -12)) < 1e-4

@@ -1,0 +1,137 @@
+"""Trace replay on the GPU against the plain implementation: each request alone and
+whole; most of it in one step and the last 32 tokens one by one; portions of changing
+size down to two tokens; up to four live requests mixed, with so few pages that they are
+used again — in float32 and bfloat16, for tiny configurations that differ in every size
+and option.  Most replays run in this process through the engine's replayer; the
+``bin/trace_run`` program itself is driven over pipes as well."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import tiny_configs
+import trace_tools
+from tiny_inference_server_b200.trace import TraceReplayer, make_runner
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir))
+LENGTHS = {"A": [1, 7, 16, 33, 50, 97, 64, 80, 120, 111, 70], "B": [2, 9, 31, 64, 100, 130, 77, 90, 128, 200],
+           "C": [3, 40, 61, 90, 150, 70, 101, 64, 33, 88], "D": [5, 18, 47, 80, 33, 60, 90, 64, 71]}
+# float32: rounding of a float32 engine against a float64 oracle.
+# bfloat16: weights are the same bfloat16 numbers on both sides; activations are rounded
+# to bfloat16 between kernels (8 bits of mantissa) on logits of size ~0.1-1.
+TOL = {"float32": 2e-4, "bfloat16": 3e-2}
+
+_cache = {}
+
+
+def _setup(name, tmp_path_factory):
+    if name in _cache:
+        return _cache[name]
+    cfg, page, seed = tiny_configs.ALL[name]
+    folder = tiny_configs.make_model_folder(cfg, seed, str(tmp_path_factory.mktemp(f"model{name}")))
+    c = plain_model.read_config(folder)
+    W = plain_model.read_weights(folder)
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], LENGTHS[name], seed=100 + seed)
+    seqs = {f"r{i}": p for i, p in enumerate(prompts)}
+    plain = {rid: plain_model.plain_forward(c, W, toks) for rid, toks in seqs.items()}
+    _cache[name] = (cfg, page, folder, seqs, plain)
+    return _cache[name]
+
+
+def _steps(mode, seqs):
+    if mode == "whole":
+        return trace_tools.trace_whole(seqs)
+    if mode == "tail":
+        return trace_tools.trace_tail(seqs, tail=32)
+    if mode == "chunks":
+        return trace_tools.trace_chunks(seqs)
+    return trace_tools.trace_mixed(seqs, max_live=4)
+
+
+def _compare(cfg, steps, out_dir, seqs, plain, tol, mtp=True):
+    got = trace_tools.gather(steps, out_dir, cfg["vocab_size"])
+    worst = 0.0
+    for rid, toks in seqs.items():
+        for p in range(len(toks)):
+            err = float(np.abs(got[rid][p] - plain[rid]["main"][p].numpy()).max())
+            assert err < tol, f"main logits of {rid} at position {p}: max error {err} (first wrong place)"
+            worst = max(worst, err)
+    if mtp:
+        for i in range(cfg["num_mtp_heads"]):
+            g = trace_tools.gather(steps, out_dir, cfg["vocab_size"], suffix=f"mtp{i}.f32")
+            for rid, toks in seqs.items():
+                for p in range(len(toks)):
+                    hp = p - 1 - i
+                    if hp < 0:
+                        assert np.isnan(g[rid][p]).all()
+                        continue
+                    err = float(np.abs(g[rid][p] - plain[rid]["mtp"][i][hp].numpy()).max())
+                    assert err < tol, f"mtp head {i} of {rid} at position {hp}: max error {err}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+def test_replay_matches_plain(name, mode, dtype, tmp_path, tmp_path_factory):
+    cfg, page, folder, seqs, plain = _setup(name, tmp_path_factory)
+    steps = _steps(mode, seqs)
+    max_tokens = trace_tools.max_live_tokens(steps, round_to=64)
+    runner = make_runner(folder, dtype, max_tokens, page_size=page, mtp=True)
+    if mode == "mixed":
+        import random
+        for g in runner.cache.groups:
+            g.pool.shuffle(random.Random(5))
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    runner.cache.check()
+    assert runner.cache.drained()
+    if mode == "mixed":
+        pool = runner.cache.groups[0].pool
+        assert pool.allocations > pool.num_pages, "the trace does not use pages again"
+    _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path, tmp_path_factory):
+    """bin/trace_run over pipes: one step at a time, the next only after ``done <step>``."""
+    cfg, page, folder, seqs, plain = _setup("B", tmp_path_factory)
+    steps = trace_tools.trace_mixed(seqs, max_live=4)
+    max_tokens = trace_tools.max_live_tokens(steps, round_to=64)
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                             "--out", out_dir, "--max-tokens", str(max_tokens)],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for s in steps:
+        proc.stdin.write(json.dumps(s) + "\n")
+        proc.stdin.flush()
+        line = proc.stdout.readline().strip()
+        assert line == f"done {s['step']}", line
+    proc.stdin.close()
+    assert proc.wait(timeout=120) == 0
+    _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype], mtp=False)
+
+
+def test_modes_agree_with_each_other_bitwise_close(tmp_path, tmp_path_factory):
+    """In float32 the four ways of cutting give logits that agree far below the tolerance
+    against the oracle: a fault of the cache or the batch would show here first."""
+    cfg, page, folder, seqs, plain = _setup("A", tmp_path_factory)
+    outs = {}
+    for mode in ("whole", "tail", "chunks", "mixed"):
+        steps = _steps(mode, seqs)
+        runner = make_runner(folder, "float32", trace_tools.max_live_tokens(steps), page_size=page, mtp=False)
+        out_dir = str(tmp_path / mode)
+        TraceReplayer(runner, out_dir).run(json.dumps(s) for s in steps)
+        outs[mode] = trace_tools.gather(steps, out_dir, cfg["vocab_size"])
+    for mode in ("tail", "chunks", "mixed"):
+        for rid, toks in seqs.items():
+            for p in range(len(toks)):
+                err = float(np.abs(outs[mode][rid][p] - outs["whole"][rid][p]).max())
+                assert err < 2e-5, f"{mode} vs whole: {rid} position {p}: {err}"

@@ -1,0 +1,107 @@
+"""The sampling kernel: probabilities against the plain implementation of upstream's
+sampler (tests/plain_model.py: plain_probs), arg-max, determinism, and the distribution of
+many draws."""
+import pytest
+import torch
+
+import kernel_refs as ref
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from tiny_inference_server_b200.kernels import ops
+    ops.library()
+    return ops
+
+
+def _run(ops, logits, temps, top_ks, top_ps, pens, seen_lists, seeds, counters, want_probs=True):
+    k, V = logits.shape
+    words = (V + 31) // 32
+    bitmap = torch.zeros(k, words, dtype=torch.int32)
+    for r, toks in enumerate(seen_lists):
+        if toks:
+            ref.bitmap_set(bitmap[r], torch.tensor(toks))
+    dev = "cuda"
+    probs = torch.empty(k, V, device=dev) if want_probs else None
+    out = torch.empty(k, dtype=torch.int32, device=dev)
+    bm = bitmap.to(dev)
+    ops.sample_rows(logits.to(dev), torch.tensor(temps, dtype=torch.float32, device=dev),
+                    torch.tensor(top_ks, dtype=torch.int32, device=dev),
+                    torch.tensor(top_ps, dtype=torch.float32, device=dev),
+                    torch.tensor(pens, dtype=torch.float32, device=dev),
+                    torch.arange(k, dtype=torch.int32, device=dev), bm,
+                    torch.tensor(seeds, dtype=torch.int64, device=dev),
+                    torch.tensor(counters, dtype=torch.int64, device=dev), out, probs)
+    return out.cpu(), (probs.cpu() if want_probs else None), bm.cpu()
+
+
+@pytest.mark.parametrize("V", [6, 100, 301, 49152])
+def test_probabilities_match_upstream_formulas(V):
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    settings = [(1.0, 0, 0.0, 1.0), (0.7, 0, 0.0, 1.0), (1.0, 3, 0.0, 1.0), (1.0, 0, 0.9, 1.0),
+                (0.9, 50, 0.95, 1.1), (1.3, 5, 0.5, 1.3), (1.0, 0, 0.0, 2.0), (0.5, 2, 0.3, 1.0)]
+    k = len(settings)
+    logits = torch.randn(k, V, generator=g) * 3
+    seen = [torch.randint(0, V, (min(V, 20),), generator=g).tolist() for _ in range(k)]
+    out, probs, _ = _run(ops, logits, [s[0] for s in settings], [s[1] for s in settings],
+                         [s[2] for s in settings], [s[3] for s in settings], seen, [1] * k, [0] * k)
+    for r, (t, tk, tp, pen) in enumerate(settings):
+        want = plain_model.plain_probs(logits[r], t, tk, tp, pen, seen[r]).float()
+        torch.testing.assert_close(probs[r], want, rtol=1e-4, atol=1e-6)
+        assert probs[r, out[r]] > 0
+
+
+def test_greedy_takes_lowest_index_of_the_maximum_and_applies_penalty():
+    ops = _ops()
+    V = 100
+    lg = torch.zeros(3, V)
+    lg[0, 5] = 5.0
+    lg[0, 7] = 4.9
+    lg[1] = lg[0]
+    lg[2, 40] = 2.0
+    lg[2, 60] = 2.0
+    out, _, bm = _run(ops, lg, [0.0, 0.0, 1.0], [0, 0, 1], [0.0] * 3, [1.0, 2.0, 1.0], [[], [5], []], [0] * 3,
+                      [0] * 3)
+    # upstream's check (test_server.py:120-122): the penalty pushes token 5 below token 7
+    assert out.tolist() == [5, 7, 40]
+
+
+def test_same_seed_same_token_and_seen_bitmap_grows():
+    ops = _ops()
+    g = torch.Generator().manual_seed(1)
+    V = 1000
+    logits = torch.randn(4, V, generator=g)
+    a, _, bm = _run(ops, logits, [1.0] * 4, [0] * 4, [0.0] * 4, [1.2] * 4, [[1]] * 4, [11, 11, 12, 11], [0, 0, 0, 1])
+    b, _, _ = _run(ops, logits, [1.0] * 4, [0] * 4, [0.0] * 4, [1.2] * 4, [[1]] * 4, [11, 11, 12, 11], [0, 0, 0, 1])
+    assert a.tolist() == b.tolist()
+    for r in range(4):
+        t = int(a[r])
+        assert (int(bm[r, t >> 5]) >> (t & 31)) & 1
+    # the reference sampler draws with the same generator and inverse CDF
+    want = torch.empty(4, dtype=torch.int32)
+    bitmap = torch.zeros(4, (V + 31) // 32, dtype=torch.int32)
+    for r in range(4):
+        ref.bitmap_set(bitmap[r], torch.tensor([1]))
+    ref.sample_rows(logits, [1.0] * 4, [0] * 4, [0.0] * 4, [1.2] * 4, list(range(4)), bitmap, [11, 11, 12, 11],
+                    [0, 0, 0, 1], want)
+    assert sum(int(x == y) for x, y in zip(a.tolist(), want.tolist())) >= 3
+
+
+@pytest.mark.parametrize("setting", [(1.0, 0, 0.0), (1.0, 3, 0.9), (0.8, 0, 0.7)])
+def test_distribution_of_many_draws(setting):
+    """4096 draws from one row of six logits (upstream's distribution test uses vocabulary 6,
+    test_server.py:124-141): total variation to the exact probabilities stays small."""
+    ops = _ops()
+    t, tk, tp = setting
+    V, N = 6, 4096
+    row = torch.tensor([1.0, 0.5, -0.3, 2.0, 0.0, 1.5])
+    logits = row.repeat(N, 1)
+    out, _, _ = _run(ops, logits, [t] * N, [tk] * N, [tp] * N, [1.0] * N, [[]] * N, [5] * N, list(range(N)),
+                     want_probs=False)
+    hist = torch.bincount(out.long(), minlength=V).double() / N
+    want = plain_model.plain_probs(row, t, tk, tp)
+    tv = 0.5 * (hist - want).abs().sum()
+    assert tv < 0.03, f"total variation {tv}"

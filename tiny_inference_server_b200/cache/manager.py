@@ -125,6 +125,10 @@ class CacheManager:
         self._require(slot)
         if not (0 <= new_len <= self.length[slot]):
             raise CacheError(f"slot {slot}: cannot truncate {self.length[slot]} tokens to {new_len}")
+        for g in self.groups:
+            if g.dead_before(new_len) < g.first[slot]:
+                raise CacheError(f"slot {slot}: group {g.gid} has already given back pages that a step from "
+                                 f"position {new_len} would read")
         self.length[slot] = new_len
 
     def pages_held(self, slot: int) -> int:

@@ -38,6 +38,7 @@ class PagePool:
         self.num_pages = num_pages
         self._free = deque(range(num_pages))
         self._held = [False] * num_pages
+        self.allocations = 0          # pages handed out so far (more than num_pages: pages were used again)
 
     @property
     def free(self) -> int:
@@ -50,6 +51,7 @@ class PagePool:
         if self._held[p]:
             raise CacheError(f"page {p} was on the free list while held")
         self._held[p] = True
+        self.allocations += 1
         return p
 
     def release(self, page: int) -> None:
