@@ -1,0 +1,295 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py --impl reference        (the upstream project's own code, if installed)
+
+A "step" is one decode step: every live request gets one token.  The default run has the
+layer sizes of the upstream 0.9B model (30 layers, width 1536, 12 query and 3 kv heads of
+128, SwiGLU 4096, vocabulary 49152, tied output matrix), random weights from a seed,
+8 requests that each hold about 4096 tokens of (synthetic) cache, bfloat16.  It prints
+one JSON line: decode tokens a second timed on the device with CUDA events (``value``),
+the same through the Python entry point with host tokens in and out (``e2e``), a prefill
+of 2048 tokens, the decode step's HBM roofline, and decode at batch 1 and 64.
+The step reads ~1.6 GB of weights and ~1.5 GB of cache, far more than the 126 MB L2, so
+no L2 flush is needed between timed steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# the upstream 0.9B model (Config/config.py:11-23; vocabulary rounded up as BASELINE.json configs[2] gives it)
+MODEL = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=30, num_heads=12,
+             num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
+             tie_word_embeddings=True, num_mtp_heads=2)
+CONTEXT = 4096
+PAGE = 16
+PREFILL_TOKENS = 2048
+# upstream's published iteration time at batch 8 without speculation: 31.7 ms on an RTX A6000
+# (its README, "iteration time p50, batch 8") -> 8 / 0.0317 tokens a second
+BASELINE_TOK_S = 8 / 0.0317
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p.get("bf16_tflops", 1590.0)), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_bytes_and_flops(cfg, n_layers, batch, ctx, elem=2):
+    d, H, KVH, hd, F, V = (cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"],
+                           cfg["ffn_hidden"], cfg["vocab_size"])
+    per_layer = d * (H + 2 * KVH) * hd + H * hd * d + 2 * d * F + F * d
+    weights = n_layers * (per_layer + 2 * d) + d + V * d            # blocks, norms, final norm, output matrix
+    kv_per_token = n_layers * 2 * KVH * hd
+    decode_bytes = (weights + batch * ctx * kv_per_token) * elem
+    t = PREFILL_TOKENS
+    prefill_flops = 2 * t * n_layers * per_layer + n_layers * 4 * t * t * H * hd / 2 + 2 * d * V
+    return decode_bytes, prefill_flops
+
+
+def fill_cache(runner, slots, length):
+    """Synthetic cache: every slot holds ``length`` tokens of random keys and values."""
+    import torch
+    for s in slots:
+        runner.cache.extend(s, length)
+    runner.cache.sync_tables()
+    g = torch.Generator(device=runner.device).manual_seed(1)
+    for grp in runner.cache.groups:
+        grp.pages.normal_(0.0, 0.5, generator=g)
+
+
+def decode_run(runner, batch, start_len, steps, warmup, sampler_cls, count_ops):
+    """Device time of ``steps`` decode steps at ``batch`` requests; returns (ms per step, launches per step)."""
+    import torch
+    from tiny_inference_server_b200.engine import StepEntry
+    from tiny_inference_server_b200.sampling import SamplingParams
+
+    slots = [runner.add_request() for _ in range(batch)]
+    fill_cache(runner, slots, start_len)
+    sampler = sampler_cls(runner.vocab_size, runner.engine.max_batch, runner.device)
+    params = [SamplingParams(temperature=0.0)] * batch
+    gen = torch.Generator().manual_seed(2)
+    feed = torch.randint(0, runner.vocab_size, (warmup + steps, batch), generator=gen).tolist()
+
+    def one(i):
+        out = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+        return sampler.sample(out.main, params, slots, [0] * batch, [i] * batch)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    l0 = count_ops()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    launches = (count_ops() - l0) / steps
+    runner.check_fault()
+    for s in slots:
+        runner.release(s)
+    return ms, launches
+
+
+def e2e_run(engine, batch, start_len, steps, warmup):
+    """The same through the Python entry point: host token ids in, host token ids out."""
+    import torch
+    from tiny_inference_server_b200.api import SamplingParams
+
+    gen = torch.Generator().manual_seed(3)
+    # prompts of a few tokens; the cache behind them is synthetic so that the context is ~4096
+    reqs = [engine.submit(torch.randint(0, engine.runner.vocab_size, (4,), generator=gen).tolist(),
+                          SamplingParams(max_new_tokens=warmup + steps + 8, temperature=0.0, ignore_eos=True))
+            for _ in range(batch)]
+    engine.step()                                        # prefill of the short prompts
+    for r in reqs:                                       # lengthen every request's context
+        extra = start_len - engine.runner.cache.length[r.slot]
+        engine.runner.cache.extend(r.slot, extra)
+        r.ids = [0] * extra + r.ids
+        r.prompt_len += extra
+        r.fed += extra
+    engine.runner.cache.sync_tables()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    return batch * steps / dt, dt / steps * 1e3
+
+
+def prefill_run(runner, tokens, reps=3):
+    import torch
+    from tiny_inference_server_b200.engine import StepEntry
+    gen = torch.Generator().manual_seed(4)
+    best = None
+    for _ in range(reps + 1):
+        ids = torch.randint(0, runner.vocab_size, (tokens,), generator=gen).tolist()
+        s = runner.add_request()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        runner.step([StepEntry(s, ids, [tokens - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        runner.release(s)
+        best = ms if best is None else min(best, ms)     # the first pass warms up
+    return best
+
+
+def reference_arm():
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = ("upstream is a folder of scripts without setup.py or pyproject.toml (pip cannot install it), it needs a "
+           "checkpoint and tokenizer files that are not present offline, and its kernels are Triton")
+    if os.path.isdir(ref) and os.listdir(ref):
+        why = "installed files found, but " + why
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=MODEL["num_layers"], help="fewer layers than the model (named in config)")
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from tiny_inference_server_b200.api import Engine
+    from tiny_inference_server_b200.config import EngineConfig
+    from tiny_inference_server_b200.engine import ModelRunner
+    from tiny_inference_server_b200.kernels import ops
+    from tiny_inference_server_b200.registry import config_from_dict
+    from tiny_inference_server_b200.sampling import Sampler
+    from tiny_inference_server_b200.weights import write_random_model
+
+    cfg_dict = dict(MODEL, num_layers=args.layers)
+    cfg = config_from_dict(cfg_dict)
+    pk = peaks()
+    tmp = tempfile.TemporaryDirectory()
+    folder = write_random_model(tmp.name, cfg, seed=0)
+    max_batch = max(64, args.batch)
+    pages_per_req = CONTEXT // PAGE
+    eng_cfg = EngineConfig(dtype="bfloat16", page_size=PAGE, num_pages=max_batch * pages_per_req + 8,
+                           max_batch=max_batch, max_tokens_per_step=PREFILL_TOKENS, mtp=False)
+    runner = ModelRunner.from_folder(folder, eng_cfg)
+    count_ops = lambda: ops.launches  # noqa: E731
+    start_len = CONTEXT - (args.steps + args.warmup) - 2
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = decode_run(runner, args.batch, start_len, args.steps, args.warmup, Sampler, count_ops)
+    clock_info = clocks.stop()
+    value = args.batch / (ms * 1e-3)
+
+    decode_bytes, prefill_flops = model_bytes_and_flops(cfg_dict, args.layers, args.batch, CONTEXT)
+    achieved = decode_bytes / (ms * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8, context 4096 (0.9B GQA+MTP model, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "gqa_mtp_0.9B", "layers": args.layers, "layers_of_model": MODEL["num_layers"],
+                   "hidden": cfg.hidden_size, "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
+                   "head_dim": cfg.head_dim, "ffn": cfg.ffn_hidden, "vocab": cfg.vocab_size,
+                   "mtp_heads": cfg.num_mtp_heads, "mtp_heads_run": 0, "tied": True, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "single_gpu",
+                   "l2": "inputs larger than L2", "peaks": pk["source"]},
+        "gpu_launches": int(round(launches * args.steps)),
+        "clocks": clock_info,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+
+    # the same through the Python entry point
+    engine = Engine(runner)
+    e2e_tok_s, e2e_ms = e2e_run(engine, args.batch, start_len, args.steps, args.warmup)
+    h2d = args.batch * 4 * 4 + args.batch * (3 * 4 + 2 * 4 + 2 * 8)       # step metadata + sampling parameters
+    d2h = args.batch * 4
+    out["e2e"] = {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    for r in list(engine.scheduler.active):
+        engine.runner.release(r.slot)
+    engine.scheduler.active = []
+
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            pms, _ = decode_run(runner, b, start_len, max(8, args.steps // 2), args.warmup, Sampler, count_ops)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+        out["points"] = points
+        pf_ms = prefill_run(runner, PREFILL_TOKENS)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(pf_ms, 3),
+                          "frac": round(prefill_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(json.dumps(out))
+    tmp.cleanup()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

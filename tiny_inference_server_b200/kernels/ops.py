@@ -18,6 +18,8 @@ from . import build as _build
 
 _lib = None
 ABI_VERSION = 1
+#: launches of this library's kernels so far (library matrix products are not counted)
+launches = 0
 
 
 class KernelError(RuntimeError):
@@ -50,8 +52,10 @@ def is_loaded() -> bool:
 
 
 def _check(status: int, lib) -> None:
+    global launches
     if status != 0:
         raise KernelError(lib.tis_last_error().decode())
+    launches += 1
 
 
 def _dt(t: torch.Tensor) -> int:
