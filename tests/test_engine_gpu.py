@@ -202,7 +202,8 @@ def test_attention_part_in_two_portions(dtype, window):
         start = cache.extend(slot, b - a)
         cache.sync_tables()
         ctx, _, _ = build_step([StepEntry(slot, [0] * (b - a))], [start], [0], [g.table_dev for g in cache.groups],
-                               [page], fault, torch.device("cuda:0"), 10)
+                               [page], fault, torch.device("cuda:0"), 10,
+                               group_sizes=att.tile_group_sizes())
         outs.append(att.forward(x[a:b].cuda(), ctx, binding).cpu())
     got = torch.cat(outs).double()
     xd = x.double()

@@ -324,3 +324,42 @@ def test_float32_products_are_not_tf32():
     w = torch.full((256, 8), 1.0).cuda()
     got = ops.gemm(a, w).cpu()
     assert abs(float(got[0, 0]) - 256 * (1.0 + 2.0 ** -12)) < 1e-4
+
+
+@pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (4, 2, 16, 16, None), (6, 2, 48, 4, 50),
+                                                  (8, 1, 64, 8, None), (5, 5, 32, 8, None), (32, 1, 80, 32, None),
+                                                  (20, 1, 96, 16, 300), (2, 2, 256, 16, None)])
+def test_paged_attention_tensor_core_long_context_and_portions(H, KVH, hd, page, window):
+    """The bfloat16 kernels with key splits: decode rows over thousands of keys, portions of
+    17 and 100 rows deep inside a context, every group size up to 32 (more than 16 query
+    heads per kv head go through the row tiles)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    dtype = torch.bfloat16
+    lens = [3000, 700, 64, 1]
+    plane, table = _fill_cache(dtype, lens, KVH, hd, page, g)
+    rows = [(0, 2999), (1, 699), (2, 63), (3, 0)]
+    rows += [(0, p) for p in range(1500, 1517)]            # a portion of 17 rows
+    rows += [(1, p) for p in range(520, 620)]              # a portion of 100 rows
+    rows += [(-1, 0), (2, 0), (2, 1)]
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    q = _rand((n, (H + 2 * KVH) * hd), dtype, g)
+    fault = torch.zeros(4, dtype=torch.int32)
+    want = ref.paged_attention(q, torch.empty(n, H * hd, dtype=dtype), plane, table, positions, row_slot, H, KVH, hd,
+                               page, window, fault)
+    fault_dev = fault.cuda()
+    got = ops.paged_attention(q.cuda(), torch.full((n, H * hd), 7.0, dtype=dtype, device="cuda"), plane.cuda(),
+                              table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault_dev)
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert int(fault_dev[0]) == 0
+
+
+def test_attention_splits_plan():
+    from tiny_inference_server_b200.kernels.ops import plan_splits
+    for tiles, kvh, max_kv, keys_mode in [(8, 3, 4096, True), (64, 3, 4096, True), (1, 1, 1, True), (1, 3, 100, True),
+                                          (128, 3, 2048, False), (4, 3, 4096, False), (500, 8, 5000, True)]:
+        per, splits = plan_splits(tiles, kvh, max_kv, keys_mode)
+        assert per % 64 == 0 and per >= 64 and splits >= 1
+        assert per * splits >= max_kv and per * (splits - 1) < max_kv

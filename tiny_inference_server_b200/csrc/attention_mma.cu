@@ -1,0 +1,456 @@
+// Causal attention of step rows over the paged bfloat16 cache on the tensor cores
+// (mma.sync m16n8k16, float32 accumulation), for decode rows and for portions of
+// prompts, with the keys split over several CTAs when that gives more parallelism.
+//
+// This file is compiled once per head size: -DTIS_HD=<multiple of 16, 16..256>.
+//
+// Work is cut into *tiles*: up to R consecutive rows of one request.  A CTA takes one
+// (tile, kv head, key split).  All G query heads that share the kv head are packed with
+// the rows into the M dimension of the products (packed row m = row * G + head), so a
+// key or value is read from HBM once per kv head, not once per query head.
+//
+//   MODE_ROWS  64 packed rows a CTA; warp w owns packed rows 16w..16w+15 and walks all keys.
+//   MODE_KEYS  16 packed rows a CTA (a decode row with up to 16 query heads per kv head);
+//              warp w owns keys 16w..16w+15 of every 64-key tile; the four warps' partial
+//              results are merged through shared memory at the end.
+//
+// Keys and values of 64 positions are staged in shared memory by cp.async, two stages,
+// found through the block table position by position, so any page size works.  Rows are
+// padded by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size.
+// Scores, running maximum, sum and the output accumulate in float32; probabilities are
+// rounded to bfloat16 for the P.V product (as paged_attention_kernels.py:108 upstream).
+// With more than one key split a CTA writes a normalised partial output and its log2-sum
+// to scratch memory and `attn_merge_kernel` combines them.
+#include "common.cuh"
+
+#ifndef TIS_HD
+#error "compile with -DTIS_HD=<head size>"
+#endif
+
+constexpr int HD = TIS_HD;
+constexpr int KT = 64;               // keys per staged tile
+constexpr int RS = HD + 8;           // shared-memory row stride (elements)
+constexpr int NTHREADS = 128;
+constexpr int KSTEPS = HD / 16;      // k16 steps of Q.K^T
+constexpr int DTILES = HD / 8;       // n8 tiles of the output
+constexpr int CHUNKS = HD / 8;       // 16-byte chunks per row
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
+
+enum { MODE_ROWS = 0, MODE_KEYS = 1 };
+
+struct AttnParams {
+    const bf16* q; int q_stride;
+    bf16* out; int out_stride;
+    const bf16* plane; const int* block_table; int bt_stride; int num_pages;
+    const int* positions; const int* row_slot;
+    const int* tile_row0; const int* tile_rows;
+    int H, KVH, G, page_size, window;
+    float scale_log2;
+    int keys_per_split, num_splits;
+    float* part_o; float* part_lse;
+    int* fault;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Stage keys and values of positions kt..kt+63 of the slot; positions outside [lo, hi) are
+// zero-filled.  Two threads per position, alternating 16-byte chunks.
+__device__ __forceinline__ void load_tile(bf16* stage, const AttnParams& p, const int* bt, int kvh, int kt, int lo,
+                                          int hi, int tid) {
+    const int key = tid >> 1, half = tid & 1;
+    const int j = kt + key;
+    const bf16* src_k = p.plane;
+    int bytes = 0;
+    if (j >= lo && j < hi) {
+        const int page = bt[j / p.page_size];
+        if (page >= 0 && page < p.num_pages) {
+            src_k = p.plane + ((size_t)page * 2 * p.KVH + kvh) * (size_t)p.page_size * HD + (size_t)(j % p.page_size) * HD;
+            bytes = 16;
+        } else {
+            atomicExch(p.fault, 3);
+        }
+    }
+    const bf16* src_v = src_k + (bytes ? (size_t)p.KVH * p.page_size * HD : 0);
+    bf16* dk = stage + key * RS;
+    bf16* dv = stage + (KT + key) * RS;
+#pragma unroll
+    for (int c = half; c < CHUNKS; c += 2) {
+        cp_async16(dk + c * 8, src_k + (bytes ? c * 8 : 0), bytes);
+        cp_async16(dv + c * 8, src_v + (bytes ? c * 8 : 0), bytes);
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(NTHREADS)
+attn_mma_kernel(const AttnParams p) {
+    constexpr int NT = MODE == MODE_ROWS ? 8 : 2;        // n8 key tiles a warp scores per staged tile
+    constexpr int KB = MODE == MODE_ROWS ? 4 : 1;        // k16 key blocks a warp multiplies with V
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw);    // 2 stages x (K[64][RS], V[64][RS])
+    __shared__ int sh_first;
+
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g_lane = lane >> 2, t_lane = lane & 3;
+    const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+    const int G = p.G;
+
+    // first valid row of the tile (rows of a stage that lags the trunk start with padding)
+    if (warp == 0) {
+        const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
+        const bool v1 = lane + 32 < rows && p.row_slot[row0 + lane + 32] >= 0;
+        const unsigned b0 = __ballot_sync(0xffffffffu, v0), b1 = __ballot_sync(0xffffffffu, v1);
+        if (lane == 0) sh_first = b0 ? __ffs(b0) - 1 : (b1 ? 32 + __ffs(b1) - 1 : -1);
+    }
+    __syncthreads();
+    const int first = sh_first;
+
+    // the two packed rows of this thread
+    const int mbase = (MODE == MODE_ROWS ? warp * 16 : 0) + g_lane;
+    int r_idx[2], head[2], hi_row[2], lo_row[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = mbase + 8 * i;
+        const int r = m / G, g = m - r * G;
+        valid[i] = r < rows && first >= 0 && r >= first;
+        r_idx[i] = row0 + (valid[i] ? r : 0);
+        head[i] = kvh * G + g;
+        const int pos = valid[i] ? p.positions[r_idx[i]] : 0;
+        hi_row[i] = valid[i] ? pos + 1 : 0;
+        lo_row[i] = (valid[i] && p.window > 0 && hi_row[i] > p.window) ? hi_row[i] - p.window : 0;
+    }
+
+    // key range of the tile and of this split
+    int range_lo = 0, range_hi = 0, slot = -1;
+    if (first >= 0) {
+        slot = p.row_slot[row0 + rows - 1];
+        const int pos_first = p.positions[row0 + first], pos_last = p.positions[row0 + rows - 1];
+        range_hi = pos_last + 1;
+        range_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
+        range_lo = max(range_lo, split * p.keys_per_split);
+        range_hi = min(range_hi, (split + 1) * p.keys_per_split);
+    }
+    const bool empty = first < 0 || range_lo >= range_hi;
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (!empty) {
+        // query fragments straight from global memory: a0 (row g, k 2t..), a1 (row g+8), a2 (row g, k 2t+8..), a3
+        unsigned qa[KSTEPS][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const bf16* qrow = p.q + (size_t)r_idx[i] * p.q_stride + (size_t)head[i] * HD;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                unsigned w0 = 0u, w1 = 0u;
+                if (valid[i]) {
+                    w0 = *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 2 * t_lane);
+                    w1 = *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 8 + 2 * t_lane);
+                }
+                qa[kk][i] = w0;
+                qa[kk][2 + i] = w1;
+            }
+        }
+        const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+        const int kt0 = (range_lo / KT) * KT;
+        const int ntiles = (range_hi - kt0 + KT - 1) / KT;
+        constexpr int STAGE_ELEMS = 2 * KT * RS;
+
+        load_tile(stages, p, bt, kvh, kt0, range_lo, range_hi, tid);
+        cp_async_commit();
+        for (int it = 0; it < ntiles; ++it) {
+            const int kt = kt0 + it * KT;
+            bf16* cur = stages + (it & 1) * STAGE_ELEMS;
+            if (it + 1 < ntiles) load_tile(stages + ((it + 1) & 1) * STAGE_ELEMS, p, bt, kvh, kt + KT, range_lo, range_hi, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+
+            const bf16* ks = cur;
+            const bf16* vs = cur + KT * RS;
+            const int kofs = MODE == MODE_ROWS ? 0 : warp * 16;      // first key of this warp inside the tile
+
+            // ---- S = Q K^T
+            float s[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+            for (int j = 0; j < NT; j += 2) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    unsigned b[4];
+                    const int key = kofs + j * 8 + ((lane >> 4) << 3) + (lane & 7);
+                    const int kcol = kk * 16 + (((lane >> 3) & 1) << 3);
+                    ldmatrix_x4(b, ks + key * RS + kcol);
+                    mma_bf16(s[j], qa[kk], b[0], b[1]);
+                    mma_bf16(s[j + 1], qa[kk], b[2], b[3]);
+                }
+            }
+            // ---- scale, mask, online softmax
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int kidx = kt + kofs + j * 8 + 2 * t_lane + (e & 1);
+                    const bool ok = kidx >= lo_row[i] && kidx < hi_row[i] && kidx >= range_lo && kidx < range_hi;
+                    const float v = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                    s[j][e] = v;
+                    mx[i] = fmaxf(mx[i], v);
+                }
+            }
+            float alpha[2], m_safe[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;
+                alpha[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f(m_run[i] - m_safe[i]);
+                m_run[i] = m_new;
+            }
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const float pv = exp2f(s[j][e] - m_safe[i]);      // exp2(-inf) = 0 for masked keys
+                    s[j][e] = pv;
+                    psum[i] += pv;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+                o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+            }
+            // ---- O += P V
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                unsigned pa[4];
+                pa[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
+                pa[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
+                pa[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+                pa[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+                const int key = kofs + kb * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int d = 0; d < DTILES; d += 2) {
+                    unsigned b[4];
+                    ldmatrix_x4_trans(b, vs + key * RS + d * 8 + ((lane >> 4) << 3));
+                    mma_bf16(o[d], pa, b[0], b[1]);
+                    mma_bf16(o[d + 1], pa, b[2], b[3]);
+                }
+            }
+            __syncthreads();        // the stage is refilled two iterations later
+        }
+        cp_async_wait<0>();
+    }
+
+    // ---- row sums over the four lanes that share a row
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+
+    if (MODE == MODE_KEYS) {
+        // merge the four warps (each saw a quarter of the keys) through shared memory
+        __syncthreads();
+        float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HD]
+        float* mm = mo + 4 * 16 * HD;                            // [4][16]
+        float* ml = mm + 4 * 16;                                 // [4][16]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int m = g_lane + 8 * i;
+            if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) {
+                mo[(warp * 16 + m) * HD + d * 8 + 2 * t_lane] = o[d][2 * i];
+                mo[(warp * 16 + m) * HD + d * 8 + 2 * t_lane + 1] = o[d][2 * i + 1];
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < 16 * HD; idx += NTHREADS) {
+            const int m = idx / HD, d = idx - m * HD;
+            const int r = m / G, g = m - r * G;
+            if (r >= rows) continue;
+            const int row = row0 + r, hq = kvh * G + g;
+            float mt = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mt = fmaxf(mt, mm[w * 16 + m]);
+            float lt = 0.f, acc = 0.f;
+            if (mt != -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float mw = mm[w * 16 + m];
+                    const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mt);
+                    lt += ml[w * 16 + m] * f;
+                    acc += mo[(w * 16 + m) * HD + d] * f;
+                }
+            }
+            const float val = lt > 0.f ? acc / lt : 0.f;
+            if (p.num_splits == 1) {
+                p.out[(size_t)row * p.out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(val);
+            } else {
+                const size_t pr = ((size_t)row * p.H + hq) * p.num_splits + split;
+                p.part_o[pr * HD + d] = val;
+                if (d == 0) p.part_lse[pr] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int m = mbase + 8 * i;
+            const int r = m / G, g = m - r * G;
+            if (r >= rows) continue;
+            const int row = row0 + r, hq = kvh * G + g;
+            const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+            if (p.num_splits == 1) {
+                bf16* dst = p.out + (size_t)row * p.out_stride + (size_t)hq * HD;
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d)
+                    *reinterpret_cast<unsigned*>(dst + d * 8 + 2 * t_lane) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+            } else {
+                const size_t pr = ((size_t)row * p.H + hq) * p.num_splits + split;
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d) {
+                    p.part_o[pr * HD + d * 8 + 2 * t_lane] = o[d][2 * i] * inv;
+                    p.part_o[pr * HD + d * 8 + 2 * t_lane + 1] = o[d][2 * i + 1] * inv;
+                }
+                if (t_lane == 0) p.part_lse[pr] = l_run[i] > 0.f ? m_run[i] + log2f(l_run[i]) : -INFINITY;
+            }
+        }
+    }
+}
+
+// out[row, head] = sum_s w_s * part_o[row, head, s],  w_s = 2^(lse_s - max) / sum, for the rows of one tile
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                  bf16* __restrict__ out, int out_stride, const int* __restrict__ tile_row0,
+                                  const int* __restrict__ tile_rows, int H, int num_splits) {
+    const int tile = blockIdx.y, hq = blockIdx.x;
+    const int row0 = tile_row0[tile], rows = tile_rows[tile];
+    for (int r = 0; r < rows; ++r) {
+        const int row = row0 + r;
+        const size_t pr = ((size_t)row * H + hq) * num_splits;
+        float mt = -INFINITY;
+        for (int s = 0; s < num_splits; ++s) mt = fmaxf(mt, part_lse[pr + s]);
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+            float acc = 0.f, wsum = 0.f;
+            if (mt != -INFINITY) {
+                for (int s = 0; s < num_splits; ++s) {
+                    const float l = part_lse[pr + s];
+                    if (l == -INFINITY) continue;
+                    const float w = exp2f(l - mt);
+                    wsum += w;
+                    acc += w * part_o[(pr + s) * HD + d];
+                }
+            }
+            out[(size_t)row * out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+        }
+    }
+}
+
+static size_t smem_bytes(int mode) {
+    size_t stage = (size_t)2 * 2 * KT * RS * sizeof(bf16);
+    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float) : 0;
+    return stage > merge ? stage : merge;
+}
+
+TIS_API int tis_attn_head_dim() { return HD; }
+
+// Scratch the caller must provide when num_splits > 1: floats for part_o and part_lse.
+TIS_API size_t tis_attn_scratch_floats(int n_rows, int H, int num_splits) {
+    return num_splits > 1 ? (size_t)n_rows * H * num_splits * (HD + 1) : 0;
+}
+
+// mode: 0 rows (tiles of up to 64/G rows), 1 keys (tiles of up to 16/G rows).
+TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
+                         const int* block_table, int bt_stride, int num_pages, const int* positions,
+                         const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles, int n_rows,
+                         int H, int KVH, int page_size, int window, float scale, int keys_per_split, int num_splits,
+                         float* scratch, int* fault, cudaStream_t stream) {
+    if (num_tiles <= 0) return TIS_OK;
+    const int G = KVH > 0 ? H / KVH : 0;
+    const int mpack = mode == MODE_ROWS ? 64 : 16;
+    if (KVH <= 0 || H % KVH) {
+        tis_set_error("attention: %d query heads are not a multiple of %d kv heads", H, KVH);
+        return TIS_BAD_SIZE;
+    }
+    if (G > mpack) {
+        tis_set_error("attention: %d query heads per kv head exceed the %d packed rows of this mode", G, mpack);
+        return TIS_BAD_SIZE;
+    }
+    if (keys_per_split <= 0 || keys_per_split % KT || num_splits <= 0) {
+        tis_set_error("attention: keys per split %d must be a positive multiple of %d", keys_per_split, KT);
+        return TIS_BAD_SIZE;
+    }
+    if (KVH > 65535 || num_splits > 65535) {
+        tis_set_error("attention: %d kv heads or %d splits exceed the grid", KVH, num_splits);
+        return TIS_BAD_SIZE;
+    }
+    if (num_splits > 1 && scratch == nullptr) {
+        tis_set_error("attention: %d key splits need scratch memory", num_splits);
+        return TIS_BAD_SIZE;
+    }
+    AttnParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.plane = (const bf16*)plane; p.block_table = block_table; p.bt_stride = bt_stride; p.num_pages = num_pages;
+    p.positions = positions; p.row_slot = row_slot; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
+    p.H = H; p.KVH = KVH; p.G = G; p.page_size = page_size; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.keys_per_split = keys_per_split; p.num_splits = num_splits;
+    p.part_o = scratch;
+    p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
+    p.fault = fault;
+    const size_t smem = smem_bytes(mode);
+    dim3 grid(num_tiles, KVH, num_splits);
+    if (mode == MODE_ROWS) {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_mma_kernel<MODE_ROWS><<<grid, NTHREADS, smem, stream>>>(p);
+    } else {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_mma_kernel<MODE_KEYS><<<grid, NTHREADS, smem, stream>>>(p);
+    }
+    int st = tis_check_launch("attn_mma");
+    if (st != TIS_OK) return st;
+    if (num_splits > 1) {
+        dim3 mg(H, num_tiles);
+        attn_merge_kernel<<<mg, HD < 128 ? (HD < 32 ? 32 : HD) : 128, 0, stream>>>(p.part_o, p.part_lse, (bf16*)out, out_stride,
+                                                                                  tile_row0, tile_rows, H, num_splits);
+        st = tis_check_launch("attn_merge");
+    }
+    return st;
+}

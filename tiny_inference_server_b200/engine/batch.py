@@ -33,6 +33,33 @@ class Segment:
     pos0: int
 
 
+class TileSet:
+    """Attention work of one step for one group size G (query heads per kv head): tiles of
+    consecutive rows of one request.  ``keys``: tiles of at most 16 // G rows (decode rows,
+    tiny portions), whose keys are split over warps and CTAs; ``rows``: tiles of at most
+    64 // G rows (portions of prompts).  Each is (first rows, row counts, number of tiles);
+    the first two are int32 device tensors."""
+
+    def __init__(self, keys, rows):
+        self.keys = keys
+        self.rows = rows
+
+
+def plan_tiles(segments: Sequence[Tuple[int, int]], group_size: int):
+    """Cut (row0, rows) segments into tiles.  Returns (keys tiles, rows tiles) as lists of
+    (row0, rows)."""
+    r_keys = 16 // group_size if group_size <= 16 else 0
+    r_rows = max(1, 64 // group_size)
+    keys, rows = [], []
+    for row0, n in segments:
+        if r_keys and n <= r_keys:
+            keys.append((row0, n))
+        else:
+            for a in range(0, n, r_rows):
+                rows.append((row0 + a, min(r_rows, n - a)))
+    return keys, rows
+
+
 class StepContext:
     """Everything a part may know about the step.  ``positions`` and ``row_slot`` are the
     ones of the *stage* the part runs in: a stage that lags the trunk by ``lag`` positions
@@ -41,7 +68,7 @@ class StepContext:
     def __init__(self, n: int, tokens, positions, row_slot, row_last, segments: List[Segment],
                  block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
                  max_position: int, trunk_slot=None, lag: int = 0, stages: Optional[dict] = None,
-                 decode_only: bool = False):
+                 decode_only: bool = False, tiles: Optional[Dict[int, TileSet]] = None):
         self.n = n
         self.tokens = tokens
         self.positions = positions
@@ -56,6 +83,8 @@ class StepContext:
         self.lag = lag
         self._stages = stages if stages is not None else {}
         self.decode_only = decode_only      # every request has exactly one row
+        self.tiles = tiles if tiles is not None else {}
+        self.scratch: Dict = {}             # buffers that kernels of this step may share
 
     def stage(self, lag: int) -> "StepContext":
         """The same rows seen by a stage that runs ``lag`` positions behind the trunk."""
@@ -63,13 +92,22 @@ class StepContext:
             return self
         return self._stages[lag]
 
+    def attn_tiles(self, group_size: int) -> TileSet:
+        """Tiles for mixers with ``group_size`` query heads per kv head.  Planned with the step
+        for the group sizes the model declares; for any other it is derived here from the
+        device arrays (which synchronises)."""
+        if group_size not in self.tiles:
+            self.tiles[group_size] = infer_tiles(self.stage(0).positions, self.stage(0).row_slot, group_size)
+        return self.tiles[group_size]
+
 
 def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int],
                block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
-               device: torch.device, vocab_size: int, pad_to: Optional[int] = None
-               ) -> Tuple[StepContext, torch.Tensor, int]:
+               device: torch.device, vocab_size: int, pad_to: Optional[int] = None,
+               group_sizes: Sequence[int] = ()) -> Tuple[StepContext, torch.Tensor, int]:
     """Lay the entries out as rows.  ``starts[i]`` is the position of entry i's first token.
-    Returns the context, the device indices of the wanted rows, and their count."""
+    Returns the context, the device indices of the wanted rows, and their count.  All
+    per-step arrays go to the device in one copy."""
     tokens: List[int] = []
     positions: List[int] = []
     slots: List[int] = []
@@ -95,28 +133,78 @@ def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequen
         segments.append(Segment(e.slot, row0, k, start))
     n_real = len(tokens)
     n = n_real
+    seg_rows = [(s.row0, s.rows) for s in segments]
     if pad_to is not None and pad_to > n:
         pad = pad_to - n
         tokens += [0] * pad
         positions += [0] * pad
         slots += [-1] * pad
         last += list(range(n, n + pad))
+        seg_rows += [(r, 1) for r in range(n, n + pad)]
         n = pad_to
     lags = [l for l in sorted(set(lags)) if l > 0]
-    rows = [tokens, positions, slots, last]
+    flat: List[int] = []
+    offsets: Dict[str, Tuple[int, int]] = {}
+
+    def put(name, values):
+        offsets[name] = (len(flat), len(values))
+        flat.extend(values)
+
+    put("tokens", tokens)
+    put("positions", positions)
+    put("slots", slots)
+    put("last", last)
     for lag in lags:
-        rows.append([max(0, p - lag) for p in positions])
-        rows.append([s if p - lag >= 0 else -1 for s, p in zip(slots, positions)])
-    packed = torch.tensor(rows, dtype=torch.int32)
-    dev = packed.to(device, non_blocking=True)
-    want_dev = torch.tensor(want_rows, dtype=torch.int64).to(device, non_blocking=True)
+        put(f"pos{lag}", [max(0, p - lag) for p in positions])
+        put(f"slot{lag}", [s if p - lag >= 0 else -1 for s, p in zip(slots, positions)])
+    plans = {}
+    for g in sorted(set(group_sizes)):
+        keys, rows = plan_tiles(seg_rows, g)
+        plans[g] = (len(keys), len(rows))
+        put(f"k0_{g}", [t[0] for t in keys])
+        put(f"kn_{g}", [t[1] for t in keys])
+        put(f"r0_{g}", [t[0] for t in rows])
+        put(f"rn_{g}", [t[1] for t in rows])
+    put("want", want_rows)
+    dev = torch.tensor(flat, dtype=torch.int32).to(device, non_blocking=True)
+
+    def view(name):
+        a, k = offsets[name]
+        return dev[a:a + k]
+
+    want_dev = view("want").to(torch.int64)
     max_pos = max(positions[:n_real]) if n_real else 0
     decode_only = all(s.rows == 1 for s in segments)
+    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr))
+             for g, (nk, nr) in plans.items()}
     stages: Dict[int, StepContext] = {}
-    ctx = StepContext(n, dev[0], dev[1], dev[2], dev[3], segments, block_tables, page_sizes, fault, max_pos,
-                      stages=stages, decode_only=decode_only)
-    for i, lag in enumerate(lags):
-        stages[lag] = StepContext(n, dev[0], dev[4 + 2 * i], dev[5 + 2 * i], dev[3], segments, block_tables,
-                                  page_sizes, fault, max(0, max_pos - lag), trunk_slot=dev[2], lag=lag,
-                                  stages=stages, decode_only=decode_only)
+    ctx = StepContext(n, view("tokens"), view("positions"), view("slots"), view("last"), segments, block_tables,
+                      page_sizes, fault, max_pos, stages=stages, decode_only=decode_only, tiles=tiles)
+    for lag in lags:
+        st = StepContext(n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), segments,
+                         block_tables, page_sizes, fault, max(0, max_pos - lag), trunk_slot=view("slots"), lag=lag,
+                         stages=stages, decode_only=decode_only, tiles=tiles)
+        st.scratch = ctx.scratch
+        stages[lag] = st
     return ctx, want_dev, len(want_rows)
+
+
+def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int) -> TileSet:
+    """Tiles from the device arrays alone (synchronises; for calls outside a step, as in
+    kernel tests): consecutive rows with one slot and consecutive positions form a segment."""
+    pos = positions.tolist()
+    slot = row_slot.tolist()
+    segs: List[Tuple[int, int]] = []
+    for r in range(len(pos)):
+        if segs and slot[r] >= 0 and slot[r] == slot[r - 1] and pos[r] == pos[r - 1] + 1:
+            segs[-1] = (segs[-1][0], segs[-1][1] + 1)
+        else:
+            segs.append((r, 1))
+    keys, rows = plan_tiles(segs, group_size)
+    dev = positions.device
+
+    def t(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    return TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
+                   (t([k[0] for k in rows]), t([k[1] for k in rows]), len(rows)))

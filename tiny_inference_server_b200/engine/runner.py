@@ -53,6 +53,8 @@ class ModelRunner:
         self.model.bind(self.cache)
         self.fault = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.lags = self.model.lags()
+        self.group_sizes = sorted({g for p in self.model.walk_parts() if hasattr(p, "tile_group_sizes")
+                                   for g in p.tile_group_sizes()})
         self.aux = bool(self.engine.mtp)
         self.steps_run = 0
         self.rows_run = 0
@@ -99,7 +101,7 @@ class ModelRunner:
         ctx, want_rows, _ = build_step(entries, starts, self.lags,
                                        [g.table_dev for g in self.cache.groups],
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,
-                                       self.vocab_size, pad_to=pad_to)
+                                       self.vocab_size, pad_to=pad_to, group_sizes=self.group_sizes)
         out = self.model.forward(ctx, want_rows, aux=self.aux)
         self.steps_run += 1
         self.rows_run += ctx.n

@@ -40,8 +40,12 @@ def _nvcc() -> str:
                      "this engine have to be compiled and there is no other implementation to fall back to")
 
 
+#: sources compiled once per head size (-DTIS_HD=<hd>) into libraries of their own
+PER_HEAD_SIZE = ("attention_mma.cu",)
+
+
 def sources():
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu") and f not in PER_HEAD_SIZE)
 
 
 def _digest() -> str:
@@ -78,9 +82,9 @@ def _say(msg: str) -> None:
     print(f"[tiny_inference_server_b200] {msg}", file=sys.stderr, flush=True)
 
 
-def _compile_one(nvcc: str, src: str, obj: str) -> None:
+def _compile_one(nvcc: str, src: str, obj: str, defines=()) -> None:
     t0 = time.time()
-    cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *defines, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
     p = subprocess.run(cmd, capture_output=True, text=True)
     if p.returncode != 0:
         raise BuildError(f"nvcc failed on {src}:\n{p.stdout}\n{p.stderr}")
@@ -102,11 +106,42 @@ def build(verbose: bool = True) -> str:
         with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
             list(ex.map(lambda so: _compile_one(nvcc, *so), zip(srcs, objs)))
         tmp_so = os.path.join(work, "lib.so")
-        p = subprocess.run([nvcc, "-shared", "-o", tmp_so, *objs, "-lcudart"], capture_output=True, text=True)
+        p = subprocess.run([nvcc, "-shared", "-o", tmp_so, *objs], capture_output=True, text=True)
         if p.returncode != 0:
             raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
         os.replace(tmp_so, out)       # atomic: a concurrent builder ends with the same file
         _say("library ready")
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    return out
+
+
+def attention_library_path(head_dim: int) -> str:
+    return os.path.join(_build_root(), f"libtis_attn_hd{head_dim}_{_digest()}.so")
+
+
+def build_attention(head_dim: int) -> str:
+    """The tensor-core attention kernels for one head size (what a model needs is compiled
+    when the model first runs)."""
+    if head_dim % 16 or not (16 <= head_dim <= 256):
+        raise BuildError(f"head size {head_dim}: the attention kernels take multiples of 16 from 16 to 256")
+    out = attention_library_path(head_dim)
+    if os.path.isfile(out):
+        return out
+    nvcc = _nvcc()
+    root = os.path.dirname(out)
+    work = tempfile.mkdtemp(prefix="tis_obj_", dir=root)
+    try:
+        _say(f"compiling the attention kernels for head size {head_dim} (first call only)")
+        jobs = [("attention_mma.cu", os.path.join(work, "attention_mma.o"), (f"-DTIS_HD={head_dim}",)),
+                ("errors.cu", os.path.join(work, "errors.o"), ())]
+        with ThreadPoolExecutor(max_workers=2) as ex:
+            list(ex.map(lambda j: _compile_one(nvcc, *j), jobs))
+        tmp_so = os.path.join(work, "lib.so")
+        p = subprocess.run([nvcc, "-shared", "-o", tmp_so, *[j[1] for j in jobs]], capture_output=True, text=True)
+        if p.returncode != 0:
+            raise BuildError(f"link failed:\n{p.stdout}\n{p.stderr}")
+        os.replace(tmp_so, out)
     finally:
         shutil.rmtree(work, ignore_errors=True)
     return out

@@ -145,20 +145,86 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Te
         n, num_heads, kv_heads, head_dim, rot, int(interleaved), page_size, int(write), _p(fault), _stream()), lib)
 
 
+_attn_libs = {}
+
+
+def attention_library(head_dim: int):
+    """The tensor-core attention kernels for one head size, compiled when first needed."""
+    lib = _attn_libs.get(head_dim)
+    if lib is None:
+        library()
+        lib = ctypes.CDLL(_build.build_attention(head_dim))
+        lib.tis_last_error.restype = ctypes.c_char_p
+        lib.tis_attn_scratch_floats.restype = ctypes.c_size_t
+        if lib.tis_attn_head_dim() != head_dim:
+            raise KernelError(f"attention library built for head size {lib.tis_attn_head_dim()}, wanted {head_dim}")
+        _attn_libs[head_dim] = lib
+    return lib
+
+
+#: CTAs that the key splits of the attention kernels aim for (148 SMs, two to three CTAs each)
+ATTN_TARGET_CTAS = 148 * 3
+
+
+def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool):
+    """(keys per split, number of splits): split the keys of long contexts over CTAs while
+    tiles x kv heads alone would leave SMs idle.  Splits are multiples of 64 keys."""
+    base = max(1, num_tiles * kv_heads)
+    max_splits = max(1, (max_kv + 63) // 64)
+    want = 1 if base >= ATTN_TARGET_CTAS else (ATTN_TARGET_CTAS + base - 1) // base
+    if not mode_keys:
+        want = min(want, 8)
+    splits = max(1, min(want, max_splits))
+    per = ((max_kv + splits - 1) // splits + 63) // 64 * 64
+    per = max(64, per)
+    splits = max(1, (max_kv + per - 1) // per)
+    return per, splits
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor,
                     positions: torch.Tensor, row_slot: torch.Tensor, num_heads: int, kv_heads: int,
                     head_dim: int, page_size: int, window: Optional[int], fault: torch.Tensor,
                     step=None) -> torch.Tensor:
     """Causal attention of the step's rows over the cache.  ``q`` is (n, >= H*hd) with the
     queries first in each row (row stride free); ``out`` is (n, H*hd).  The row at position
-    p of slot s sees keys max(0, p-window+1)..p of ``plane`` through ``block_table[s]``."""
+    p of slot s sees keys max(0, p-window+1)..p of ``plane`` through ``block_table[s]``.
+
+    float32: CUDA-core kernel, everything in 32-bit.  bfloat16: tensor-core kernels over
+    tiles of rows (``step.attn_tiles``), keys of long contexts split over CTAs."""
     lib = library()
     n = q.shape[0]
     scale = 1.0 / math.sqrt(head_dim)
-    _check(lib.tis_paged_attention_simt(
-        _dt(q), _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table), block_table.stride(0),
-        plane.shape[0], _p(positions), _p(row_slot), n, num_heads, kv_heads, head_dim, page_size,
-        int(window or 0), _f(scale), _p(fault), _stream()), lib)
+    if q.dtype == torch.float32:
+        _check(lib.tis_paged_attention_simt(
+            _dt(q), _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table), block_table.stride(0),
+            plane.shape[0], _p(positions), _p(row_slot), n, num_heads, kv_heads, head_dim, page_size,
+            int(window or 0), _f(scale), _p(fault), _stream()), lib)
+        return out
+    if kv_heads <= 0 or num_heads % kv_heads:
+        raise KernelError(f"paged_attention: {num_heads} query heads are not a multiple of {kv_heads} kv heads")
+    g = num_heads // kv_heads
+    if g > 64:
+        raise KernelError(f"paged_attention: {g} query heads per kv head; the bfloat16 kernels take up to 64")
+    alib = attention_library(head_dim)
+    if step is not None:
+        tiles = step.attn_tiles(g)
+        max_kv = step.max_position + 1
+    else:
+        from ..engine.batch import infer_tiles
+        tiles = infer_tiles(positions, row_slot, g)
+        max_kv = int(positions.max().item()) + 1 if n else 1
+    for mode, (row0, rows, count) in ((1, tiles.keys), (0, tiles.rows)):
+        if count == 0:
+            continue
+        per, splits = plan_splits(count, kv_heads, max_kv, mode == 1)
+        scratch = None
+        if splits > 1:
+            need = alib.tis_attn_scratch_floats(n, num_heads, splits)
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        _check(alib.tis_attn_mma(mode, _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
+                                 block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
+                                 _p(rows), count, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
+                                 per, splits, _p(scratch), _p(fault), _stream()), alib)
     return out
 
 

@@ -52,6 +52,9 @@ class GqaAttention(Mixer):
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.kv_heads, self.head_dim, self.window, self.lag)
 
+    def tile_group_sizes(self):
+        return (self.num_heads // self.kv_heads,)
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         hq, hkv = self.num_heads * self.head_dim, self.kv_heads * self.head_dim
         return {

@@ -124,6 +124,10 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def tile_group_sizes(self) -> Tuple[int, ...]:
+        """Query heads per kv head for which the step should plan attention tiles."""
+        return ()
+
     def forward(self, x, step, binding: LayerBinding):
         raise NotImplementedError
 
