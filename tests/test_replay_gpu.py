@@ -100,6 +100,31 @@ def test_replay_matches_plain(name, mode, dtype, tmp_path, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_from_cuda_graphs_equal_plain_launches(dtype, tmp_path, tmp_path_factory):
+    """Steps of single tokens are replayed from captured graphs; the same trace without
+    graphs gives the same logits to rounding, and both equal the plain implementation."""
+    cfg, page, folder, seqs, plain = _setup("B", tmp_path_factory)
+    steps = trace_tools.trace_mixed(seqs, max_live=4, decode_from=0.3, skip_every=0)
+    max_tokens = trace_tools.max_live_tokens(steps, round_to=64)
+    got = {}
+    for graphs in (True, False):
+        runner = make_runner(folder, dtype, max_tokens, page_size=page, mtp=True, cuda_graphs=graphs)
+        out_dir = str(tmp_path / f"out{int(graphs)}")
+        TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+        if graphs:
+            assert runner.graphs is not None and runner.graphs.replays > 10
+        else:
+            assert runner.graphs is None
+        assert runner.cache.drained()
+        _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+        got[graphs] = trace_tools.gather(steps, out_dir, cfg["vocab_size"])
+    for rid, toks in seqs.items():
+        for p in range(len(toks)):
+            err = float(np.abs(got[True][rid][p] - got[False][rid][p]).max())
+            assert err < (2e-5 if dtype == "float32" else 3e-2), f"{rid} position {p}: {err}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(dtype, tmp_path, tmp_path_factory):
     """bin/trace_run over pipes: one step at a time, the next only after ``done <step>``."""
     cfg, page, folder, seqs, plain = _setup("B", tmp_path_factory)

@@ -437,11 +437,17 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.fault = fault;
     const size_t smem = smem_bytes(mode);
     dim3 grid(num_tiles, KVH, num_splits);
+    static bool configured = false;          // once per process (and before any stream capture)
+    if (!configured) {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes(MODE_ROWS));
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes(MODE_KEYS));
+        configured = true;
+    }
     if (mode == MODE_ROWS) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_mma_kernel<MODE_ROWS><<<grid, NTHREADS, smem, stream>>>(p);
     } else {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_mma_kernel<MODE_KEYS><<<grid, NTHREADS, smem, stream>>>(p);
     }
     int st = tis_check_launch("attn_mma");

@@ -101,13 +101,27 @@ class StepContext:
         return self.tiles[group_size]
 
 
-def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int],
-               block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
-               device: torch.device, vocab_size: int, pad_to: Optional[int] = None,
-               group_sizes: Sequence[int] = ()) -> Tuple[StepContext, torch.Tensor, int]:
-    """Lay the entries out as rows.  ``starts[i]`` is the position of entry i's first token.
-    Returns the context, the device indices of the wanted rows, and their count.  All
-    per-step arrays go to the device in one copy."""
+@dataclass
+class StepLayout:
+    """The per-step arrays as one flat list of int32 words, and where each array lies."""
+    flat: List[int]
+    offsets: Dict[str, Tuple[int, int]]
+    n: int
+    segments: List[Segment]
+    lags: List[int]
+    tile_counts: Dict[int, Tuple[int, int]]
+    n_want: int
+    max_position: int
+    decode_only: bool
+
+
+def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
+                pad_to: Optional[int] = None, group_sizes: Sequence[int] = (), want_all: bool = False,
+                max_position: Optional[int] = None) -> StepLayout:
+    """Lay the entries out as rows (host only).  ``starts[i]`` is the position of entry i's
+    first token.  ``pad_to``: add padding rows (slot -1) up to this many rows.  ``want_all``:
+    every row is wanted, padding included.  ``max_position``: an upper bound to plan key
+    splits with instead of the largest position of this step."""
     tokens: List[int] = []
     positions: List[int] = []
     slots: List[int] = []
@@ -157,36 +171,97 @@ def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequen
     for lag in lags:
         put(f"pos{lag}", [max(0, p - lag) for p in positions])
         put(f"slot{lag}", [s if p - lag >= 0 else -1 for s, p in zip(slots, positions)])
-    plans = {}
+    counts = {}
     for g in sorted(set(group_sizes)):
         keys, rows = plan_tiles(seg_rows, g)
-        plans[g] = (len(keys), len(rows))
+        counts[g] = (len(keys), len(rows))
         put(f"k0_{g}", [t[0] for t in keys])
         put(f"kn_{g}", [t[1] for t in keys])
         put(f"r0_{g}", [t[0] for t in rows])
         put(f"rn_{g}", [t[1] for t in rows])
+    if want_all:
+        want_rows = list(range(n))
     put("want", want_rows)
-    dev = torch.tensor(flat, dtype=torch.int32).to(device, non_blocking=True)
+    max_pos = max(positions[:n_real]) if n_real else 0
+    if max_position is not None:
+        max_pos = max(max_pos, max_position)
+    return StepLayout(flat, offsets, n, segments, lags, counts, len(want_rows), max_pos,
+                      all(s.rows == 1 for s in segments))
+
+
+def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[torch.Tensor],
+                        page_sizes: List[int], fault: torch.Tensor) -> Tuple[StepContext, torch.Tensor]:
+    """Views of the device copy of a layout as a StepContext; returns it and the wanted rows."""
 
     def view(name):
-        a, k = offsets[name]
+        a, k = lay.offsets[name]
         return dev[a:a + k]
 
-    want_dev = view("want").to(torch.int64)
-    max_pos = max(positions[:n_real]) if n_real else 0
-    decode_only = all(s.rows == 1 for s in segments)
     tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr))
-             for g, (nk, nr) in plans.items()}
+             for g, (nk, nr) in lay.tile_counts.items()}
     stages: Dict[int, StepContext] = {}
-    ctx = StepContext(n, view("tokens"), view("positions"), view("slots"), view("last"), segments, block_tables,
-                      page_sizes, fault, max_pos, stages=stages, decode_only=decode_only, tiles=tiles)
-    for lag in lags:
-        st = StepContext(n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), segments,
-                         block_tables, page_sizes, fault, max(0, max_pos - lag), trunk_slot=view("slots"), lag=lag,
-                         stages=stages, decode_only=decode_only, tiles=tiles)
+    ctx = StepContext(lay.n, view("tokens"), view("positions"), view("slots"), view("last"), lay.segments,
+                      block_tables, page_sizes, fault, lay.max_position, stages=stages,
+                      decode_only=lay.decode_only, tiles=tiles)
+    for lag in lay.lags:
+        st = StepContext(lay.n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), lay.segments,
+                         block_tables, page_sizes, fault, max(0, lay.max_position - lag), trunk_slot=view("slots"),
+                         lag=lag, stages=stages, decode_only=lay.decode_only, tiles=tiles)
         st.scratch = ctx.scratch
         stages[lag] = st
-    return ctx, want_dev, len(want_rows)
+    return ctx, view("want")
+
+
+def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int],
+               block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
+               device: torch.device, vocab_size: int, pad_to: Optional[int] = None,
+               group_sizes: Sequence[int] = ()) -> Tuple[StepContext, torch.Tensor, int]:
+    """Rows, metadata and context of one step; all per-step arrays go to the device in one
+    copy.  Returns the context, the device indices of the wanted rows, and their count."""
+    lay = layout_step(entries, starts, lags, vocab_size, pad_to=pad_to, group_sizes=group_sizes)
+    dev = torch.tensor(lay.flat, dtype=torch.int32).to(device, non_blocking=True)
+    ctx, want = context_from_layout(lay, dev, block_tables, page_sizes, fault)
+    return ctx, want, lay.n_want
+
+
+class StaticMeta:
+    """A fixed device buffer for the per-step arrays of steps that all have the same layout
+    (the same number of rows, tiles and wanted rows), filled through a small ring of pinned
+    host buffers: a host buffer is written again only after the copy that read it last has
+    finished, so the host may run ahead of the device."""
+
+    RING = 4
+
+    def __init__(self, capacity: int, device: torch.device):
+        cuda = device.type == "cuda"
+        self.hosts = [torch.zeros(capacity, dtype=torch.int32).pin_memory() if cuda else
+                      torch.zeros(capacity, dtype=torch.int32) for _ in range(self.RING)]
+        self.events = [torch.cuda.Event() if cuda else None for _ in range(self.RING)]
+        self.recorded = [False] * self.RING
+        self.turn = 0
+        self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
+        self.layout: Optional[Dict[str, Tuple[int, int]]] = None
+        self.used = 0
+
+    def upload(self, flat: List[int], offsets: Dict[str, Tuple[int, int]]) -> torch.Tensor:
+        if len(flat) > self.dev.numel():
+            raise ValueError(f"step metadata of {len(flat)} words exceeds the static buffer ({self.dev.numel()})")
+        if self.layout is None:
+            self.layout = dict(offsets)
+            self.used = len(flat)
+        elif self.layout != offsets:
+            raise ValueError("the layout of a step's metadata changed under a captured graph")
+        i = self.turn
+        self.turn = (self.turn + 1) % self.RING
+        if self.recorded[i]:
+            self.events[i].synchronize()
+        host = self.hosts[i]
+        host[: self.used] = torch.tensor(flat, dtype=torch.int32)
+        self.dev[: self.used].copy_(host[: self.used], non_blocking=True)
+        if self.events[i] is not None:
+            self.events[i].record()
+            self.recorded[i] = True
+        return self.dev
 
 
 def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int) -> TileSet:

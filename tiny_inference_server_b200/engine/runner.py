@@ -56,6 +56,10 @@ class ModelRunner:
         self.group_sizes = sorted({g for p in self.model.walk_parts() if hasattr(p, "tile_group_sizes")
                                    for g in p.tile_group_sizes()})
         self.aux = bool(self.engine.mtp)
+        self.graphs = None
+        if self.engine.cuda_graphs and self.device.type == "cuda" and all(p.graph_safe for p in self.model.walk_parts()):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
         self.steps_run = 0
         self.rows_run = 0
 
@@ -98,6 +102,10 @@ class ModelRunner:
                                  f"the context limit {self.max_positions}")
         starts = [self.cache.extend(e.slot, len(e.tokens)) for e in entries]
         self.cache.sync_tables()
+        if self.graphs is not None and pad_to is None and all(len(e.tokens) == 1 for e in entries):
+            self.steps_run += 1
+            self.rows_run += len(entries)
+            return self.graphs.step(entries, starts)
         ctx, want_rows, _ = build_step(entries, starts, self.lags,
                                        [g.table_dev for g in self.cache.groups],
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,

@@ -24,6 +24,8 @@ class GqaAttention(Mixer):
     ``lag``: the layer belongs to a stage that runs this many positions behind the trunk.
     """
 
+    graph_safe = True
+
     def __init__(self, width: int, num_heads: int, kv_heads: int, head_dim: int, position,
                  window: Optional[int] = None, lag: int = 0, prefix: str = "",
                  names: Optional[Dict[str, str]] = None):

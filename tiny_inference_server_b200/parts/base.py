@@ -70,6 +70,11 @@ class LayerBinding:
 class Part:
     """Base of every part: weights by name, placed on the device in ``load``."""
 
+    #: whether ``forward`` may be captured in a CUDA graph: it launches the same kernels with
+    #: the same arguments whatever the step holds, and reads what changes (tokens, positions,
+    #: slots, tiles) from the step's device arrays only
+    graph_safe = True
+
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
 
@@ -116,7 +121,11 @@ class Mixer(Part):
     ``n`` rows of this step in the compute dtype; the result is the update the block
     adds to the residual stream.  ``step`` (``engine.batch.StepContext``) says which
     request and position each row is; rows of one request are contiguous and in order.
+    A mixer that walks ``step.segments`` on the host is not ``graph_safe`` (the default for
+    mixers); one that leaves all of that to its kernels says so.
     """
+
+    graph_safe = False
 
     def kv_spec(self) -> Optional[KVSpec]:
         return None

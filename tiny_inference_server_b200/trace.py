@@ -85,13 +85,13 @@ class TraceReplayer:
 
 
 def make_runner(model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, mtp: bool = False,
-                device: str = "cuda:0") -> ModelRunner:
+                device: str = "cuda:0", cuda_graphs: bool = True) -> ModelRunner:
     """A runner whose cache pool is made for ``max_tokens`` tokens (each request's count
     rounded up to whole pages), so that a trace which ends and starts requests uses pages
     again."""
     num_pages = max(1, (max_tokens + page_size - 1) // page_size)
     eng = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, max_batch=MAX_LIVE, mtp=mtp,
-                       cuda_graphs=False, device=device)
+                       cuda_graphs=cuda_graphs, device=device)
     return ModelRunner.from_folder(model_dir, eng)
 
 
