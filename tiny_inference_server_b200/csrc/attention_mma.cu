@@ -460,3 +460,54 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     }
     return st;
 }
+
+
+// ----------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate (attention_noalloc.h):
+// the partial results of the key splits go to a fixed array inside this library.
+// ----------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[TIS_NOALLOC_SCRATCH_FLOATS];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel may use; the device address is looked up once per device and kept here.
+static float* g_noalloc_ptr[64] = {nullptr};
+
+TIS_API int tis_attn_decode_noalloc(const void* q, int q_stride, void* out, int out_stride, const void* plane,
+                                    const int* block_table, int bt_stride, int num_pages, const int* positions,
+                                    const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                                    int n_rows, int H, int KVH, int page_size, int window, float scale,
+                                    int keys_per_split, int num_splits, int* fault, cudaStream_t stream) {
+    if (n_rows <= 0 || H <= 0 || num_splits <= 0) {
+        tis_set_error("attn_decode_noalloc: %d rows, %d heads, %d splits", n_rows, H, num_splits);
+        return TIS_BAD_SIZE;
+    }
+    const size_t need = (size_t)n_rows * H * num_splits * (HD + 1);
+    if (need > (size_t)TIS_NOALLOC_SCRATCH_FLOATS) {
+        tis_set_error("attn_decode_noalloc: %d rows x %d heads x %d splits need %zu floats of scratch; the built-in "
+                      "array holds %u (use fewer splits or rows, or tis_attn_mma with scratch of your own)",
+                      n_rows, H, num_splits, need, (unsigned)TIS_NOALLOC_SCRATCH_FLOATS);
+        return TIS_BAD_SIZE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        tis_set_error("attn_decode_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+        return TIS_CUDA_ERROR;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // set-up, once per device, with that device current
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            tis_set_error("attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return TIS_CUDA_ERROR;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    // one split needs no scratch at all; tis_attn_mma ignores the pointer then
+    return tis_attn_mma(MODE_KEYS, q, q_stride, out, out_stride, plane, block_table, bt_stride, num_pages, positions,
+                        row_slot, tile_row0, tile_rows, num_tiles, n_rows, H, KVH, page_size, window, scale,
+                        keys_per_split, num_splits, g_noalloc_ptr[dev], fault, stream);
+}
