@@ -21,7 +21,8 @@ from tiny_inference_server_b200.trace import TraceReplayer, make_runner
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir))
-LENGTHS = {"A": [1, 7, 16, 33, 50, 97, 64, 80, 120, 111, 70], "B": [2, 9, 31, 64, 100, 130, 77, 90, 128, 200],
+LENGTHS_WIDE = [70, 33, 150, 5, 200, 90]
+LENGTHS = {"WIDE": LENGTHS_WIDE, "A": [1, 7, 16, 33, 50, 97, 64, 80, 120, 111, 70], "B": [2, 9, 31, 64, 100, 130, 77, 90, 128, 200],
            "C": [3, 40, 61, 90, 150, 70, 101, 64, 33, 88], "D": [5, 18, 47, 80, 33, 60, 90, 64, 71]}
 # float32: rounding of a float32 engine against a float64 oracle.
 # bfloat16: weights are the same bfloat16 numbers on both sides; activations are rounded
@@ -97,6 +98,27 @@ def test_replay_matches_plain(name, mode, dtype, tmp_path, tmp_path_factory):
         pool = runner.cache.groups[0].pool
         assert pool.allocations > pool.num_pages, "the trace does not use pages again"
     _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "mixed"])
+def test_replay_at_the_sizes_of_the_0_9b_model(mode, dtype, tmp_path, tmp_path_factory):
+    """Two layers and one MTP head with the 0.9B model's layer sizes (width 1536, 12 query
+    and 3 kv heads of 128, SwiGLU 4096, vocabulary 49152)."""
+    cfg, page, folder, seqs, plain = _setup("WIDE", tmp_path_factory)
+    steps = _steps(mode, seqs)
+    max_tokens = trace_tools.max_live_tokens(steps, round_to=64)
+    runner = make_runner(folder, dtype, max_tokens, page_size=page, mtp=True)
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    assert runner.cache.drained()
+    # float32: the same absolute bound as for the tiny models.  bfloat16: logits reach ~4.7 here
+    # (width 1536) and every activation is rounded to 8 bits of mantissa (0.4 % each time), so
+    # the bound is relative to the largest logit: 1.5 %.
+    scale = float(max(plain[r]["main"].abs().max() for r in plain))
+    tol = TOL["float32"] if dtype == "float32" else 1.5e-2 * scale
+    worst = _compare(cfg, steps, out_dir, seqs, plain, tol)
+    print(f"worst error {worst:.3g} at logit scale {scale:.3g}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

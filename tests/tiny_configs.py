@@ -34,8 +34,14 @@ TINY_D = dict(architecture="gqa_mtp_transformer", vocab_size=200, hidden_size=48
               cache_source=[None, None, 1])
 TINY_D_PAGE = 16
 
+# the layer sizes of the upstream 0.9B model (Config/config.py:11-23), two layers and one MTP head of them
+WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=2, num_heads=12,
+            num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
+            tie_word_embeddings=True, num_mtp_heads=1)
+WIDE_PAGE = 16
+
 ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
-       "D": (TINY_D, TINY_D_PAGE, 3)}
+       "D": (TINY_D, TINY_D_PAGE, 3), "WIDE": (WIDE, WIDE_PAGE, 4)}
 
 
 def make_model_folder(cfg_dict: dict, seed: int, folder: str, std: float = 0.02) -> str:
