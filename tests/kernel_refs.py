@@ -64,6 +64,20 @@ def _rotate(x, cos, sin, interleaved):
     return y
 
 
+def cache_row(x, pos):
+    """The cache's row format: a row of keys or values (last axis: head size) is stored as
+    16-byte chunks rotated by the position, logical chunk c at chunk (c + pos) mod chunks."""
+    n = 16 // x.element_size()
+    hd = x.shape[-1]
+    return x.reshape(*x.shape[:-1], hd // n, n).roll(pos % (hd // n), dims=-2).reshape(x.shape)
+
+
+def cache_row_inverse(x, pos):
+    n = 16 // x.element_size()
+    hd = x.shape[-1]
+    return x.reshape(*x.shape[:-1], hd // n, n).roll(-(pos % (hd // n)), dims=-2).reshape(x.shape)
+
+
 def rope_kv_write(qkv, positions, row_slot, cos, sin, plane, block_table, num_heads, kv_heads, head_dim,
                   page_size, fault, interleaved=False, write_kv=True):
     n = qkv.shape[0]
@@ -84,17 +98,28 @@ def rope_kv_write(qkv, positions, row_slot, cos, sin, plane, block_table, num_he
             continue
         k = qkv[r, hq:hq + hkv].to(torch.float32).view(kv_heads, head_dim)
         v = qkv[r, hq + hkv:hq + 2 * hkv].view(kv_heads, head_dim)
-        plane[page, 0, :, pos % page_size, :] = _rotate(k, c, s, interleaved).to(plane.dtype)
-        plane[page, 1, :, pos % page_size, :] = v.to(plane.dtype)
+        plane[page, 0, :, pos % page_size, :] = cache_row(_rotate(k, c, s, interleaved).to(plane.dtype), pos)
+        plane[page, 1, :, pos % page_size, :] = cache_row(v.to(plane.dtype), pos)
 
 
 def gather_kv(plane, block_table, slot, lo, hi, page_size):
     """Keys and values lo..hi-1 of a slot: (hi-lo, KVH, hd) each, float32."""
     idx = torch.arange(lo, hi)
     pages = block_table[slot, (idx // page_size)].long()
-    k = plane[pages, 0, :, idx % page_size, :].to(torch.float32)
-    v = plane[pages, 1, :, idx % page_size, :].to(torch.float32)
-    return k, v
+    k = _unrotate_rows(plane[pages, 0, :, idx % page_size, :], idx)
+    v = _unrotate_rows(plane[pages, 1, :, idx % page_size, :], idx)
+    return k.to(torch.float32), v.to(torch.float32)
+
+
+def _unrotate_rows(x, positions):
+    """x (L, KVH, hd) as stored, row i belonging to positions[i]: back to logical order."""
+    n = 16 // x.element_size()
+    L, kvh, hd = x.shape
+    nch = hd // n
+    chunks = x.reshape(L, kvh, nch, n).permute(0, 2, 1, 3)                       # (L, nch, KVH, n)
+    phys = (torch.arange(nch)[None, :] + positions[:, None]) % nch               # logical c -> physical chunk
+    out = chunks[torch.arange(L)[:, None], phys]                                 # (L, nch, KVH, n)
+    return out.permute(0, 2, 1, 3).reshape(L, kvh, hd)
 
 
 def paged_attention(q, out, plane, block_table, positions, row_slot, num_heads, kv_heads, head_dim, page_size,

@@ -167,8 +167,8 @@ def _fill_cache(dtype, slots_len, KVH, hd, page, gen, scale=1.0):
         v = _rand((L, KVH, hd), dtype, gen)
         for t in range(L):
             pg = int(table[s, t // page])
-            plane[pg, 0, :, t % page] = k[t]
-            plane[pg, 1, :, t % page] = v[t]
+            plane[pg, 0, :, t % page] = ref.cache_row(k[t], t)
+            plane[pg, 1, :, t % page] = ref.cache_row(v[t], t)
     return plane, table
 
 
@@ -217,8 +217,8 @@ def test_paged_attention_finds_a_far_key(dtype):
         pg = int(table[0, far // page])
         marker = torch.zeros(hd)
         marker[3] = 30.0
-        pl[pg, 0, :, far % page] = marker.to(dtype)          # key: large along one axis
-        pl[pg, 1, :, far % page] = torch.full((hd,), 5.0).to(dtype)   # value: easy to recognise
+        pl[pg, 0, :, far % page] = ref.cache_row(marker.to(dtype), far)   # key: large along one axis
+        pl[pg, 1, :, far % page] = torch.full((hd,), 5.0).to(dtype)       # value: easy to recognise
         qq = q.clone()
         qq[:, : H * hd] = 0
         for h in range(H):
@@ -249,7 +249,7 @@ def test_paged_attention_window_edge(dtype):
         pg = int(table[0, key_pos // page])
         marker = torch.zeros(hd)
         marker[0] = 40.0
-        pl[pg, 0, 0, key_pos % page] = marker.to(dtype)
+        pl[pg, 0, 0, key_pos % page] = ref.cache_row(marker.to(dtype), key_pos)
         pl[pg, 1, 0, key_pos % page] = torch.full((hd,), 9.0).to(dtype)
         q = torch.zeros(1, (H + 2 * KVH) * hd)
         q[0, 0] = 40.0

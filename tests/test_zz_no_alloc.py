@@ -41,11 +41,12 @@ def _call(lib, name, q, out, plane, table, positions, row_slot, tiles0, tilesn, 
     n = q.shape[0]
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     scale = ctypes.c_float(1.0 / math.sqrt(hd))
-    common = [p(q), q.stride(0), p(out), out.stride(0), p(plane), p(table), table.stride(0), plane.shape[0],
-              p(positions), p(row_slot), p(tiles0), p(tilesn), n, n, H, KVH, page, 0, scale, per, splits]
+    head = [p(q), q.stride(0), p(out), out.stride(0), p(plane), p(table), table.stride(0), plane.shape[0],
+            p(positions), p(row_slot), p(tiles0), p(tilesn), n]
+    tail = [n, H, KVH, page, 0, scale, per, splits]
     if name == "tis_attn_mma":
-        return lib.tis_attn_mma(1, *common, p(scratch), p(fault), stream)
-    return lib.tis_attn_decode_noalloc(*common, p(fault), stream)
+        return lib.tis_attn_mma(1, *head, 1, *tail, p(scratch), p(None), p(fault), stream)
+    return lib.tis_attn_decode_noalloc(*head, *tail, p(fault), stream)
 
 
 @pytest.mark.parametrize("H,KVH,hd,page,lens,splits", [(12, 3, 128, 16, [4000, 517, 64, 1, 2300, 999, 3, 70], 16),

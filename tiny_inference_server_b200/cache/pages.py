@@ -7,6 +7,14 @@ they keep every key or a window of them — and every group has pages of its own
 tensor ``[planes, pages, 2, kv_heads, page_size, head_dim]``, a free list, and one
 block table per request slot.  A page id addresses the same page in every plane of its
 group, as upstream's does in every layer.
+
+Row format.  Inside a page the keys (and the values) of one kv head are ``page_size`` rows
+of ``head_dim`` elements.  Each row is stored as 16-byte chunks *rotated by the token's
+position*: logical chunk ``c`` lies at chunk ``(c + position) mod chunks_per_row``
+(``cache_chunk`` in ``csrc/common.cuh``).  The attention kernels copy a page's rows into
+shared memory unchanged, in one bulk copy, and the rotation is what lets them read the
+dense rows there without bank conflicts.  Only kernels read and write the pages; anything
+else that does (tests) has to apply the same rotation.
 """
 from __future__ import annotations
 

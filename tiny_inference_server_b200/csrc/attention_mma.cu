@@ -14,13 +14,17 @@
 //              warp w owns keys 16w..16w+15 of every 64-key tile; the four warps' partial
 //              results are merged through shared memory at the end.
 //
-// Keys and values of 64 positions are staged in shared memory by cp.async, two stages,
-// found through the block table position by position, so any page size works.  Rows are
-// padded by 16 bytes, which keeps ldmatrix free of bank conflicts for every head size.
+// Keys and values of 64 positions are staged in shared memory by the TMA engine: one bulk
+// copy (cp.async.bulk) per page's share of the tile (any page size), counted on an mbarrier
+// per stage.  The cache stores each row with its 16-byte chunks rotated by the position
+// (common.cuh), so the rows can lie dense in shared memory, exactly as copied, and ldmatrix
+// still meets no bank conflict (head sizes 64, 128, 256; a few two-way conflicts at others).
+// Every wait on an mbarrier is bounded; one that runs out sets the fault word.
 // Scores, running maximum, sum and the output accumulate in float32; probabilities are
 // rounded to bfloat16 for the P.V product (as paged_attention_kernels.py:108 upstream).
 // With more than one key split a CTA writes a normalised partial output and its log2-sum
-// to scratch memory and `attn_merge_kernel` combines them.
+// to scratch memory; the split that finishes last (a counter per tile and kv head) merges
+// them, or, when the caller gives no counters, `attn_merge_kernel` does.
 #include "common.cuh"
 
 #ifndef TIS_HD
@@ -29,11 +33,20 @@
 
 constexpr int HD = TIS_HD;
 constexpr int KT = 64;               // keys per staged tile
-constexpr int RS = HD + 8;           // shared-memory row stride (elements)
+constexpr int RS = HD;               // shared-memory row stride (elements): rows lie dense, as in the cache
 constexpr int NTHREADS = 128;
+// stages of the copy pipeline: two.  The kernels are bound by the latency of a warp's own
+// instruction stream, so CTAs per SM (three at head size 128 with two stages) count for more
+// than a deeper pipeline; measured on a B200.
+constexpr int STAGE_BYTES = 2 * KT * RS * 2;
+#ifdef TIS_ATTN_STAGES
+constexpr int STAGES = TIS_ATTN_STAGES;
+#else
+constexpr int STAGES = 2;
+#endif
+constexpr int NCH = HD / 8;          // 16-byte chunks of a cache row (rotated by the position: common.cuh)
 constexpr int KSTEPS = HD / 16;      // k16 steps of Q.K^T
 constexpr int DTILES = HD / 8;       // n8 tiles of the output
-constexpr int CHUNKS = HD / 8;       // 16-byte chunks per row
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
 
 enum { MODE_ROWS = 0, MODE_KEYS = 1 };
@@ -48,15 +61,46 @@ struct AttnParams {
     float scale_log2;
     int keys_per_split, num_splits;
     float* part_o; float* part_lse;
+    int* counters;          // per (tile, kv head): splits that have finished; null: merge in a kernel of its own
     int* fault;
 };
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+// ---- mbarrier and bulk-copy (TMA) helpers --------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, int bytes) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n"
+                 ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One row of `bytes` (a multiple of 16) from global to shared memory by the TMA engine; the
+// bytes are counted on `bar` when they have landed.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, int bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Wait for the phase with this parity, at most MBAR_SPINS polls: a wait that runs out sets
+// the fault word and goes on (the kernel never hangs; its result is then not to be used).
+constexpr int MBAR_SPINS = 1 << 20;
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, int* fault) {
+    unsigned done = 0;
+    for (int spin = 0; spin < MBAR_SPINS; ++spin) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (done) return;
+    }
+    atomicExch(fault, 4);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -78,41 +122,69 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Stage keys and values of positions kt..kt+63 of the slot; positions outside [lo, hi) are
-// zero-filled.  Two threads per position, alternating 16-byte chunks.
-__device__ __forceinline__ void load_tile(bf16* stage, const AttnParams& p, const int* bt, int kvh, int kt, int lo,
-                                          int hi, int tid) {
-    const int key = tid >> 1, half = tid & 1;
-    const int j = kt + key;
-    const bf16* src_k = p.plane;
-    int bytes = 0;
-    if (j >= lo && j < hi) {
-        const int page = bt[j / p.page_size];
-        if (page >= 0 && page < p.num_pages) {
-            src_k = p.plane + ((size_t)page * 2 * p.KVH + kvh) * (size_t)p.page_size * HD + (size_t)(j % p.page_size) * HD;
-            bytes = 16;
-        } else {
-            atomicExch(p.fault, 3);
-        }
-    }
-    const bf16* src_v = src_k + (bytes ? (size_t)p.KVH * p.page_size * HD : 0);
-    bf16* dk = stage + key * RS;
-    bf16* dv = stage + (KT + key) * RS;
-#pragma unroll
-    for (int c = half; c < CHUNKS; c += 2) {
-        cp_async16(dk + c * 8, src_k + (bytes ? c * 8 : 0), bytes);
-        cp_async16(dv + c * 8, src_v + (bytes ? c * 8 : 0), bytes);
-    }
+// Page id of the segment that thread `tid` leads in the tile that starts at position kt
+// (-1: no such segment).  Segment s of a tile is its share of logical page kt / page_size + s;
+// threads 2s and 2s+1 lead its keys and its values.
+__device__ __forceinline__ int fetch_page(const AttnParams& p, const int* bt, int kt, int hi, int tid) {
+    const int lp = kt / p.page_size + (tid >> 1);
+    const long long first = (long long)lp * p.page_size;
+    if (first >= kt + KT || first >= hi) return -1;
+    return bt[lp];
 }
 
-template <int MODE>
+// Stage keys and values of positions kt..kt+63 of the slot.  The rows of one page lie
+// together in the cache, so one bulk copy brings a page's share of the tile (keys or values)
+// into the dense shared-memory tile: threads 2s / 2s+1 order segment s.  Rows of positions
+// outside [lo, hi) are zero-filled by thread pairs.  Every thread arrives on the stage's
+// mbarrier, leaders with the bytes they ordered.  `page` is the leader's page id (fetch_page).
+__device__ __forceinline__ void load_tile(bf16* stage, unsigned long long* bar, const AttnParams& p, int page,
+                                          int kvh, int kt, int lo, int hi, int tid) {
+    const int which = tid & 1;
+    // zero-fill: thread pair (row = tid/2, which) if its position is outside the range
+    {
+        const int j = kt + (tid >> 1);
+        if (j < lo || j >= hi) {
+            bf16* dst = stage + (which * KT + (tid >> 1)) * RS;
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = z;
+        }
+    }
+    // segment leader
+    const int lp = kt / p.page_size + (tid >> 1);
+    const long long pfirst = (long long)lp * p.page_size;
+    int j0 = (int)(pfirst > kt ? pfirst : kt);
+    if (j0 < lo) j0 = lo;
+    long long j1 = pfirst + p.page_size;
+    if (j1 > kt + KT) j1 = kt + KT;
+    if (j1 > hi) j1 = hi;
+    const int nrows = (int)(j1 - j0);
+    if (pfirst < kt + KT && nrows > 0) {
+        if (page >= 0 && page < p.num_pages) {
+            const bf16* src = p.plane + (((size_t)page * 2 + which) * p.KVH + kvh) * (size_t)p.page_size * HD +
+                              (size_t)(j0 - pfirst) * HD;
+            const int bytes = nrows * HD * 2;
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_copy_g2s(stage + (which * KT + (j0 - kt)) * RS, src, bytes, bar);
+            return;
+        }
+        atomicExch(p.fault, 3);
+    }
+    mbar_arrive(bar);
+}
+
+// NR: packed rows a thread keeps softmax state for.  2: rows g and g+8 of the 16 a warp owns.
+// 1: only row g -- the tile has at most 8 packed rows (a decode row with up to 8 query heads per
+// kv head), rows 8..15 are padding and all their bookkeeping is left out.
+template <int MODE, int NR>
 __global__ void __launch_bounds__(NTHREADS)
 attn_mma_kernel(const AttnParams p) {
     constexpr int NT = MODE == MODE_ROWS ? 8 : 2;        // n8 key tiles a warp scores per staged tile
     constexpr int KB = MODE == MODE_ROWS ? 4 : 1;        // k16 key blocks a warp multiplies with V
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* stages = reinterpret_cast<bf16*>(smem_raw);    // 2 stages x (K[64][RS], V[64][RS])
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw);    // STAGES x (K[64][RS], V[64][RS])
     __shared__ int sh_first;
+    __shared__ __align__(8) unsigned long long bars[STAGES];
 
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -121,6 +193,11 @@ attn_mma_kernel(const AttnParams p) {
     const int G = p.G;
 
     // first valid row of the tile (rows of a stage that lags the trunk start with padding)
+    if (tid == 0) {
+#pragma unroll
+        for (int st = 0; st < STAGES; ++st) mbar_init(&bars[st], NTHREADS);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
     if (warp == 0) {
         const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
         const bool v1 = lane + 32 < rows && p.row_slot[row0 + lane + 32] >= 0;
@@ -138,7 +215,7 @@ attn_mma_kernel(const AttnParams p) {
     for (int i = 0; i < 2; ++i) {
         const int m = mbase + 8 * i;
         const int r = m / G, g = m - r * G;
-        valid[i] = r < rows && first >= 0 && r >= first;
+        valid[i] = i < NR && r < rows && first >= 0 && r >= first;
         r_idx[i] = row0 + (valid[i] ? r : 0);
         head[i] = kvh * G + g;
         const int pos = valid[i] ? p.positions[r_idx[i]] : 0;
@@ -185,15 +262,33 @@ attn_mma_kernel(const AttnParams p) {
         const int ntiles = (range_hi - kt0 + KT - 1) / KT;
         constexpr int STAGE_ELEMS = 2 * KT * RS;
 
-        load_tile(stages, p, bt, kvh, kt0, range_lo, range_hi, tid);
-        cp_async_commit();
+        // prologue: order STAGES-1 tiles; the page id a thread needs for the tile after is
+        // fetched one tile ahead, so its latency is off the path
+        int page = fetch_page(p, bt, kt0, range_hi, tid);
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < ntiles) {
+                const int page_next = fetch_page(p, bt, kt0 + (st + 1) * KT, range_hi, tid);
+                load_tile(stages + st * STAGE_ELEMS, &bars[st], p, page, kvh, kt0 + st * KT, range_lo, range_hi, tid);
+                page = page_next;
+            }
+        }
         for (int it = 0; it < ntiles; ++it) {
             const int kt = kt0 + it * KT;
-            bf16* cur = stages + (it & 1) * STAGE_ELEMS;
-            if (it + 1 < ntiles) load_tile(stages + ((it + 1) & 1) * STAGE_ELEMS, p, bt, kvh, kt + KT, range_lo, range_hi, tid);
-            cp_async_commit();
-            cp_async_wait<1>();
-            __syncthreads();
+            const int stg = it % STAGES;
+            bf16* cur = stages + stg * STAGE_ELEMS;
+            __syncthreads();                   // everyone is done reading the stage of tile it-1 ...
+            {
+                const int nx = it + STAGES - 1;    // ... which tile it+STAGES-1 takes
+                if (nx < ntiles) {
+                    const int page_next = fetch_page(p, bt, kt0 + (nx + 1) * KT, range_hi, tid);
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    load_tile(stages + (nx % STAGES) * STAGE_ELEMS, &bars[nx % STAGES], p, page, kvh, kt0 + nx * KT,
+                              range_lo, range_hi, tid);
+                    page = page_next;
+                }
+            }
+            mbar_wait(&bars[stg], (unsigned)((it / STAGES) & 1), p.fault);     // tile `it` has landed
 
             const bf16* ks = cur;
             const bf16* vs = cur + KT * RS;
@@ -209,53 +304,72 @@ attn_mma_kernel(const AttnParams p) {
                 for (int kk = 0; kk < KSTEPS; ++kk) {
                     unsigned b[4];
                     const int key = kofs + j * 8 + ((lane >> 4) << 3) + (lane & 7);
-                    const int kcol = kk * 16 + (((lane >> 3) & 1) << 3);
-                    ldmatrix_x4(b, ks + key * RS + kcol);
+                    const int chunk = (2 * kk + ((lane >> 3) & 1) + kt + key) % NCH;     // rotated by the position
+                    ldmatrix_x4(b, ks + key * RS + chunk * 8);
                     mma_bf16(s[j], qa[kk], b[0], b[1]);
                     mma_bf16(s[j + 1], qa[kk], b[2], b[3]);
                 }
             }
-            // ---- scale, mask, online softmax
+            // ---- scale, mask (only where a row's range ends inside this tile), online softmax
             float mx[2] = {-INFINITY, -INFINITY};
+            const int t_lo = kt + kofs, t_hi = kt + kofs + NT * 8;
+            const bool interior = t_lo >= range_lo && t_hi <= range_hi && t_lo >= lo_row[0] && t_hi <= hi_row[0] &&
+                                  (NR == 1 || (t_lo >= lo_row[1] && t_hi <= hi_row[1]));
+            if (interior) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
+                for (int j = 0; j < NT; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = e >> 1;
-                    const int kidx = kt + kofs + j * 8 + 2 * t_lane + (e & 1);
-                    const bool ok = kidx >= lo_row[i] && kidx < hi_row[i] && kidx >= range_lo && kidx < range_hi;
-                    const float v = ok ? s[j][e] * p.scale_log2 : -INFINITY;
-                    s[j][e] = v;
-                    mx[i] = fmaxf(mx[i], v);
+                    for (int e = 0; e < 2 * NR; ++e) {
+                        const float v = s[j][e] * p.scale_log2;
+                        s[j][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 2 * NR; ++e) {
+                        const int i = e >> 1;
+                        const int kidx = kt + kofs + j * 8 + 2 * t_lane + (e & 1);
+                        const bool ok = kidx >= lo_row[i] && kidx < hi_row[i] && kidx >= range_lo && kidx < range_hi;
+                        const float v = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                        s[j][e] = v;
+                        mx[i] = fmaxf(mx[i], v);
+                    }
                 }
             }
-            float alpha[2], m_safe[2];
+            float alpha[2] = {1.f, 1.f}, m_safe[2] = {0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NR; ++i) {
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
                 const float m_new = fmaxf(m_run[i], mx[i]);
                 m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;
-                alpha[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f(m_run[i] - m_safe[i]);
+                alpha[i] = (m_run[i] == -INFINITY) ? 0.f : fast_exp2(m_run[i] - m_safe[i]);
                 m_run[i] = m_new;
             }
             float psum[2] = {0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
+                for (int e = 0; e < 2 * NR; ++e) {
                     const int i = e >> 1;
-                    const float pv = exp2f(s[j][e] - m_safe[i]);      // exp2(-inf) = 0 for masked keys
+                    const float pv = fast_exp2(s[j][e] - m_safe[i]);  // 2^-inf = 0 for masked keys
                     s[j][e] = pv;
                     psum[i] += pv;
                 }
+                if (NR == 1) { s[j][2] = 0.f; s[j][3] = 0.f; }
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+            for (int i = 0; i < NR; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+            // the running maxima settle after a few tiles; skip the rescaling when none moved
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-            for (int d = 0; d < DTILES; ++d) {
-                o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
-                o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+                for (int d = 0; d < DTILES; ++d) {
+                    o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+                    if (NR == 2) { o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
+                }
             }
             // ---- O += P V
 #pragma unroll
@@ -269,19 +383,17 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
                 for (int d = 0; d < DTILES; d += 2) {
                     unsigned b[4];
-                    ldmatrix_x4_trans(b, vs + key * RS + d * 8 + ((lane >> 4) << 3));
+                    ldmatrix_x4_trans(b, vs + key * RS + ((d + (lane >> 4) + kt + key) % NCH) * 8);
                     mma_bf16(o[d], pa, b[0], b[1]);
                     mma_bf16(o[d + 1], pa, b[2], b[3]);
                 }
             }
-            __syncthreads();        // the stage is refilled two iterations later
         }
-        cp_async_wait<0>();
     }
 
     // ---- row sums over the four lanes that share a row
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NR; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
@@ -293,7 +405,7 @@ attn_mma_kernel(const AttnParams p) {
         float* mm = mo + 4 * 16 * HD;                            // [4][16]
         float* ml = mm + 4 * 16;                                 // [4][16]
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NR; ++i) {
             const int m = g_lane + 8 * i;
             if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
 #pragma unroll
@@ -354,6 +466,70 @@ attn_mma_kernel(const AttnParams p) {
             }
         }
     }
+
+    // ---- the split that finishes last merges all partial results of this (tile, kv head)
+    if (p.num_splits > 1 && p.counters != nullptr) {
+        __shared__ int sh_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int t = atomicAdd(&p.counters[tile * p.KVH + kvh], 1);
+            sh_last = (t == p.num_splits - 1);
+        }
+        __syncthreads();
+        if (sh_last) {
+            __threadfence();
+            // weights of every (row, head, split) first, into shared memory (the staging area is free now)
+            float* wgt = reinterpret_cast<float*>(smem_raw);
+            const int pairs = rows * G;
+            const int ns = p.num_splits;
+            const bool fits = (size_t)pairs * ns * sizeof(float) <= (size_t)STAGES * STAGE_BYTES;
+            for (int rg = warp; rg < pairs; rg += NTHREADS / 32) {
+                const int r = rg / G, g = rg - r * G;
+                const size_t pr = ((size_t)(row0 + r) * p.H + kvh * G + g) * ns;
+                float mt = -INFINITY;
+                for (int sp = lane; sp < ns; sp += 32) mt = fmaxf(mt, __ldcg(p.part_lse + pr + sp));
+                mt = warp_max(mt);
+                float ws = 0.f;
+                for (int sp = lane; sp < ns; sp += 32) {
+                    const float l = __ldcg(p.part_lse + pr + sp);
+                    ws += (l == -INFINITY) ? 0.f : exp2f(l - mt);
+                }
+                ws = warp_sum(ws);
+                const float inv = ws > 0.f ? 1.f / ws : 0.f;
+                if (fits)
+                    for (int sp = lane; sp < ns; sp += 32) {
+                        const float l = __ldcg(p.part_lse + pr + sp);
+                        wgt[rg * ns + sp] = (l == -INFINITY) ? 0.f : exp2f(l - mt) * inv;
+                    }
+            }
+            __syncthreads();
+            for (int idx = tid; idx < pairs * HD; idx += NTHREADS) {
+                const int rg = idx / HD, d = idx - rg * HD;
+                const int r = rg / G, g = rg - r * G;
+                const int row = row0 + r, hq = kvh * G + g;
+                const size_t pr = ((size_t)row * p.H + hq) * ns;
+                float acc = 0.f;
+                if (fits) {
+                    const float* w = wgt + rg * ns;
+#pragma unroll 4
+                    for (int sp = 0; sp < ns; ++sp) acc += w[sp] * __ldcg(p.part_o + (pr + sp) * HD + d);
+                } else {
+                    float mt = -INFINITY, ws = 0.f;
+                    for (int sp = 0; sp < ns; ++sp) mt = fmaxf(mt, __ldcg(p.part_lse + pr + sp));
+                    for (int sp = 0; sp < ns; ++sp) {
+                        const float l = __ldcg(p.part_lse + pr + sp);
+                        const float w = (l == -INFINITY) ? 0.f : exp2f(l - mt);
+                        ws += w;
+                        acc += w * __ldcg(p.part_o + (pr + sp) * HD + d);
+                    }
+                    acc = ws > 0.f ? acc / ws : 0.f;
+                }
+                p.out[(size_t)row * p.out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(acc);
+            }
+            if (tid == 0) p.counters[tile * p.KVH + kvh] = 0;      // ready for the next launch
+        }
+    }
 }
 
 // out[row, head] = sum_s w_s * part_o[row, head, s],  w_s = 2^(lse_s - max) / sum, for the rows of one tile
@@ -384,12 +560,32 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 }
 
 static size_t smem_bytes(int mode) {
-    size_t stage = (size_t)2 * 2 * KT * RS * sizeof(bf16);
+    size_t stage = (size_t)STAGES * STAGE_BYTES;
     size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float) : 0;
     return stage > merge ? stage : merge;
 }
 
 TIS_API int tis_attn_head_dim() { return HD; }
+
+// CTAs of one SM that run at a time (registers and shared memory), times the SMs of the device.
+TIS_API int tis_attn_resident_ctas(int mode, int half) {
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t smem = smem_bytes(mode);
+    if (mode == MODE_ROWS) {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_ROWS, 2>, NTHREADS, smem);
+    } else if (half) {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 1>, NTHREADS, smem);
+    } else {
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 2>, NTHREADS, smem);
+    }
+    cudaGetLastError();
+    return per_sm > 0 && sms > 0 ? per_sm * sms : 148 * 2;
+}
 
 // Scratch the caller must provide when num_splits > 1: floats for part_o and part_lse.
 TIS_API size_t tis_attn_scratch_floats(int n_rows, int H, int num_splits) {
@@ -397,11 +593,15 @@ TIS_API size_t tis_attn_scratch_floats(int n_rows, int H, int num_splits) {
 }
 
 // mode: 0 rows (tiles of up to 64/G rows), 1 keys (tiles of up to 16/G rows).
+// max_tile_rows: the most rows any tile has (0: unknown); keys-mode tiles of at most 8 packed
+// rows take a kernel that keeps no state for the padding rows.
+// CTAs of a mode that one SM holds at a time: tis_attn_resident_ctas.
 TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
                          const int* block_table, int bt_stride, int num_pages, const int* positions,
-                         const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles, int n_rows,
-                         int H, int KVH, int page_size, int window, float scale, int keys_per_split, int num_splits,
-                         float* scratch, int* fault, cudaStream_t stream) {
+                         const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                         int max_tile_rows, int n_rows, int H, int KVH, int page_size, int window, float scale,
+                         int keys_per_split, int num_splits, float* scratch, int* counters, int* fault,
+                         cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
     const int G = KVH > 0 ? H / KVH : 0;
     const int mpack = mode == MODE_ROWS ? 64 : 16;
@@ -434,25 +634,30 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.keys_per_split = keys_per_split; p.num_splits = num_splits;
     p.part_o = scratch;
     p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
+    p.counters = num_splits > 1 ? counters : nullptr;
     p.fault = fault;
     const size_t smem = smem_bytes(mode);
     dim3 grid(num_tiles, KVH, num_splits);
     static bool configured = false;          // once per process (and before any stream capture)
     if (!configured) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_ROWS));
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem_bytes(MODE_KEYS));
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_KEYS));
         configured = true;
     }
     if (mode == MODE_ROWS) {
-        attn_mma_kernel<MODE_ROWS><<<grid, NTHREADS, smem, stream>>>(p);
+        attn_mma_kernel<MODE_ROWS, 2><<<grid, NTHREADS, smem, stream>>>(p);
+    } else if (max_tile_rows > 0 && max_tile_rows * G <= 8) {
+        attn_mma_kernel<MODE_KEYS, 1><<<grid, NTHREADS, smem, stream>>>(p);
     } else {
-        attn_mma_kernel<MODE_KEYS><<<grid, NTHREADS, smem, stream>>>(p);
+        attn_mma_kernel<MODE_KEYS, 2><<<grid, NTHREADS, smem, stream>>>(p);
     }
     int st = tis_check_launch("attn_mma");
     if (st != TIS_OK) return st;
-    if (num_splits > 1) {
+    if (num_splits > 1 && counters == nullptr) {
         dim3 mg(H, num_tiles);
         attn_merge_kernel<<<mg, HD < 128 ? (HD < 32 ? 32 : HD) : 128, 0, stream>>>(p.part_o, p.part_lse, (bf16*)out, out_stride,
                                                                                   tile_row0, tile_rows, H, num_splits);
@@ -508,6 +713,6 @@ TIS_API int tis_attn_decode_noalloc(const void* q, int q_stride, void* out, int 
     }
     // one split needs no scratch at all; tis_attn_mma ignores the pointer then
     return tis_attn_mma(MODE_KEYS, q, q_stride, out, out_stride, plane, block_table, bt_stride, num_pages, positions,
-                        row_slot, tile_row0, tile_rows, num_tiles, n_rows, H, KVH, page_size, window, scale,
-                        keys_per_split, num_splits, g_noalloc_ptr[dev], fault, stream);
+                        row_slot, tile_row0, tile_rows, num_tiles, 0, n_rows, H, KVH, page_size, window, scale,
+                        keys_per_split, num_splits, g_noalloc_ptr[dev], nullptr, fault, stream);
 }

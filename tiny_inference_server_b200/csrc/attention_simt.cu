@@ -7,40 +7,26 @@
 // Keys are taken 128 at a time: every thread scores one key, the CTA agrees on the new
 // running maximum, then the threads split the head dimension and add the 128 weighted
 // value rows (online softmax, as paged_attention_kernels.py:88-111 upstream, in base e).
+// Cache rows are stored with their 16-byte chunks rotated by the position (common.cuh).
 #include "common.cuh"
 
 #define SIMT_KEYS 128
 
+// q . k for one cache row of position `pos`: the row's 16-byte chunks are rotated by the
+// position (common.cuh), so physical chunk pc holds logical chunk (pc - pos) mod chunks.
 template <typename T>
-__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd);
-
-template <>
-__device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd, int pos) {
+    constexpr int N = Vec16<T>::N;
+    const int nch = hd / N;
+    int c = (nch - pos % nch) % nch;           // logical chunk of physical chunk 0
     float acc = 0.f;
-    const float4* k4 = reinterpret_cast<const float4*>(k);
-    for (int i = 0; i < hd / 4; ++i) {
-        const float4 v = k4[i];
-        acc += q[4 * i] * v.x;
-        acc += q[4 * i + 1] * v.y;
-        acc += q[4 * i + 2] * v.z;
-        acc += q[4 * i + 3] * v.w;
-    }
-    return acc;
-}
-
-template <>
-__device__ __forceinline__ float dot_row<bf16>(const float* __restrict__ q, const bf16* __restrict__ k, int hd) {
-    float acc = 0.f;
-    const uint4* k8 = reinterpret_cast<const uint4*>(k);
-    for (int i = 0; i < hd / 8; ++i) {
-        const uint4 raw = k8[i];
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int pc = 0; pc < nch; ++pc) {
+        float v[N];
+        Vec16<T>::load(k + pc * N, v);
+        const float* qq = q + c * N;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(p[j]);
-            acc += q[8 * i + 2 * j] * f.x;
-            acc += q[8 * i + 2 * j + 1] * f.y;
-        }
+        for (int j = 0; j < N; ++j) acc += qq[j] * v[j];
+        c = (c + 1 == nch) ? 0 : c + 1;
     }
     return acc;
 }
@@ -89,7 +75,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                 atomicExch(fault, 2);
             } else {
                 ko = (long long)((size_t)page * page_elems + ((size_t)kvh * page_size + (j % page_size)) * hd);
-                s = dot_row<T>(qs, plane + ko, hd) * scale;
+                s = dot_row<T>(qs, plane + ko, hd, j) * scale;
             }
         }
         voff[tid] = ko < 0 ? -1 : ko + (long long)v_shift;
@@ -102,16 +88,20 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
         acc0 *= alpha;
         acc1 *= alpha;
         const int cnt = min(SIMT_KEYS, hi - t0);
+        constexpr int N = Vec16<T>::N;
+        const int nch = hd / N;
         if (tid < hd) {
+            const int c = tid / N, e = tid % N;
             for (int jj = 0; jj < cnt; ++jj) {
                 const long long vo = voff[jj];
-                if (vo >= 0) acc0 += ps[jj] * to_f32(plane[vo + tid]);
+                if (vo >= 0) acc0 += ps[jj] * to_f32(plane[vo + cache_chunk(c, t0 + jj, nch) * N + e]);
             }
         }
         if (tid + SIMT_KEYS < hd) {
+            const int c = (tid + SIMT_KEYS) / N, e = (tid + SIMT_KEYS) % N;
             for (int jj = 0; jj < cnt; ++jj) {
                 const long long vo = voff[jj];
-                if (vo >= 0) acc1 += ps[jj] * to_f32(plane[vo + tid + SIMT_KEYS]);
+                if (vo >= 0) acc1 += ps[jj] * to_f32(plane[vo + cache_chunk(c, t0 + jj, nch) * N + e]);
             }
         }
         __syncthreads();                       // ps, voff are rewritten by the next tile

@@ -15,7 +15,17 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
     const int r = blockIdx.x;
     const T* src = table + (size_t)tokens[r] * d;
     float* dst = out + (size_t)r * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]);
+    constexpr int N = Vec16<T>::N;
+    if (d % N == 0) {
+        for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+            float v[N];
+            Vec16<T>::load(src + i, v);
+#pragma unroll
+            for (int j = 0; j < N; ++j) dst[i + j] = v[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]);
+    }
 }
 
 TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, float* out, int n, int d,
@@ -36,20 +46,53 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
     extern __shared__ float row[];
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * d;
+    constexpr int N = Vec16<T>::N;
+    const bool vec = (d % N == 0);
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = res[base + i];
-        if (delta != nullptr) {
-            v += to_f32(delta[base + i]);
-            res[base + i] = v;
+    if (vec) {
+        for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+            float v[N];
+#pragma unroll
+            for (int j = 0; j < N; j += 4) {
+                const float4 x = *reinterpret_cast<const float4*>(res + base + i + j);
+                v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
+            }
+            if (delta != nullptr) {
+                float dv[N];
+                Vec16<T>::load(delta + base + i, dv);
+#pragma unroll
+                for (int j = 0; j < N; ++j) v[j] += dv[j];
+#pragma unroll
+                for (int j = 0; j < N; j += 4)
+                    *reinterpret_cast<float4*>(res + base + i + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) { row[i + j] = v[j]; ss += v[j] * v[j]; }
         }
-        row[i] = v;
-        ss += v * v;
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = res[base + i];
+            if (delta != nullptr) {
+                v += to_f32(delta[base + i]);
+                res[base + i] = v;
+            }
+            row[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, red);
     const float inv = sqrtf((float)d) / (sqrtf(ss) + eps);
-    if (out != nullptr)
+    if (out == nullptr) return;
+    if (vec) {
+        for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+            float v[N];
+#pragma unroll
+            for (int j = 0; j < N; ++j) v[j] = row[i + j] * inv * scale[i + j];
+            Vec16<T>::store(out + base + i, v);
+        }
+    } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) out[base + i] = from_f32<T>(row[i] * inv * scale[i]);
+    }
 }
 
 TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const float* scale, float eps,
@@ -74,7 +117,8 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
 //
 // qkv row layout: [H*hd queries | KVH*hd keys | KVH*hd values] (keys before values, as
 // the upstream kv_proj: main_models_new.py:104-106).  q is rotated in place.
-// plane layout: [page][2 (k, v)][KVH][page_size][hd].
+// plane layout: [page][2 (k, v)][KVH][page_size][hd]; inside a row the 16-byte chunks are
+// rotated by the position (cache_chunk in common.cuh).
 // pairing: half-split (i, i + rot/2) as upstream rotate_half (main_models_new.py:71-73),
 // or interleaved (2i, 2i+1); only the first `rot` entries of a head are rotated.
 // cos/sin tables: [positions][rot/2] float.
@@ -94,8 +138,70 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     const int half = rot >> 1;
     const float* cs = cos_t + (size_t)pos * half;
     const float* sn = sin_t + (size_t)pos * half;
+    constexpr int N = Vec16<T>::N;                 // elements of a 16-byte chunk
+    const int nch = hd / N;                        // chunks of a cache row
+    const bool fast = !interleaved && rot == hd && (half % N) == 0;
 
-    // queries, in place
+    int page = -1;
+    if (write_kv) {
+        page = block_table[(size_t)slot * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(fault, 1);
+            page = -1;
+        }
+    }
+    const int in_page = pos % page_size;
+    T* kdst = page >= 0 ? plane + ((size_t)page * 2 * KVH * page_size + in_page) * hd : nullptr;   // + h*page_size*hd
+    T* vdst = page >= 0 ? kdst + (size_t)KVH * page_size * hd : nullptr;
+    const T* ksrc = row + (size_t)H * hd;
+    const T* vsrc = ksrc + (size_t)KVH * hd;
+
+    if (fast) {
+        // one work item = the chunk pair (c, c + half/N) of one head: both halves of N rotation pairs
+        const int cpairs = half / N;
+        const int q_items = H * cpairs, k_items = page >= 0 ? KVH * cpairs : 0, v_items = page >= 0 ? KVH * nch : 0;
+        for (int w = threadIdx.x; w < q_items + k_items + v_items; w += blockDim.x) {
+            if (w < q_items + k_items) {
+                const bool is_k = w >= q_items;
+                const int ww = is_k ? w - q_items : w;
+                const int h = ww / cpairs, c = ww - h * cpairs;
+                const T* src = (is_k ? ksrc : row) + (size_t)h * hd;
+                float x1[N], x2[N], cv[N], sv[N], o1[N], o2[N];
+                Vec16<T>::load(src + c * N, x1);
+                Vec16<T>::load(src + half + c * N, x2);
+#pragma unroll
+                for (int j = 0; j < N; j += 4) {
+                    const float4 cc = *reinterpret_cast<const float4*>(cs + c * N + j);
+                    const float4 sc = *reinterpret_cast<const float4*>(sn + c * N + j);
+                    cv[j] = cc.x; cv[j + 1] = cc.y; cv[j + 2] = cc.z; cv[j + 3] = cc.w;
+                    sv[j] = sc.x; sv[j + 1] = sc.y; sv[j + 2] = sc.z; sv[j + 3] = sc.w;
+                }
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    o1[j] = x1[j] * cv[j] - x2[j] * sv[j];
+                    o2[j] = x2[j] * cv[j] + x1[j] * sv[j];
+                }
+                if (!is_k) {
+                    T* dst = row + (size_t)h * hd;
+                    Vec16<T>::store(dst + c * N, o1);
+                    Vec16<T>::store(dst + half + c * N, o2);
+                } else {
+                    T* dst = kdst + (size_t)h * page_size * hd;
+                    Vec16<T>::store(dst + cache_chunk(c, pos, nch) * N, o1);
+                    Vec16<T>::store(dst + cache_chunk(c + cpairs, pos, nch) * N, o2);
+                }
+            } else {
+                const int ww = w - q_items - k_items;
+                const int h = ww / nch, c = ww - h * nch;
+                float v[N];
+                Vec16<T>::load(vsrc + (size_t)h * hd + c * N, v);
+                Vec16<T>::store(vdst + (size_t)h * page_size * hd + cache_chunk(c, pos, nch) * N, v);
+            }
+        }
+        return;
+    }
+
+    // general pairing (interleaved, or only part of the head rotated): element by element
     for (int w = threadIdx.x; w < H * half; w += blockDim.x) {
         const int h = w / half, i = w - h * half;
         const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
@@ -105,37 +211,26 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
         x[a] = from_f32<T>(x1 * c - x2 * s);
         x[b] = from_f32<T>(x2 * c + x1 * s);
     }
-    if (!write_kv) return;
-
-    const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
-    if (page < 0 || page >= num_pages) {
-        if (threadIdx.x == 0) atomicExch(fault, 1);
-        return;
-    }
-    const int in_page = pos % page_size;
-    T* kdst = plane + ((size_t)page * 2 * KVH * page_size + in_page) * hd;      // + h*page_size*hd
-    T* vdst = kdst + (size_t)KVH * page_size * hd;
-    const T* ksrc = row + (size_t)H * hd;
-    const T* vsrc = ksrc + (size_t)KVH * hd;
+    if (page < 0) return;
     for (int w = threadIdx.x; w < KVH * half; w += blockDim.x) {
         const int h = w / half, i = w - h * half;
         const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
         const float x1 = to_f32(ksrc[h * hd + a]), x2 = to_f32(ksrc[h * hd + b]);
         const float c = cs[i], s = sn[i];
         T* o = kdst + (size_t)h * page_size * hd;
-        o[a] = from_f32<T>(x1 * c - x2 * s);
-        o[b] = from_f32<T>(x2 * c + x1 * s);
+        o[cache_chunk(a / N, pos, nch) * N + a % N] = from_f32<T>(x1 * c - x2 * s);
+        o[cache_chunk(b / N, pos, nch) * N + b % N] = from_f32<T>(x2 * c + x1 * s);
     }
     if (rot < hd) {
         const int rest = hd - rot;
         for (int w = threadIdx.x; w < KVH * rest; w += blockDim.x) {
             const int h = w / rest, i = rot + (w - h * rest);
-            kdst[(size_t)h * page_size * hd + i] = ksrc[h * hd + i];
+            kdst[(size_t)h * page_size * hd + cache_chunk(i / N, pos, nch) * N + i % N] = ksrc[h * hd + i];
         }
     }
     for (int w = threadIdx.x; w < KVH * hd; w += blockDim.x) {
         const int h = w / hd, i = w - h * hd;
-        vdst[(size_t)h * page_size * hd + i] = vsrc[w];
+        vdst[(size_t)h * page_size * hd + cache_chunk(i / N, pos, nch) * N + i % N] = vsrc[w];
     }
 }
 
@@ -146,6 +241,10 @@ TIS_API int tis_rope_kv_write(int dtype, void* qkv, int row_stride, const int* p
     if (n <= 0) return TIS_OK;
     if (rot % 2 || rot > hd || rot < 0) {
         tis_set_error("rope_kv_write: rotary size %d must be even and at most the head size %d", rot, hd);
+        return TIS_BAD_SIZE;
+    }
+    if (hd % 8) {
+        tis_set_error("rope_kv_write: head size %d must be a multiple of 8 (cache rows are stored in 16-byte chunks)", hd);
         return TIS_BAD_SIZE;
     }
     TIS_DISPATCH_DTYPE(dtype, T,
@@ -160,6 +259,23 @@ TIS_API int tis_rope_kv_write(int dtype, void* qkv, int row_stride, const int* p
 // ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    constexpr int N = Vec16<T>::N;
+    if (F % N == 0) {
+        const size_t nvec = total / N;
+        const int fv = F / N;
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec;
+             idx += (size_t)gridDim.x * blockDim.x) {
+            const size_t r = idx / fv;
+            const int j = (int)(idx - r * fv) * N;
+            float g[N], u[N], o[N];
+            Vec16<T>::load(gu + r * 2 * F + j, g);
+            Vec16<T>::load(gu + r * 2 * F + F + j, u);
+#pragma unroll
+            for (int k = 0; k < N; ++k) o[k] = g[k] / (1.f + expf(-g[k])) * u[k];
+            Vec16<T>::store(out + r * F + j, o);
+        }
+        return;
+    }
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / F;
@@ -173,7 +289,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     const size_t total = (size_t)n * F;
-    size_t blocks = (total + 255) / 256;
+    size_t blocks = (total / 4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
     if (blocks > 148 * 16) blocks = 148 * 16;
     TIS_DISPATCH_DTYPE(dtype, T,
         swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)out, F, total));

@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -40,9 +41,10 @@ class TileSet:
     64 // G rows (portions of prompts).  Each is (first rows, row counts, number of tiles);
     the first two are int32 device tensors."""
 
-    def __init__(self, keys, rows):
+    def __init__(self, keys, rows, keys_max_rows: int = 0):
         self.keys = keys
         self.rows = rows
+        self.keys_max_rows = keys_max_rows      # the most rows of any ``keys`` tile (0: not known)
 
 
 def plan_tiles(segments: Sequence[Tuple[int, int]], group_size: int):
@@ -104,12 +106,12 @@ class StepContext:
 @dataclass
 class StepLayout:
     """The per-step arrays as one flat list of int32 words, and where each array lies."""
-    flat: List[int]
+    flat: "np.ndarray"
     offsets: Dict[str, Tuple[int, int]]
     n: int
     segments: List[Segment]
     lags: List[int]
-    tile_counts: Dict[int, Tuple[int, int]]
+    tile_counts: Dict[int, Tuple[int, int, int]]
     n_want: int
     max_position: int
     decode_only: bool
@@ -118,63 +120,71 @@ class StepLayout:
 def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
                 pad_to: Optional[int] = None, group_sizes: Sequence[int] = (), want_all: bool = False,
                 max_position: Optional[int] = None) -> StepLayout:
-    """Lay the entries out as rows (host only).  ``starts[i]`` is the position of entry i's
-    first token.  ``pad_to``: add padding rows (slot -1) up to this many rows.  ``want_all``:
-    every row is wanted, padding included.  ``max_position``: an upper bound to plan key
-    splits with instead of the largest position of this step."""
-    tokens: List[int] = []
-    positions: List[int] = []
-    slots: List[int] = []
-    last: List[int] = []
+    """Lay the entries out as rows (host only, array arithmetic: no loop over tokens).
+    ``starts[i]`` is the position of entry i's first token.  ``pad_to``: add padding rows
+    (slot -1) up to this many rows.  ``want_all``: every row is wanted, padding included.
+    ``max_position``: an upper bound to plan key splits with instead of the largest position
+    of this step."""
+    tok_parts, pos_parts, slot_parts, last_parts = [], [], [], []
     want_rows: List[int] = []
     segments: List[Segment] = []
+    row0 = 0
     for e, start in zip(entries, starts):
-        k = len(e.tokens)
+        toks = np.asarray(e.tokens, dtype=np.int64)
+        k = int(toks.shape[0])
         if k == 0:
             raise ValueError(f"slot {e.slot}: an entry needs at least one token")
-        row0 = len(tokens)
-        for t in e.tokens:
-            if not (0 <= int(t) < vocab_size):
-                raise ValueError(f"slot {e.slot}: token id {t} outside the vocabulary (0..{vocab_size - 1})")
-        tokens += [int(t) for t in e.tokens]
-        positions += list(range(start, start + k))
-        slots += [e.slot] * k
-        last += [row0 + k - 1] * k
+        if toks.min() < 0 or toks.max() >= vocab_size:
+            bad = int(toks[(toks < 0) | (toks >= vocab_size)][0])
+            raise ValueError(f"slot {e.slot}: token id {bad} outside the vocabulary (0..{vocab_size - 1})")
+        tok_parts.append(toks.astype(np.int32))
+        pos_parts.append(np.arange(start, start + k, dtype=np.int32))
+        slot_parts.append(np.full(k, e.slot, dtype=np.int32))
+        last_parts.append(np.full(k, row0 + k - 1, dtype=np.int32))
         for w in e.want:
             if not (0 <= int(w) < k):
                 raise ValueError(f"slot {e.slot}: wanted place {w} outside its {k} tokens")
             want_rows.append(row0 + int(w))
         segments.append(Segment(e.slot, row0, k, start))
-    n_real = len(tokens)
+        row0 += k
+    n_real = row0
     n = n_real
     seg_rows = [(s.row0, s.rows) for s in segments]
     if pad_to is not None and pad_to > n:
         pad = pad_to - n
-        tokens += [0] * pad
-        positions += [0] * pad
-        slots += [-1] * pad
-        last += list(range(n, n + pad))
+        tok_parts.append(np.zeros(pad, dtype=np.int32))
+        pos_parts.append(np.zeros(pad, dtype=np.int32))
+        slot_parts.append(np.full(pad, -1, dtype=np.int32))
+        last_parts.append(np.arange(n, n + pad, dtype=np.int32))
         seg_rows += [(r, 1) for r in range(n, n + pad)]
         n = pad_to
+    tokens = np.concatenate(tok_parts)
+    positions = np.concatenate(pos_parts)
+    slots = np.concatenate(slot_parts)
+    last = np.concatenate(last_parts)
     lags = [l for l in sorted(set(lags)) if l > 0]
-    flat: List[int] = []
+    parts: List[np.ndarray] = []
     offsets: Dict[str, Tuple[int, int]] = {}
+    cursor = 0
 
     def put(name, values):
-        offsets[name] = (len(flat), len(values))
-        flat.extend(values)
+        nonlocal cursor
+        arr = np.asarray(values, dtype=np.int32).reshape(-1)
+        offsets[name] = (cursor, int(arr.shape[0]))
+        parts.append(arr)
+        cursor += int(arr.shape[0])
 
     put("tokens", tokens)
     put("positions", positions)
     put("slots", slots)
     put("last", last)
     for lag in lags:
-        put(f"pos{lag}", [max(0, p - lag) for p in positions])
-        put(f"slot{lag}", [s if p - lag >= 0 else -1 for s, p in zip(slots, positions)])
+        put(f"pos{lag}", np.maximum(positions - lag, 0))
+        put(f"slot{lag}", np.where(positions - lag >= 0, slots, -1))
     counts = {}
     for g in sorted(set(group_sizes)):
         keys, rows = plan_tiles(seg_rows, g)
-        counts[g] = (len(keys), len(rows))
+        counts[g] = (len(keys), len(rows), max((t[1] for t in keys), default=0))
         put(f"k0_{g}", [t[0] for t in keys])
         put(f"kn_{g}", [t[1] for t in keys])
         put(f"r0_{g}", [t[0] for t in rows])
@@ -182,9 +192,10 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
     if want_all:
         want_rows = list(range(n))
     put("want", want_rows)
-    max_pos = max(positions[:n_real]) if n_real else 0
+    max_pos = int(positions[:n_real].max()) if n_real else 0
     if max_position is not None:
         max_pos = max(max_pos, max_position)
+    flat = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
     return StepLayout(flat, offsets, n, segments, lags, counts, len(want_rows), max_pos,
                       all(s.rows == 1 for s in segments))
 
@@ -197,8 +208,8 @@ def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[t
         a, k = lay.offsets[name]
         return dev[a:a + k]
 
-    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr))
-             for g, (nk, nr) in lay.tile_counts.items()}
+    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr), kmax)
+             for g, (nk, nr, kmax) in lay.tile_counts.items()}
     stages: Dict[int, StepContext] = {}
     ctx = StepContext(lay.n, view("tokens"), view("positions"), view("slots"), view("last"), lay.segments,
                       block_tables, page_sizes, fault, lay.max_position, stages=stages,
@@ -219,7 +230,7 @@ def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequen
     """Rows, metadata and context of one step; all per-step arrays go to the device in one
     copy.  Returns the context, the device indices of the wanted rows, and their count."""
     lay = layout_step(entries, starts, lags, vocab_size, pad_to=pad_to, group_sizes=group_sizes)
-    dev = torch.tensor(lay.flat, dtype=torch.int32).to(device, non_blocking=True)
+    dev = torch.from_numpy(lay.flat).to(device, non_blocking=True)
     ctx, want = context_from_layout(lay, dev, block_tables, page_sizes, fault)
     return ctx, want, lay.n_want
 
@@ -243,7 +254,7 @@ class StaticMeta:
         self.layout: Optional[Dict[str, Tuple[int, int]]] = None
         self.used = 0
 
-    def upload(self, flat: List[int], offsets: Dict[str, Tuple[int, int]]) -> torch.Tensor:
+    def upload(self, flat, offsets: Dict[str, Tuple[int, int]]) -> torch.Tensor:
         if len(flat) > self.dev.numel():
             raise ValueError(f"step metadata of {len(flat)} words exceeds the static buffer ({self.dev.numel()})")
         if self.layout is None:
@@ -256,7 +267,7 @@ class StaticMeta:
         if self.recorded[i]:
             self.events[i].synchronize()
         host = self.hosts[i]
-        host[: self.used] = torch.tensor(flat, dtype=torch.int32)
+        host[: self.used] = torch.from_numpy(flat)
         self.dev[: self.used].copy_(host[: self.used], non_blocking=True)
         if self.events[i] is not None:
             self.events[i].record()
@@ -282,4 +293,5 @@ def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int
         return torch.tensor(v, dtype=torch.int32, device=dev)
 
     return TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
-                   (t([k[0] for k in rows]), t([k[1] for k in rows]), len(rows)))
+                   (t([k[0] for k in rows]), t([k[1] for k in rows]), len(rows)),
+                   max((k[1] for k in keys), default=0))

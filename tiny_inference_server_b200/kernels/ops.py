@@ -146,6 +146,18 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Te
 
 
 _attn_libs = {}
+_attn_counters = {}
+
+
+def _counters(device, need: int):
+    """Zeroed counters for the split-key merge (per tile and kv head); the kernel leaves them
+    zero again.  None when a launch needs more than are kept (it then merges in a second kernel)."""
+    if need > (1 << 16):
+        return None
+    t = _attn_counters.get(device)
+    if t is None:
+        t = _attn_counters[device] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return t
 
 
 def attention_library(head_dim: int):
@@ -156,29 +168,43 @@ def attention_library(head_dim: int):
         lib = ctypes.CDLL(_build.build_attention(head_dim))
         lib.tis_last_error.restype = ctypes.c_char_p
         lib.tis_attn_scratch_floats.restype = ctypes.c_size_t
+        lib.resident = {}
         if lib.tis_attn_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.tis_attn_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
     return lib
 
 
-#: CTAs that the key splits of the attention kernels aim for (148 SMs, two to three CTAs each)
-ATTN_TARGET_CTAS = 148 * 3
+#: CTAs of the attention kernels that are resident at a time when the library cannot be asked
+#: (148 SMs, two CTAs each at head size 128)
+ATTN_RESIDENT_CTAS = 148 * 2
+#: cost of starting and finishing a CTA, and of merging one more split, in units of one 64-key tile
+ATTN_CTA_OVERHEAD_TILES = 8.0
+ATTN_MERGE_PER_SPLIT_TILES = 0.1
 
 
-def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool):
-    """(keys per split, number of splits): split the keys of long contexts over CTAs while
-    tiles x kv heads alone would leave SMs idle.  Splits are multiples of 64 keys."""
+def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, resident: int = ATTN_RESIDENT_CTAS):
+    """(keys per split, number of splits) for contexts of up to ``max_kv`` keys.
+
+    One CTA walks the keys of one (tile, kv head, split), 64 at a time.  With few tiles the
+    SMs idle unless the keys are split; with too many splits every CTA is all overhead, and
+    one CTA more than fit the GPU at a time costs a whole second round.  The number of
+    splits minimises  rounds x (overhead + tiles per split) + merge cost."""
     base = max(1, num_tiles * kv_heads)
-    max_splits = max(1, (max_kv + 63) // 64)
-    want = 1 if base >= ATTN_TARGET_CTAS else (ATTN_TARGET_CTAS + base - 1) // base
-    if not mode_keys:
-        want = min(want, 8)
-    splits = max(1, min(want, max_splits))
-    per = ((max_kv + splits - 1) // splits + 63) // 64 * 64
-    per = max(64, per)
-    splits = max(1, (max_kv + per - 1) // per)
-    return per, splits
+    total_tiles = max(1, (max_kv + 63) // 64)
+    best, best_cost = 1, None
+    limit = total_tiles if mode_keys else min(total_tiles, 8)
+    for s in range(1, limit + 1):
+        per_tiles = (total_tiles + s - 1) // s
+        real = (total_tiles + per_tiles - 1) // per_tiles      # splits that per_tiles gives
+        if real != s:
+            continue
+        rounds = (base * s + resident - 1) // resident
+        cost = rounds * (ATTN_CTA_OVERHEAD_TILES + per_tiles) + (ATTN_MERGE_PER_SPLIT_TILES * s if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    per = ((total_tiles + best - 1) // best) * 64
+    return per, max(1, (max_kv + per - 1) // per)
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor,
@@ -216,15 +242,21 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     for mode, (row0, rows, count) in ((1, tiles.keys), (0, tiles.rows)):
         if count == 0:
             continue
-        per, splits = plan_splits(count, kv_heads, max_kv, mode == 1)
+        max_rows = tiles.keys_max_rows if mode == 1 else 0
+        half = int(mode == 1 and 0 < max_rows * g <= 8)
+        resident = alib.resident.get((mode, half))
+        if resident is None:
+            resident = alib.resident[(mode, half)] = alib.tis_attn_resident_ctas(mode, half)
+        per, splits = plan_splits(count, kv_heads, max_kv, mode == 1, resident)
         scratch = None
         if splits > 1:
             need = alib.tis_attn_scratch_floats(n, num_heads, splits)
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         _check(alib.tis_attn_mma(mode, _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
                                  block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
-                                 _p(rows), count, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
-                                 per, splits, _p(scratch), _p(fault), _stream()), alib)
+                                 _p(rows), count, max_rows, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
+                                 per, splits, _p(scratch), _p(_counters(q.device, count * kv_heads) if splits > 1 else None),
+                                 _p(fault), _stream()), alib)
     return out
 
 
