@@ -145,12 +145,19 @@ def paged_attention(q, out, plane, block_table, positions, row_slot, num_heads, 
     return out
 
 
-def swiglu(gu, out):
+def swiglu(gu, out, block=None):
     f = out.shape[1]
-    g = gu[:, :f].to(torch.float32)
-    u = gu[:, f:].to(torch.float32)
+    block = block or f
+    both = gu.to(torch.float32).reshape(gu.shape[0], f // block, 2, block)
+    g = both[:, :, 0, :].reshape(-1, f)
+    u = both[:, :, 1, :].reshape(-1, f)
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
     return out
+
+
+def gemm_swiglu(a, w_gu, hidden, block):
+    gu = gemm(a, w_gu)
+    return swiglu(gu, torch.empty((a.shape[0], hidden), dtype=a.dtype), block)
 
 
 def mtp_input(h_prev, state, row_slot, row_last, tokens, table, scale, eps, out):
@@ -254,7 +261,7 @@ def bitmap_set(bitmap_row, tokens):
         bitmap_row[t >> 5] = w - (1 << 32) if w >= (1 << 31) else w
 
 
-_NAMES = ["gemm", "gemm_f32_out", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
+_NAMES = ["gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set"]
 
 

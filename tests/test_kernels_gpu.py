@@ -75,14 +75,53 @@ def test_add_rmsnorm_eps_is_added_to_the_norm():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,F", [(3, 200), (17, 4096), (1, 10)])
-def test_swiglu(dtype, n, F):
+@pytest.mark.parametrize("n,F,block", [(3, 200, None), (17, 4096, None), (1, 10, None), (5, 352, 32), (9, 200, 5)])
+def test_swiglu(dtype, n, F, block):
     ops = _ops()
     g = torch.Generator().manual_seed(2)
     gu = _rand((n, 2 * F), dtype, g, 2.0)
-    want = ref.swiglu(gu, torch.empty(n, F, dtype=dtype))
-    got = ops.swiglu(gu.cuda(), torch.empty(n, F, dtype=dtype, device="cuda"))
+    want = ref.swiglu(gu, torch.empty(n, F, dtype=dtype), block)
+    got = ops.swiglu(gu.cuda(), torch.empty(n, F, dtype=dtype, device="cuda"), block)
     torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("n", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("K,N", [(1536, 2304), (128, 64), (200, 120), (4096, 1536), (72, 8), (1000, 1096)])
+def test_skinny_gemm(n, K, N):
+    """The weight-streaming product for few rows, for every split of K over a cluster."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(12)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, N), torch.bfloat16, g, 0.05)
+    want = (a.double() @ w.double())
+    for ksplit in (None, 1, 2, 4, 8):
+        got = ops.gemm_skinny(a.cuda(), w.cuda(), ksplit=ksplit)
+        assert got.shape == (n, N) and got.dtype == torch.bfloat16
+        torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    # a weight matrix that is a column slice of a wider one (row stride larger than its width)
+    wide = _rand((K, N + 64), torch.bfloat16, g, 0.05).cuda()
+    got = ops.gemm_skinny(a.cuda(), wide[:, :N])
+    torch.testing.assert_close(got.cpu().double(), a.double() @ wide[:, :N].cpu().double(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n", [1, 8, 40, 64])
+@pytest.mark.parametrize("K,F", [(1536, 4096), (120, 352), (64, 32)])
+def test_skinny_gemm_with_swiglu_epilogue(n, K, F):
+    ops = _ops()
+    g = torch.Generator().manual_seed(13)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, 2 * F), torch.bfloat16, g, 0.05)
+    gu = (a.double() @ w.double()).reshape(n, F // 32, 2, 32)
+    want = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(n, F)
+    got = ops.gemm_swiglu(a.cuda(), w.cuda(), F, 32)
+    assert got.shape == (n, F)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    # more rows than the kernel takes: the library product and the gating kernel, same result
+    if n == 64:
+        a2 = _rand((80, K), torch.bfloat16, g)
+        gu2 = (a2.double() @ w.double()).reshape(80, F // 32, 2, 32)
+        want2 = (torch.nn.functional.silu(gu2[:, :, 0]) * gu2[:, :, 1]).reshape(80, F)
+        torch.testing.assert_close(ops.gemm_swiglu(a2.cuda(), w.cuda(), F, 32).cpu().double(), want2, rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

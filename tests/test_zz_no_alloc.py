@@ -69,12 +69,12 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice(H, KVH, hd, page, le
         assert _call(lib, "tis_attn_mma", q, want, plane, table, positions, row_slot, tiles0, tilesn, H, KVH, page,
                      per, nsplit, scratch, fault) == 0
         got = torch.full((n, H * hd), -3.0, dtype=torch.bfloat16, device=dev)
-        before = torch.cuda.memory_allocated()
+        before = torch.cuda.memory_stats()["allocation.all.allocated"]      # allocations made so far
         status = _call(lib, "tis_attn_decode_noalloc", q, got, plane, table, positions, row_slot, tiles0, tilesn, H,
                        KVH, page, per, nsplit, None, fault)
         assert status == 0, lib.tis_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
         assert int(fault[0]) == 0
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         # and both agree with the plain reference of the operation

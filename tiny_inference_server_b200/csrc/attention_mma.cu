@@ -186,6 +186,8 @@ attn_mma_kernel(const AttnParams p) {
     __shared__ int sh_first;
     __shared__ __align__(8) unsigned long long bars[STAGES];
 
+    pdl_launch_dependents();         // tiles, slots, positions and block tables below are step metadata,
+                                     // not written by the kernel before; pdl_wait() comes before q and the cache
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g_lane = lane >> 2, t_lane = lane & 3;
@@ -239,6 +241,7 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    pdl_wait();
 
     if (!empty) {
         // query fragments straight from global memory: a0 (row g, k 2t..), a1 (row g+8), a2 (row g, k 2t+8..), a3
@@ -649,11 +652,11 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         configured = true;
     }
     if (mode == MODE_ROWS) {
-        attn_mma_kernel<MODE_ROWS, 2><<<grid, NTHREADS, smem, stream>>>(p);
+        tis_launch(attn_mma_kernel<MODE_ROWS, 2>, grid, dim3(NTHREADS), smem, stream, p);
     } else if (max_tile_rows > 0 && max_tile_rows * G <= 8) {
-        attn_mma_kernel<MODE_KEYS, 1><<<grid, NTHREADS, smem, stream>>>(p);
+        tis_launch(attn_mma_kernel<MODE_KEYS, 1>, grid, dim3(NTHREADS), smem, stream, p);
     } else {
-        attn_mma_kernel<MODE_KEYS, 2><<<grid, NTHREADS, smem, stream>>>(p);
+        tis_launch(attn_mma_kernel<MODE_KEYS, 2>, grid, dim3(NTHREADS), smem, stream, p);
     }
     int st = tis_check_launch("attn_mma");
     if (st != TIS_OK) return st;

@@ -106,6 +106,34 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return t;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------
+// Kernels of a step form a chain, each reading what the one before wrote.  Launched with the
+// attribute below a kernel may start while the kernel before it still runs: it tells the
+// hardware at once that the kernel after it may start too (pdl_launch_dependents), does what
+// does not depend on the kernel before (metadata, weights), and then waits for it (pdl_wait)
+// before it reads or writes anything else.  Inside a CUDA graph the launches become
+// programmatic edges.  TIS_NO_PDL=1 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+bool tis_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tis_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Dispatch on the storage dtype inside a launcher.
 #define TIS_DISPATCH_DTYPE(dtype, T, ...)                                   \
     do {                                                                    \

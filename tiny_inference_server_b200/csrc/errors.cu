@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 static thread_local char g_err[512] = "";
 
@@ -23,6 +24,14 @@ int tis_check_launch(const char* what) {
 
 TIS_API const char* tis_last_error() { return g_err; }
 
+bool tis_pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("TIS_NO_PDL");
+        return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+    }();
+    return on;
+}
+
 // Version of the launcher interface; the Python side refuses a library built from
 // other sources than its own.
-TIS_API int tis_abi_version() { return 1; }
+TIS_API int tis_abi_version() { return 2; }

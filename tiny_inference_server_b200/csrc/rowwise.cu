@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const T* src = table + (size_t)tokens[r] * d;
     float* dst = out + (size_t)r * d;
@@ -32,7 +34,7 @@ TIS_API int tis_embed_rows(int dtype, const void* table, const int* tokens, floa
                            cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
     TIS_DISPATCH_DTYPE(dtype, T,
-        embed_rows_kernel<T><<<n, 256, 0, stream>>>((const T*)table, tokens, out, d));
+        tis_launch(embed_rows_kernel<T>, dim3(n), dim3(256), 0, stream, (const T*)table, tokens, out, d));
     return tis_check_launch("embed_rows");
 }
 
@@ -45,6 +47,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ res, const T* __restrict_
                                    const float* __restrict__ scale, float eps, T* __restrict__ out, int d) {
     extern __shared__ float row[];
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * d;
     constexpr int N = Vec16<T>::N;
     const bool vec = (d % N == 0);
@@ -107,7 +111,8 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
     TIS_DISPATCH_DTYPE(dtype, T, {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<T><<<n, threads, smem, stream>>>(residual, (const T*)delta, scale, eps, (T*)out, d);
+        tis_launch(add_rmsnorm_kernel<T>, dim3(n), dim3(threads), smem, stream, residual, (const T*)delta, scale, eps,
+                   (T*)out, d);
     });
     return tis_check_launch("add_rmsnorm");
 }
@@ -130,10 +135,12 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const int* __restrict__ block_table, int bt_stride, int num_pages,
                                      int H, int KVH, int hd, int rot, int interleaved, int page_size,
                                      int write_kv, int* __restrict__ fault) {
+    pdl_launch_dependents();
     const int r = blockIdx.x;
-    const int slot = row_slot[r];
+    const int slot = row_slot[r];              // step metadata: not written by the kernel before
     if (slot < 0) return;
     const int pos = positions[r];
+    pdl_wait();
     T* row = qkv + (size_t)r * row_stride;
     const int half = rot >> 1;
     const float* cs = cos_t + (size_t)pos * half;
@@ -248,28 +255,34 @@ TIS_API int tis_rope_kv_write(int dtype, void* qkv, int row_stride, const int* p
         return TIS_BAD_SIZE;
     }
     TIS_DISPATCH_DTYPE(dtype, T,
-        rope_kv_write_kernel<T><<<n, 256, 0, stream>>>((T*)qkv, row_stride, positions, row_slot, cos_t, sin_t,
-                                                        (T*)plane, block_table, bt_stride, num_pages, H, KVH, hd,
-                                                        rot, interleaved, page_size, write_kv, fault));
+        tis_launch(rope_kv_write_kernel<T>, dim3(n), dim3(256), 0, stream, (T*)qkv, row_stride, positions, row_slot,
+                   cos_t, sin_t, (T*)plane, block_table, bt_stride, num_pages, H, KVH, hd, rot, interleaved, page_size,
+                   write_kv, fault));
     return tis_check_launch("rope_kv_write");
 }
 
 // ----------------------------------------------------------------------------------
-// SwiGLU gating: out[r, j] = silu(gu[r, j]) * gu[r, F + j]   (main_models_new.py:51)
+// SwiGLU gating: out[r, j] = silu(gate_j) * up_j   (main_models_new.py:51).  The input row
+// holds gate and up in alternating blocks of `block` columns: [gate 0..b-1 | up 0..b-1 |
+// gate b..2b-1 | ...]; block = F is the plain layout [all gates | all ups].
 // ----------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, int block, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int N = Vec16<T>::N;
-    if (F % N == 0) {
+    if (block % N == 0) {
         const size_t nvec = total / N;
         const int fv = F / N;
         for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec;
              idx += (size_t)gridDim.x * blockDim.x) {
             const size_t r = idx / fv;
             const int j = (int)(idx - r * fv) * N;
+            const int b = j / block;
+            const T* src = gu + r * 2 * F + (size_t)b * 2 * block + (j - b * block);
             float g[N], u[N], o[N];
-            Vec16<T>::load(gu + r * 2 * F + j, g);
-            Vec16<T>::load(gu + r * 2 * F + F + j, u);
+            Vec16<T>::load(src, g);
+            Vec16<T>::load(src + block, u);
 #pragma unroll
             for (int k = 0; k < N; ++k) o[k] = g[k] / (1.f + expf(-g[k])) * u[k];
             Vec16<T>::store(out + r * F + j, o);
@@ -280,20 +293,27 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t r = idx / F;
         const int j = (int)(idx - r * F);
-        const float g = to_f32(gu[r * 2 * F + j]);
-        const float u = to_f32(gu[r * 2 * F + F + j]);
+        const int b = j / block;
+        const T* src = gu + r * 2 * F + (size_t)b * 2 * block + (j - b * block);
+        const float g = to_f32(src[0]);
+        const float u = to_f32(src[block]);
         out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, cudaStream_t stream) {
+TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, int block, cudaStream_t stream) {
     if (n <= 0) return TIS_OK;
+    if (block <= 0 || F % block) {
+        tis_set_error("swiglu: block %d does not divide the hidden size %d", block, F);
+        return TIS_BAD_SIZE;
+    }
     const size_t total = (size_t)n * F;
     size_t blocks = (total / 4 + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 16) blocks = 148 * 16;
     TIS_DISPATCH_DTYPE(dtype, T,
-        swiglu_kernel<T><<<(int)blocks, 256, 0, stream>>>((const T*)gu, (T*)out, F, total));
+        tis_launch(swiglu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, F, block,
+                   total));
     return tis_check_launch("swiglu");
 }
 
@@ -302,6 +322,8 @@ TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, cudaS
 // ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ res, const T* __restrict__ delta, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x)
         res[idx] += to_f32(delta[idx]);
@@ -313,7 +335,8 @@ TIS_API int tis_residual_add(int dtype, float* residual, const void* delta, int 
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     TIS_DISPATCH_DTYPE(dtype, T,
-        residual_add_kernel<T><<<(int)blocks, 256, 0, stream>>>(residual, (const T*)delta, total));
+        tis_launch(residual_add_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, residual, (const T*)delta,
+                   total));
     return tis_check_launch("residual_add");
 }
 
@@ -330,6 +353,8 @@ __global__ void mtp_input_kernel(const T* __restrict__ h_prev, T* __restrict__ s
                                  const float* __restrict__ scale, float eps, T* __restrict__ out, int d) {
     extern __shared__ float row[];
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int slot = row_slot[r];
     if (slot < 0) return;
@@ -370,8 +395,8 @@ TIS_API int tis_mtp_input(int dtype, const void* h_prev, void* state, const int*
     TIS_DISPATCH_DTYPE(dtype, T, {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(mtp_input_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mtp_input_kernel<T><<<n, 256, smem, stream>>>((const T*)h_prev, (T*)state, row_slot, row_last, tokens,
-                                                       (const T*)table, scale, eps, (T*)out, d);
+        tis_launch(mtp_input_kernel<T>, dim3(n), dim3(256), smem, stream, (const T*)h_prev, (T*)state, row_slot,
+                   row_last, tokens, (const T*)table, scale, eps, (T*)out, d);
     });
     return tis_check_launch("mtp_input");
 }

@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 1
+ABI_VERSION = 2
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 
@@ -83,13 +83,63 @@ def _f(x: float):
 # main_models_new.py:20,29,226)
 # ---------------------------------------------------------------------------------------
 
+#: rows up to which bfloat16 products go to the weight-streaming kernel instead of the library
+SKINNY_MAX_ROWS = 16
+EPI_STORE, EPI_SWIGLU = 0, 1
+
+
+def _skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < a.shape[0] <= SKINNY_MAX_ROWS
+            and w.stride(1) == 1 and a.stride(1) == 1 and a.shape[1] % 8 == 0 and w.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def _ksplit(n_cols: int, k: int) -> int:
+    """CTAs that share a 64-column strip of the weights (a cluster adding up over K): as many as
+    keep the grid near two CTAs per SM, each with at least 128 rows of K."""
+    strips = (n_cols + 63) // 64
+    ks = 8
+    while ks > 1 and (strips * ks > 2 * 148 * 2 or k // ks < 128):
+        ks //= 2
+    return ks
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                ksplit: Optional[int] = None) -> torch.Tensor:
+    """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by the weight-streaming kernel; with ``swiglu``
+    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    lib = library()
+    n, k = a.shape
+    cols = w.shape[1]
+    if out is None:
+        out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    _check(lib.tis_gemm_skinny(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                               ksplit or _ksplit(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _stream()), lib)
+    return out
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32."""
+    """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Up to 64
+    bfloat16 rows go to the weight-streaming kernel of this library, everything else to the
+    library product."""
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
+    if _skinny_ok(a, w):
+        return gemm_skinny(a, w, out)
     if out is None:
         return torch.mm(a, w)
     return torch.mm(a, w, out=out)
+
+
+def gemm_swiglu(a: torch.Tensor, w_gu: torch.Tensor, hidden: int, block: int) -> torch.Tensor:
+    """``swiglu(a @ w_gu)``: (n, hidden).  ``w_gu`` (K, 2*hidden) holds gate and up columns in
+    alternating blocks of ``block``.  Few bfloat16 rows with block 32: one kernel with the
+    gating in its epilogue; else the product and the gating kernel."""
+    if block == 32 and _skinny_ok(a, w_gu):
+        return gemm_skinny(a, w_gu, swiglu=True)
+    gu = torch.mm(a, w_gu)
+    out = torch.empty((a.shape[0], hidden), dtype=a.dtype, device=a.device)
+    return swiglu(gu, out, block)
 
 
 def gemm_f32_out(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -260,11 +310,12 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     return out
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[r, j] = silu(gu[r, j]) * gu[r, F + j]."""
+def swiglu(gu: torch.Tensor, out: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
+    """out[r, j] = silu(gate_j) * up_j where a row of ``gu`` holds gate and up columns in
+    alternating blocks of ``block`` (default: the hidden size, i.e. [all gates | all ups])."""
     lib = library()
     n, f = out.shape
-    _check(lib.tis_swiglu(_dt(gu), _p(gu), _p(out), n, f, _stream()), lib)
+    _check(lib.tis_swiglu(_dt(gu), _p(gu), _p(out), n, f, block or f, _stream()), lib)
     return out
 
 

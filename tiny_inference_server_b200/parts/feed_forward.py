@@ -13,7 +13,10 @@ from .base import BuildContext, FeedForward, WeightSpec
 class SwiGLU(FeedForward):
     """``(silu(x W1) * (x W2)) W3`` (upstream ``swiglu`` and ``ffn_router``,
     main_models_new.py:44-60); weights ``(in, out)``: W1 gate and W2 up ``(width, hidden)``,
-    W3 ``(hidden, width)``.  On the device gate and up are one matrix ``(width, 2*hidden)``."""
+    W3 ``(hidden, width)``.  On the device gate and up are one matrix ``(width, 2*hidden)``
+    whose columns alternate in blocks of 32 gates and 32 ups (when 32 divides the hidden size;
+    else all gates, then all ups), so that one 64-column strip of the product holds both
+    factors of 32 outputs and the gating can be the product's epilogue."""
 
     def __init__(self, width: int, hidden: int, prefix: str = "", names: Optional[Dict[str, str]] = None):
         super().__init__(prefix)
@@ -24,6 +27,7 @@ class SwiGLU(FeedForward):
             self.names.update(names)
         self.w_gate_up = None
         self.w_down = None
+        self.block = hidden
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {
@@ -35,13 +39,14 @@ class SwiGLU(FeedForward):
     def load(self, tensors, ctx: BuildContext) -> None:
         gate = tensors[self.prefix + self.names["gate"]]
         up = tensors[self.prefix + self.names["up"]]
-        self.w_gate_up = torch.cat([gate, up], dim=1).to(device=ctx.device, dtype=ctx.dtype).contiguous()
+        self.block = 32 if self.hidden % 32 == 0 else self.hidden
+        nb = self.hidden // self.block
+        both = torch.stack([gate.reshape(self.width, nb, self.block), up.reshape(self.width, nb, self.block)], dim=2)
+        self.w_gate_up = both.reshape(self.width, 2 * self.hidden).to(device=ctx.device, dtype=ctx.dtype).contiguous()
         self.w_down = tensors[self.prefix + self.names["down"]].to(device=ctx.device, dtype=ctx.dtype).contiguous()
 
     def forward(self, x: torch.Tensor, step=None) -> torch.Tensor:
-        gu = ops.gemm(x, self.w_gate_up)
-        h = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
-        ops.swiglu(gu, h)
+        h = ops.gemm_swiglu(x, self.w_gate_up, self.hidden, self.block)
         return ops.gemm(h, self.w_down)
 
 
