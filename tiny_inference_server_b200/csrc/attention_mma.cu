@@ -26,6 +26,7 @@
 // to scratch memory; the split that finishes last (a counter per tile and kv head) merges
 // them, or, when the caller gives no counters, `attn_merge_kernel` does.
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 #ifndef TIS_HD
 #error "compile with -DTIS_HD=<head size>"
@@ -62,6 +63,8 @@ struct AttnParams {
     int keys_per_split, num_splits;
     float* part_o; float* part_lse;
     int* counters;          // per (tile, kv head): splits that have finished; null: merge in a kernel of its own
+    int cluster_merge;      // the splits of a (tile, kv head) are one thread-block cluster and merge through
+                            // distributed shared memory: no scratch, no counters (keys mode, 2..8 splits)
     int* fault;
 };
 
@@ -241,6 +244,11 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // block table and the first page ids are step metadata too: fetch them before the wait
+    const int* bt = p.block_table + (size_t)(slot >= 0 ? slot : 0) * p.bt_stride;
+    const int kt0 = (range_lo / KT) * KT;
+    const int ntiles = empty ? 0 : (range_hi - kt0 + KT - 1) / KT;
+    int page = empty ? -1 : fetch_page(p, bt, kt0, range_hi, tid);
     pdl_wait();
 
     if (!empty) {
@@ -260,14 +268,10 @@ attn_mma_kernel(const AttnParams p) {
                 qa[kk][2 + i] = w1;
             }
         }
-        const int* bt = p.block_table + (size_t)slot * p.bt_stride;
-        const int kt0 = (range_lo / KT) * KT;
-        const int ntiles = (range_hi - kt0 + KT - 1) / KT;
         constexpr int STAGE_ELEMS = 2 * KT * RS;
 
         // prologue: order STAGES-1 tiles; the page id a thread needs for the tile after is
         // fetched one tile ahead, so its latency is off the path
-        int page = fetch_page(p, bt, kt0, range_hi, tid);
 #pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
             if (st < ntiles) {
@@ -439,11 +443,46 @@ attn_mma_kernel(const AttnParams p) {
             const float val = lt > 0.f ? acc / lt : 0.f;
             if (p.num_splits == 1) {
                 p.out[(size_t)row * p.out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(val);
+            } else if (p.cluster_merge) {
+                float* cm_o = ml + 4 * 16;                       // [16][HD] this split's normalised output
+                float* cm_lse = cm_o + 16 * HD;                  // [16]
+                cm_o[m * HD + d] = val;
+                if (d == 0) cm_lse[m] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
             } else {
                 const size_t pr = ((size_t)row * p.H + hq) * p.num_splits + split;
                 p.part_o[pr * HD + d] = val;
                 if (d == 0) p.part_lse[pr] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
             }
+        }
+        if (p.num_splits > 1 && p.cluster_merge) {
+            // the splits of this (tile, kv head) are the CTAs of one cluster: every CTA merges its
+            // share of the outputs, reading all splits' results from their shared memory
+            namespace cg = cooperative_groups;
+            cg::cluster_group cluster = cg::this_cluster();
+            float* cm_o = ml + 4 * 16;
+            float* cm_lse = cm_o + 16 * HD;
+            cluster.sync();
+            const int ns = p.num_splits;
+            const int pairs = rows * G;
+            for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
+                const int m = idx / HD, d = idx - m * HD;
+                const int r = m / G, g = m - r * G;
+                float mt = -INFINITY;
+                for (int sp = 0; sp < ns; ++sp) mt = fmaxf(mt, cluster.map_shared_rank(cm_lse, sp)[m]);
+                float acc = 0.f, wsum = 0.f;
+                if (mt != -INFINITY) {
+                    for (int sp = 0; sp < ns; ++sp) {
+                        const float l = cluster.map_shared_rank(cm_lse, sp)[m];
+                        if (l == -INFINITY) continue;
+                        const float w = fast_exp2(l - mt);
+                        wsum += w;
+                        acc += w * cluster.map_shared_rank(cm_o, sp)[m * HD + d];
+                    }
+                }
+                p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
+                    __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+            }
+            cluster.sync();              // nobody leaves while its shared memory may still be read
         }
     } else {
 #pragma unroll
@@ -471,7 +510,7 @@ attn_mma_kernel(const AttnParams p) {
     }
 
     // ---- the split that finishes last merges all partial results of this (tile, kv head)
-    if (p.num_splits > 1 && p.counters != nullptr) {
+    if (p.num_splits > 1 && p.counters != nullptr && !p.cluster_merge) {
         __shared__ int sh_last;
         __threadfence();
         __syncthreads();
@@ -564,7 +603,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 static size_t smem_bytes(int mode) {
     size_t stage = (size_t)STAGES * STAGE_BYTES;
-    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16) * sizeof(float) : 0;
+    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float) : 0;
     return stage > merge ? stage : merge;
 }
 
@@ -624,7 +663,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         tis_set_error("attention: %d kv heads or %d splits exceed the grid", KVH, num_splits);
         return TIS_BAD_SIZE;
     }
-    if (num_splits > 1 && scratch == nullptr) {
+    if (num_splits > 1 && scratch == nullptr && !(mode == MODE_KEYS && num_splits <= 8)) {
         tis_set_error("attention: %d key splits need scratch memory", num_splits);
         return TIS_BAD_SIZE;
     }
@@ -638,6 +677,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.part_o = scratch;
     p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
     p.counters = num_splits > 1 ? counters : nullptr;
+    p.cluster_merge = (mode == MODE_KEYS && num_splits > 1 && num_splits <= 8) ? 1 : 0;
     p.fault = fault;
     const size_t smem = smem_bytes(mode);
     dim3 grid(num_tiles, KVH, num_splits);
@@ -653,14 +693,35 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     }
     if (mode == MODE_ROWS) {
         tis_launch(attn_mma_kernel<MODE_ROWS, 2>, grid, dim3(NTHREADS), smem, stream, p);
-    } else if (max_tile_rows > 0 && max_tile_rows * G <= 8) {
-        tis_launch(attn_mma_kernel<MODE_KEYS, 1>, grid, dim3(NTHREADS), smem, stream, p);
     } else {
-        tis_launch(attn_mma_kernel<MODE_KEYS, 2>, grid, dim3(NTHREADS), smem, stream, p);
+        // keys mode: with 2..8 splits the splits of a (tile, kv head) form a cluster
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(NTHREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attrs[2];
+        int na = 0;
+        if (p.cluster_merge) {
+            attrs[na].id = cudaLaunchAttributeClusterDimension;
+            attrs[na].val.clusterDim.x = 1;
+            attrs[na].val.clusterDim.y = 1;
+            attrs[na].val.clusterDim.z = num_splits;
+            ++na;
+        }
+        if (tis_pdl_enabled()) {
+            attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        cfg.attrs = attrs;
+        cfg.numAttrs = na;
+        if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1>, p);
+        else cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2>, p);
     }
     int st = tis_check_launch("attn_mma");
     if (st != TIS_OK) return st;
-    if (num_splits > 1 && counters == nullptr) {
+    if (num_splits > 1 && counters == nullptr && !p.cluster_merge) {
         dim3 mg(H, num_tiles);
         attn_merge_kernel<<<mg, HD < 128 ? (HD < 32 ? 32 : HD) : 128, 0, stream>>>(p.part_o, p.part_lse, (bf16*)out, out_stride,
                                                                                   tile_row0, tile_rows, H, num_splits);

@@ -20,6 +20,9 @@
 // that first call should therefore come before any stream capture.  Later calls launch
 // kernels and nothing else: no cudaMalloc, no cudaFree, no library routine that allocates.
 //
+// With two to eight splits the kernel merges the splits inside a thread-block cluster and
+// needs no scratch at all; the built-in array serves calls with more splits than that.
+//
 // Limits.  Only decode-style tiles (at most 16 / G rows each, G = query heads per kv
 // head).  The call is refused with a clear error (TIS_BAD_SIZE, text in tis_last_error())
 // when  n_rows * H * num_splits * (head size + 1)  exceeds TIS_NOALLOC_SCRATCH_FLOATS.

@@ -243,7 +243,7 @@ def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, res
     base = max(1, num_tiles * kv_heads)
     total_tiles = max(1, (max_kv + 63) // 64)
     best, best_cost = 1, None
-    limit = total_tiles if mode_keys else min(total_tiles, 8)
+    limit = min(total_tiles, 8)        # keys mode: the splits are one thread-block cluster (at most 8 CTAs)
     for s in range(1, limit + 1):
         per_tiles = (total_tiles + s - 1) // s
         real = (total_tiles + per_tiles - 1) // per_tiles      # splits that per_tiles gives
@@ -299,13 +299,14 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
             resident = alib.resident[(mode, half)] = alib.tis_attn_resident_ctas(mode, half)
         per, splits = plan_splits(count, kv_heads, max_kv, mode == 1, resident)
         scratch = None
-        if splits > 1:
+        if splits > 1 and mode == 0:           # keys mode merges inside a cluster, without scratch
             need = alib.tis_attn_scratch_floats(n, num_heads, splits)
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         _check(alib.tis_attn_mma(mode, _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
                                  block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
                                  _p(rows), count, max_rows, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
-                                 per, splits, _p(scratch), _p(_counters(q.device, count * kv_heads) if splits > 1 else None),
+                                 per, splits, _p(scratch),
+                                 _p(_counters(q.device, count * kv_heads) if splits > 1 and mode == 0 else None),
                                  _p(fault), _stream()), alib)
     return out
 
