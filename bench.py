@@ -111,18 +111,17 @@ def decode_run(runner, batch, start_len, steps, warmup, sampler_cls, count_ops):
     """Device time of ``steps`` decode steps at ``batch`` requests; returns (ms per step, launches per step)."""
     import torch
     from tiny_inference_server_b200.engine import StepEntry
-    from tiny_inference_server_b200.sampling import SamplingParams
+    from tiny_inference_server_b200.sampling import SampleSpec, SamplingParams
 
     slots = [runner.add_request() for _ in range(batch)]
     fill_cache(runner, slots, start_len)
-    sampler = sampler_cls(runner.vocab_size, runner.engine.max_batch, runner.device)
-    params = [SamplingParams(temperature=0.0)] * batch
+    greedy = SamplingParams(temperature=0.0)
     gen = torch.Generator().manual_seed(2)
     feed = torch.randint(0, runner.vocab_size, (warmup + steps, batch), generator=gen).tolist()
 
     def one(i):
-        out = runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
-        return sampler.sample(out.main, params, slots, [0] * batch, [i] * batch)
+        # the step samples too (inside the captured graph); tokens stay on the device here
+        return runner.step([StepEntry(s, [feed[i][j]], [0], SampleSpec(greedy, 0, i)) for j, s in enumerate(slots)])
 
     for i in range(warmup):
         one(i)
@@ -268,7 +267,9 @@ def main(argv=None):
     # the same through the Python entry point
     engine = Engine(runner)
     e2e_tok_s, e2e_ms = e2e_run(engine, args.batch, start_len, args.steps, args.warmup)
-    h2d = args.batch * 4 * 4 + args.batch * (3 * 4 + 2 * 4 + 2 * 8)       # step metadata + sampling parameters
+    # one upload a step: rows, tiles and sampling parameters in one int32 buffer (plus, now and then, a
+    # block-table row when a request opens a new page)
+    h2d = max((g.static.used * 4 for g in runner.graphs.graphs.values()), default=0) if runner.graphs else 0
     d2h = args.batch * 4
     out["e2e"] = {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}

@@ -16,7 +16,7 @@ from .engine.batch import StepEntry
 from .engine.runner import ModelRunner
 from .engine.scheduler import PoolTooSmall, Request, Scheduler, StepPlan
 from .sampling.params import SamplingParams
-from .sampling.sampler import Sampler
+from .sampling.sampler import Sampler, SampleSpec
 
 __all__ = ["Engine", "Request", "SamplingParams", "PoolTooSmall"]
 
@@ -28,7 +28,7 @@ class Engine:
         eos = getattr(runner.config, "eos_token_id", None)
         self.scheduler = Scheduler(runner.cache, max_batch=eng.max_batch, max_tokens_per_step=eng.max_tokens_per_step,
                                    max_context=runner.max_positions, admission=eng.admission, eos_token_id=eos)
-        self.sampler = Sampler(runner.vocab_size, eng.max_batch, runner.device, seed=eng.seed)
+        self.sampler = runner.sampler
         self.last_aux = None
 
     @classmethod
@@ -52,17 +52,17 @@ class Engine:
         plan = sch.plan_step()
         if not plan.entries:
             return []
-        entries = [StepEntry(e.request.slot, e.request.ids[e.request.fed:e.request.fed + e.n_tokens],
-                             [e.n_tokens - 1] if e.sample else []) for e in plan.entries]
+        entries = []
+        for e in plan.entries:
+            r = e.request
+            spec = SampleSpec(r.params, self.sampler.request_seed(r.params, r.id), len(r.ids) - r.prompt_len) \
+                if e.sample else None
+            entries.append(StepEntry(r.slot, r.ids[r.fed:r.fed + e.n_tokens], [e.n_tokens - 1] if e.sample else [],
+                                     spec))
         out = self.runner.step(entries)
         self.last_aux = out.aux
-        tokens: List[int] = []
-        rows = [e.request for e in plan.entries if e.sample]
-        if rows:
-            dev = self.sampler.sample(out.main, [r.params for r in rows], [r.slot for r in rows],
-                                      [self.sampler.request_seed(r.params, r.id) for r in rows],
-                                      [len(r.ids) - r.prompt_len for r in rows])
-            tokens = dev.tolist()          # the step's one device-to-host read (upstream: server.py:240)
+        # the step's one device-to-host read (upstream: server.py:240)
+        tokens: List[int] = out.tokens.tolist() if out.tokens is not None else []
         return sch.commit(plan, tokens)
 
     def run(self) -> List[Request]:

@@ -24,6 +24,7 @@ class StepEntry:
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    sample: object = None        # sampling.SampleSpec: draw the token after the entry's last token
 
 
 @dataclass
@@ -200,6 +201,60 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
                       all(s.rows == 1 for s in segments))
 
 
+def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
+                  pad_to: int, group_sizes: Sequence[int], max_position: Optional[int] = None) -> StepLayout:
+    """``layout_step`` for the common case of a decode-only step (one token per entry, every
+    row wanted, padded to ``pad_to`` rows), with plain lists: for a handful of rows that is
+    several times faster than array arithmetic.  Same layout, word for word."""
+    n_real = len(entries)
+    n = max(pad_to, n_real)
+    pad = n - n_real
+    tokens = [int(e.tokens[0]) for e in entries]
+    for e, t in zip(entries, tokens):
+        if not (0 <= t < vocab_size):
+            raise ValueError(f"slot {e.slot}: token id {t} outside the vocabulary (0..{vocab_size - 1})")
+    positions = list(starts) + [0] * pad
+    slots = [e.slot for e in entries] + [-1] * pad
+    tokens += [0] * pad
+    rows = list(range(n))
+    flat: List[int] = []
+    offsets: Dict[str, Tuple[int, int]] = {}
+
+    def put(name, values):
+        offsets[name] = (len(flat), len(values))
+        flat.extend(values)
+
+    put("tokens", tokens)
+    put("positions", positions)
+    put("slots", slots)
+    put("last", rows)
+    lags = [l for l in sorted(set(lags)) if l > 0]
+    for lag in lags:
+        put(f"pos{lag}", [p - lag if p >= lag else 0 for p in positions])
+        put(f"slot{lag}", [s if p >= lag else -1 for s, p in zip(slots, positions)])
+    counts = {}
+    ones = [1] * n
+    for g in sorted(set(group_sizes)):
+        if g <= 16:
+            counts[g] = (n, 0, 1)
+            put(f"k0_{g}", rows)
+            put(f"kn_{g}", ones)
+            put(f"r0_{g}", [])
+            put(f"rn_{g}", [])
+        else:
+            counts[g] = (0, n, 0)
+            put(f"k0_{g}", [])
+            put(f"kn_{g}", [])
+            put(f"r0_{g}", rows)
+            put(f"rn_{g}", ones)
+    put("want", rows)
+    max_pos = max(starts) if n_real else 0
+    if max_position is not None:
+        max_pos = max(max_pos, max_position)
+    segments = [Segment(e.slot, i, 1, starts[i]) for i, e in enumerate(entries)]
+    return StepLayout(flat, offsets, n, segments, lags, counts, n, max_pos, True)
+
+
 def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[torch.Tensor],
                         page_sizes: List[int], fault: torch.Tensor) -> Tuple[StepContext, torch.Tensor]:
     """Views of the device copy of a layout as a StepContext; returns it and the wanted rows."""
@@ -267,7 +322,8 @@ class StaticMeta:
         if self.recorded[i]:
             self.events[i].synchronize()
         host = self.hosts[i]
-        host[: self.used] = torch.from_numpy(flat)
+        host[: self.used] = torch.from_numpy(flat) if isinstance(flat, np.ndarray) else \
+            torch.tensor(flat, dtype=torch.int32)
         self.dev[: self.used].copy_(host[: self.used], non_blocking=True)
         if self.events[i] is not None:
             self.events[i].record()

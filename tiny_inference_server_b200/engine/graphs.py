@@ -18,7 +18,8 @@ import torch
 
 from ..kernels import ops
 from ..models.base import StepOutput
-from .batch import StaticMeta, StepEntry, context_from_layout, layout_step
+from ..sampling.sampler import WORDS_PER_ROW
+from .batch import StaticMeta, StepEntry, context_from_layout, layout_decode
 
 
 def _next_pow2(x: int) -> int:
@@ -28,20 +29,26 @@ def _next_pow2(x: int) -> int:
 class GraphedDecode:
     """One captured decode step for ``bucket`` rows and contexts up to ``kv_bound`` keys."""
 
-    def __init__(self, runner, bucket: int, kv_bound: int):
+    def __init__(self, runner, bucket: int, kv_bound: int, sampled: bool):
         self.runner = runner
         self.bucket = bucket
         self.kv_bound = kv_bound
+        self.sampled = sampled            # the graph also draws a token for every row
         n_arrays = 4 + 2 * len([l for l in runner.lags if l > 0]) + 4 * len(runner.group_sizes) + 1
-        self.static = StaticMeta(n_arrays * bucket + 16, runner.device)
+        self.static = StaticMeta((n_arrays + WORDS_PER_ROW) * bucket + 16, runner.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[StepOutput] = None
         self.kernels = 0                # launches of this library's kernels inside the graph
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepOutput:
         r = self.runner
-        lay = layout_step(entries, starts, r.lags, r.vocab_size, pad_to=self.bucket, group_sizes=r.group_sizes,
-                          want_all=True, max_position=self.kv_bound - 1)
+        lay = layout_decode(entries, starts, r.lags, r.vocab_size, self.bucket, r.group_sizes,
+                            max_position=self.kv_bound - 1)
+        if self.sampled:
+            if len(lay.flat) % 2:
+                lay.flat.append(0)        # the block of sampling parameters starts 8-byte aligned
+            lay.offsets["sampling"] = (len(lay.flat), WORDS_PER_ROW * self.bucket)
+            lay.flat.extend(r.sampler.pack([e.sample for e in entries], [e.slot for e in entries], self.bucket))
         dev = self.static.upload(lay.flat, lay.offsets)
         if self.graph is not None:
             self.graph.replay()
@@ -51,12 +58,23 @@ class GraphedDecode:
         tables = [g.table_dev for g in r.cache.groups]
         sizes = [g.page_size for g in r.cache.groups]
         ctx, want = context_from_layout(lay, dev, tables, sizes, r.fault)
-        out = r.model.forward(ctx, want, aux=r.aux)
+        words = None
+        if self.sampled:
+            a, k = lay.offsets["sampling"]
+            words = dev[a:a + k]
+
+        def run_once() -> StepOutput:
+            o = r.model.forward(ctx, want, aux=r.aux)
+            if words is not None:
+                o.tokens = r.sampler.sample_packed(o.main, words)
+            return o
+
+        out = run_once()
         torch.cuda.synchronize(r.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph):
-            self.out = r.model.forward(ctx, want, aux=r.aux)
+            self.out = run_once()
         self.kernels = ops.launches - before
         ops.launches = before           # captured, not run
         self.graph = graph
@@ -76,18 +94,24 @@ class DecodeGraphs:
         bucket = min(_next_pow2(n), max(n, r.engine.max_batch))
         max_kv = max(starts) + 1
         kv_bound = min(max(self.min_kv, _next_pow2(max_kv)), max(r.max_positions, max_kv))
-        key = (bucket, kv_bound)
+        sampled = any(e.sample is not None for e in entries)
+        key = (bucket, kv_bound, sampled)
         g = self.graphs.get(key)
         if g is None:
-            g = self.graphs[key] = GraphedDecode(r, bucket, kv_bound)
+            g = self.graphs[key] = GraphedDecode(r, bucket, kv_bound, sampled)
         else:
             self.replays += 1
         full = g.run(entries, starts)
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        drawn = [i for i, e in enumerate(entries) if e.sample is not None]
+        tokens = None
+        if full.tokens is not None and drawn:
+            tokens = full.tokens[: len(drawn)] if drawn == list(range(len(drawn))) else \
+                full.tokens.index_select(0, torch.tensor(drawn, dtype=torch.int64, device=r.device))
         if wanted == list(range(len(wanted))):
             k = len(wanted)
             return StepOutput(main=full.main[:k], aux=[a[:k] for a in full.aux],
-                              aux_valid=[v[:k] for v in full.aux_valid])
+                              aux_valid=[v[:k] for v in full.aux_valid], tokens=tokens)
         idx = torch.tensor(wanted, dtype=torch.int64, device=r.device)
         return StepOutput(main=full.main.index_select(0, idx), aux=[a.index_select(0, idx) for a in full.aux],
-                          aux_valid=[v.index_select(0, idx) for v in full.aux_valid])
+                          aux_valid=[v.index_select(0, idx) for v in full.aux_valid], tokens=tokens)

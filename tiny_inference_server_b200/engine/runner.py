@@ -56,6 +56,8 @@ class ModelRunner:
         self.group_sizes = sorted({g for p in self.model.walk_parts() if hasattr(p, "tile_group_sizes")
                                    for g in p.tile_group_sizes()})
         self.aux = bool(self.engine.mtp)
+        from ..sampling.sampler import Sampler
+        self.sampler = Sampler(self.vocab_size, self.engine.max_batch, self.device, seed=self.engine.seed)
         self.graphs = None
         if self.engine.cuda_graphs and self.device.type == "cuda" and all(p.graph_safe for p in self.model.walk_parts()):
             from .graphs import DecodeGraphs
@@ -111,9 +113,28 @@ class ModelRunner:
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,
                                        self.vocab_size, pad_to=pad_to, group_sizes=self.group_sizes)
         out = self.model.forward(ctx, want_rows, aux=self.aux)
+        self._sample(entries, out)
         self.steps_run += 1
         self.rows_run += ctx.n
         return out
+
+    def _sample(self, entries: Sequence[StepEntry], out: StepOutput) -> None:
+        """Draw a token for every entry that asks for one (its last wanted row)."""
+        rows, specs, slots = [], [], []
+        k = 0
+        for e in entries:
+            if e.sample is not None:
+                if not len(e.want):
+                    raise ValueError(f"slot {e.slot}: an entry that wants a sample must want a row's logits")
+                rows.append(k + len(e.want) - 1)
+                specs.append(e.sample)
+                slots.append(e.slot)
+            k += len(e.want)
+        if not rows:
+            return
+        logits = out.main if rows == list(range(out.main.shape[0])) else \
+            out.main.index_select(0, torch.tensor(rows, dtype=torch.int64, device=self.device))
+        out.tokens = self.sampler.sample_specs(logits, specs, slots)
 
     def check_fault(self) -> None:
         """Synchronises.  Raises if a kernel saw a page id outside its pool."""

@@ -43,6 +43,7 @@ class StepOutput:
     aux: List[torch.Tensor] = field(default_factory=list)
     aux_valid: List[torch.Tensor] = field(default_factory=list)
     hidden: Optional[torch.Tensor] = None
+    tokens: Optional[torch.Tensor] = None      # int32, one per entry that asked for a sample, in entry order
 
 
 class Model:

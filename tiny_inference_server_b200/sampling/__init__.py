@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import Sampler
+from .sampler import Sampler, SampleSpec
 
-__all__ = ["SamplingParams", "Sampler"]
+__all__ = ["SamplingParams", "Sampler", "SampleSpec"]

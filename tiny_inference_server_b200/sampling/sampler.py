@@ -8,12 +8,27 @@ the kernel itself extends with the token it draws.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..kernels import ops
 from .params import SamplingParams
+
+
+@dataclass
+class SampleSpec:
+    """How to draw the token after an entry's last token: the request's options, the seed of
+    its random stream and how many tokens it has drawn so far (the stream's counter)."""
+    params: SamplingParams
+    seed: int
+    counter: int
+
+
+#: int32 words per row of the packed sampling parameters (see ``Sampler.pack``)
+WORDS_PER_ROW = 9
 
 
 class Sampler:
@@ -37,6 +52,51 @@ class Sampler:
     def request_seed(self, params: SamplingParams, request_id: int) -> int:
         base = params.seed if params.seed is not None else self.seed * 1000003 + request_id
         return base & 0xFFFFFFFFFFFFFFFF
+
+    # ---- parameters as int32 words, for steps whose arguments live in one fixed buffer -----
+    def pack(self, specs: Sequence[Optional[SampleSpec]], slots: Sequence[int], rows: int) -> List[int]:
+        """``rows`` rows of sampling parameters as ``WORDS_PER_ROW * rows`` int32 words: seeds and
+        counters as 64-bit little-endian pairs first (the block must start 8-byte aligned), then
+        temperature, top_p, penalty (float bits), top_k, bitmap slot.  Rows beyond ``specs``
+        (padding) and entries without a spec are greedy and touch no bitmap."""
+        temps, tps, pens, tks, bslots, seeds, ctrs = [], [], [], [], [], [], []
+        for i in range(rows):
+            sp = specs[i] if i < len(specs) else None
+            if sp is None:
+                temps.append(0.0); tps.append(0.0); pens.append(1.0); tks.append(0); bslots.append(-1)
+                seeds.append(0); ctrs.append(0)
+            else:
+                p = sp.params
+                temps.append(p.temperature); tps.append(p.top_p); pens.append(p.rep_penalty); tks.append(p.top_k)
+                bslots.append(slots[i] if p.rep_penalty != 1.0 else -1)
+                seeds.append(sp.seed & 0xFFFFFFFFFFFFFFFF); ctrs.append(sp.counter)
+        f = np.array([temps, tps, pens], dtype=np.float32).view(np.int32).reshape(-1).tolist()
+        u = np.array([seeds, ctrs], dtype=np.uint64).view(np.int32).reshape(-1).tolist()
+        return u + f + tks + bslots
+
+    @staticmethod
+    def unpack(words: torch.Tensor, rows: int):
+        """Device views of a packed block (``words`` int32, 8-byte aligned): temps, top_ps,
+        penalties (float32), top_ks, slots (int32), seeds, counters (int64)."""
+        u = words[: 4 * rows].view(torch.int64)
+        f = words[4 * rows: 7 * rows].view(torch.float32)
+        i = words[7 * rows: 9 * rows]
+        return f[:rows], f[rows:2 * rows], f[2 * rows:], i[:rows], i[rows:], u[:rows], u[rows:]
+
+    def sample_packed(self, logits: torch.Tensor, words: torch.Tensor, out: Optional[torch.Tensor] = None):
+        rows = logits.shape[0]
+        temps, tps, pens, tks, slots, seeds, ctrs = self.unpack(words, rows)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        ops.sample_rows(logits, temps, tks, tps, pens, slots, self.seen, seeds, ctrs, out, None)
+        return out
+
+    def sample_specs(self, logits: torch.Tensor, specs: Sequence[SampleSpec], slots: Sequence[int]) -> torch.Tensor:
+        """One token per row of ``logits`` for the given specs (one upload of all parameters)."""
+        rows = logits.shape[0]
+        words = self.pack(specs, slots, rows)
+        dev = torch.tensor(words + [0], dtype=torch.int32).to(self.device, non_blocking=True)
+        return self.sample_packed(logits, dev[: WORDS_PER_ROW * rows])
 
     def sample(self, logits: torch.Tensor, params: List[SamplingParams], slots: List[int], seeds: List[int],
                counters: List[int], probs_out: Optional[torch.Tensor] = None) -> torch.Tensor:
