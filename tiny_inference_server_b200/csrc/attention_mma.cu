@@ -485,6 +485,7 @@ attn_mma_kernel(const AttnParams p) {
             cluster.sync();              // nobody leaves while its shared memory may still be read
         }
     } else {
+        if (p.num_splits > 1 && p.cluster_merge) __syncthreads();     // all warps are done with the last tile
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int m = mbase + 8 * i;
@@ -497,6 +498,16 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
                 for (int d = 0; d < DTILES; ++d)
                     *reinterpret_cast<unsigned*>(dst + d * 8 + 2 * t_lane) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+            } else if (p.cluster_merge) {
+                // this split's normalised rows into shared memory (the staging area is free now)
+                float* cm_o = reinterpret_cast<float*>(smem_raw);        // [64][HD]
+                float* cm_lse = cm_o + 64 * HD;                          // [64]
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d) {
+                    cm_o[m * HD + d * 8 + 2 * t_lane] = o[d][2 * i] * inv;
+                    cm_o[m * HD + d * 8 + 2 * t_lane + 1] = o[d][2 * i + 1] * inv;
+                }
+                if (t_lane == 0) cm_lse[m] = l_run[i] > 0.f ? m_run[i] + log2f(l_run[i]) : -INFINITY;
             } else {
                 const size_t pr = ((size_t)row * p.H + hq) * p.num_splits + split;
 #pragma unroll
@@ -506,6 +517,35 @@ attn_mma_kernel(const AttnParams p) {
                 }
                 if (t_lane == 0) p.part_lse[pr] = l_run[i] > 0.f ? m_run[i] + log2f(l_run[i]) : -INFINITY;
             }
+        }
+        if (p.num_splits > 1 && p.cluster_merge) {
+            // the splits of this (tile, kv head) are one cluster: merge through distributed shared memory
+            namespace cg = cooperative_groups;
+            cg::cluster_group cluster = cg::this_cluster();
+            float* cm_o = reinterpret_cast<float*>(smem_raw);
+            float* cm_lse = cm_o + 64 * HD;
+            cluster.sync();
+            const int ns = p.num_splits;
+            const int pairs = rows * G;
+            for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
+                const int m = idx / HD, d = idx - m * HD;
+                const int r = m / G, g = m - r * G;
+                float mt = -INFINITY;
+                for (int sp = 0; sp < ns; ++sp) mt = fmaxf(mt, cluster.map_shared_rank(cm_lse, sp)[m]);
+                float acc = 0.f, wsum = 0.f;
+                if (mt != -INFINITY) {
+                    for (int sp = 0; sp < ns; ++sp) {
+                        const float l = cluster.map_shared_rank(cm_lse, sp)[m];
+                        if (l == -INFINITY) continue;
+                        const float w = fast_exp2(l - mt);
+                        wsum += w;
+                        acc += w * cluster.map_shared_rank(cm_o, sp)[m * HD + d];
+                    }
+                }
+                p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
+                    __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+            }
+            cluster.sync();
         }
     }
 
@@ -603,7 +643,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 static size_t smem_bytes(int mode) {
     size_t stage = (size_t)STAGES * STAGE_BYTES;
-    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float) : 0;
+    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float)
+                                     : (size_t)(64 * HD + 64) * sizeof(float);
     return stage > merge ? stage : merge;
 }
 
@@ -663,7 +704,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         tis_set_error("attention: %d kv heads or %d splits exceed the grid", KVH, num_splits);
         return TIS_BAD_SIZE;
     }
-    if (num_splits > 1 && scratch == nullptr && !(mode == MODE_KEYS && num_splits <= 8)) {
+    if (num_splits > 8 && scratch == nullptr) {
         tis_set_error("attention: %d key splits need scratch memory", num_splits);
         return TIS_BAD_SIZE;
     }
@@ -677,7 +718,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.part_o = scratch;
     p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
     p.counters = num_splits > 1 ? counters : nullptr;
-    p.cluster_merge = (mode == MODE_KEYS && num_splits > 1 && num_splits <= 8) ? 1 : 0;
+    p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
     p.fault = fault;
     const size_t smem = smem_bytes(mode);
     dim3 grid(num_tiles, KVH, num_splits);
@@ -691,10 +732,8 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
                              (int)smem_bytes(MODE_KEYS));
         configured = true;
     }
-    if (mode == MODE_ROWS) {
-        tis_launch(attn_mma_kernel<MODE_ROWS, 2>, grid, dim3(NTHREADS), smem, stream, p);
-    } else {
-        // keys mode: with 2..8 splits the splits of a (tile, kv head) form a cluster
+    {
+        // with 2..8 splits the splits of a (tile, kv head) form a thread-block cluster
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(NTHREADS);
@@ -716,7 +755,8 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         }
         cfg.attrs = attrs;
         cfg.numAttrs = na;
-        if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1>, p);
+        if (mode == MODE_ROWS) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2>, p);
+        else if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1>, p);
         else cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2>, p);
     }
     int st = tis_check_launch("attn_mma");

@@ -83,6 +83,7 @@ class StepContext:
         self.page_sizes = page_sizes
         self.fault = fault
         self.max_position = max_position    # largest position among the rows (host)
+        self.min_position = 0               # smallest position among the rows (host)
         self.lag = lag
         self._stages = stages if stages is not None else {}
         self.decode_only = decode_only      # every request has exactly one row
@@ -116,6 +117,7 @@ class StepLayout:
     n_want: int
     max_position: int
     decode_only: bool
+    min_position: int = 0
 
 
 def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
@@ -198,7 +200,7 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
         max_pos = max(max_pos, max_position)
     flat = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
     return StepLayout(flat, offsets, n, segments, lags, counts, len(want_rows), max_pos,
-                      all(s.rows == 1 for s in segments))
+                      all(s.rows == 1 for s in segments), int(positions[:n_real].min()) if n_real else 0)
 
 
 def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
@@ -252,7 +254,7 @@ def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seq
     if max_position is not None:
         max_pos = max(max_pos, max_position)
     segments = [Segment(e.slot, i, 1, starts[i]) for i, e in enumerate(entries)]
-    return StepLayout(flat, offsets, n, segments, lags, counts, n, max_pos, True)
+    return StepLayout(flat, offsets, n, segments, lags, counts, n, max_pos, True, min(starts) if n_real else 0)
 
 
 def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[torch.Tensor],
@@ -269,11 +271,13 @@ def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[t
     ctx = StepContext(lay.n, view("tokens"), view("positions"), view("slots"), view("last"), lay.segments,
                       block_tables, page_sizes, fault, lay.max_position, stages=stages,
                       decode_only=lay.decode_only, tiles=tiles)
+    ctx.min_position = lay.min_position
     for lag in lay.lags:
         st = StepContext(lay.n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), lay.segments,
                          block_tables, page_sizes, fault, max(0, lay.max_position - lag), trunk_slot=view("slots"),
                          lag=lag, stages=stages, decode_only=lay.decode_only, tiles=tiles)
         st.scratch = ctx.scratch
+        st.min_position = max(0, lay.min_position - lag)
         stages[lag] = st
     return ctx, view("want")
 

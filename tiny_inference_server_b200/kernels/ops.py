@@ -233,24 +233,50 @@ ATTN_CTA_OVERHEAD_TILES = 8.0
 ATTN_MERGE_PER_SPLIT_TILES = 0.1
 
 
-def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, resident: int = ATTN_RESIDENT_CTAS):
+def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, resident: int = ATTN_RESIDENT_CTAS,
+                min_kv: Optional[int] = None):
     """(keys per split, number of splits) for contexts of up to ``max_kv`` keys.
 
     One CTA walks the keys of one (tile, kv head, split), 64 at a time.  With few tiles the
-    SMs idle unless the keys are split; with too many splits every CTA is all overhead, and
-    one CTA more than fit the GPU at a time costs a whole second round.  The number of
-    splits minimises  rounds x (overhead + tiles per split) + merge cost."""
-    base = max(1, num_tiles * kv_heads)
+    SMs idle unless the keys are split; with too many splits every CTA is all overhead.
+    Tiles of a prompt see different numbers of keys (``min_kv`` .. ``max_kv``, causal): without
+    splits the CTA of the last tile works long after the others are done.  The number of
+    splits minimises an estimate of the time: CTAs that have keys at all, each costing
+    overhead + its tiles, spread over the CTAs that are resident at a time, but never less
+    than the longest CTA; plus the cost of merging."""
     total_tiles = max(1, (max_kv + 63) // 64)
+    lo_tiles = total_tiles if min_kv is None else max(1, (min(min_kv, max_kv) + 63) // 64)
+    limit = min(total_tiles, 8)        # the splits are one thread-block cluster (at most 8 CTAs)
+    if not mode_keys and lo_tiles < 0.75 * total_tiles:
+        # a prompt from its start: tiles see very different numbers of keys.  The CTAs of a cluster
+        # leave together, so a split without keys would hold its place until the longest one is
+        # done: splitting gains nothing there (measured: a 2048-token prompt gets slower).
+        limit = 1
     best, best_cost = 1, None
-    limit = min(total_tiles, 8)        # keys mode: the splits are one thread-block cluster (at most 8 CTAs)
     for s in range(1, limit + 1):
         per_tiles = (total_tiles + s - 1) // s
-        real = (total_tiles + per_tiles - 1) // per_tiles      # splits that per_tiles gives
-        if real != s:
+        if (total_tiles + per_tiles - 1) // per_tiles != s:
             continue
-        rounds = (base * s + resident - 1) // resident
-        cost = rounds * (ATTN_CTA_OVERHEAD_TILES + per_tiles) + (ATTN_MERGE_PER_SPLIT_TILES * s if s > 1 else 0.0)
+        # tiles with key counts spread evenly from lo_tiles to total_tiles
+        work, ctas = 0.0, 0.0
+        samples = min(num_tiles, 16)
+        for i in range(samples):
+            kv = lo_tiles + (total_tiles - lo_tiles) * (i + 0.5) / samples
+            full, rest = divmod(kv, per_tiles)
+            ctas += full + (1 if rest > 1e-9 else 0)
+            work += full * (ATTN_CTA_OVERHEAD_TILES + per_tiles) + ((ATTN_CTA_OVERHEAD_TILES + rest) if rest > 1e-9 else 0)
+        scale = num_tiles * kv_heads / samples
+        ctas, work = ctas * scale, work * scale
+        longest = ATTN_CTA_OVERHEAD_TILES + per_tiles
+        if lo_tiles == total_tiles:
+            # equal CTAs run in whole rounds: one CTA more than fit at a time costs a second round
+            cost = math.ceil(ctas / resident - 1e-9) * longest
+        else:
+            cost = max(longest, work / min(resident, max(ctas, 1.0)))
+        if s > 1:
+            cost += ATTN_MERGE_PER_SPLIT_TILES * s
+            if not mode_keys:
+                cost += 1.0            # 64 rows of partial outputs go through shared memory of the cluster
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     per = ((total_tiles + best - 1) // best) * 64
@@ -282,9 +308,12 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     if g > 64:
         raise KernelError(f"paged_attention: {g} query heads per kv head; the bfloat16 kernels take up to 64")
     alib = attention_library(head_dim)
+    min_kv = None
     if step is not None:
         tiles = step.attn_tiles(g)
         max_kv = step.max_position + 1
+        min_kv = getattr(step, "min_position", None)
+        min_kv = None if min_kv is None else min_kv + 1
     else:
         from ..engine.batch import infer_tiles
         tiles = infer_tiles(positions, row_slot, g)
@@ -297,16 +326,16 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         resident = alib.resident.get((mode, half))
         if resident is None:
             resident = alib.resident[(mode, half)] = alib.tis_attn_resident_ctas(mode, half)
-        per, splits = plan_splits(count, kv_heads, max_kv, mode == 1, resident)
+        per, splits = plan_splits(count, kv_heads, max_kv, mode == 1, resident, None if mode == 1 else min_kv)
         scratch = None
-        if splits > 1 and mode == 0:           # keys mode merges inside a cluster, without scratch
+        if splits > 8:                         # up to 8 splits merge inside a cluster, without scratch
             need = alib.tis_attn_scratch_floats(n, num_heads, splits)
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         _check(alib.tis_attn_mma(mode, _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
                                  block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
                                  _p(rows), count, max_rows, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
                                  per, splits, _p(scratch),
-                                 _p(_counters(q.device, count * kv_heads) if splits > 1 and mode == 0 else None),
+                                 _p(_counters(q.device, count * kv_heads) if splits > 8 else None),
                                  _p(fault), _stream()), alib)
     return out
 
