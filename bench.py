@@ -190,14 +190,86 @@ def prefill_run(runner, tokens, reps=3):
     return best
 
 
-def reference_arm():
+def reference_arm(args):
+    """The upstream project's own code (an unmodified copy of its files under baseline/_ref: it is
+    a folder of scripts, pip cannot install it) on the same metric: its Transformer with its own
+    random initialisation in bfloat16, its block_table pool and Scheduler without speculation
+    (server.py), 8 requests of ~4096 tokens of context; W warm-up and K timed calls of
+    Scheduler.step(), timed on the device with CUDA events.  Prints `unavailable` if it cannot run."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = ("upstream is a folder of scripts without setup.py or pyproject.toml (pip cannot install it), it needs a "
-           "checkpoint and tokenizer files that are not present offline, and its kernels are Triton")
-    if os.path.isdir(ref) and os.listdir(ref):
-        why = "installed files found, but " + why
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}))
+        return 0
+
+    if not os.path.isfile(os.path.join(ref, "server.py")):
+        return unavailable("upstream is a folder of scripts without setup.py or pyproject.toml (pip cannot install "
+                           "it) and no copy of its files is present under baseline/_ref")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        sys.path.insert(0, ref)
+        cwd = os.getcwd()
+        os.chdir(ref)
+        try:
+            import server as S                     # upstream: Scheduler, Request, cfg
+            from block_table import block_table
+            from main_models_new import Transformer
+        finally:
+            os.chdir(cwd)
+        cfg = S.cfg
+        batch, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
+        dev = "cuda:0"
+        torch.manual_seed(0)
+        model = Transformer(cfg.VOCAB_SIZE, cfg.MAX_CONTEXT, cfg.MAX_FREQ, cfg.D_MODEL, cfg.N_HEAD, cfg.NUM_LAYERS,
+                            cfg.FFN_HIDDEN_DIM, cfg.NUM_GROUPS, mtp_heads=cfg.MTP_HEADS).to(dev).to(torch.bfloat16)
+        model.buffers_to_float()
+        model.eval()
+        planes = cfg.NUM_LAYERS + cfg.MTP_HEADS
+        kvh, hd = cfg.N_HEAD // cfg.NUM_GROUPS, cfg.D_MODEL // cfg.N_HEAD
+        page_bytes = 16 * 2 * 2 * kvh * planes * hd
+        pool = block_table(planes, kvh, hd, (batch * (CONTEXT // 16 + 2)) * page_bytes, 16, dev)
+        sched = S.Scheduler(model, pool, batch, cfg.MAX_CONTEXT, dev, spec=False)
+        start_len = CONTEXT - (steps + warmup) - 2
+        gen = torch.Generator().manual_seed(3)
+        for _ in range(batch):
+            ids = torch.randint(0, 47000, (start_len,), generator=gen).tolist()
+            sched.submit(S.Request(ids, steps + warmup + 8, temperature=1.0, top_k=1))
+        clocks = ClockSampler()
+        sched.admit()
+        sched.step()                               # prefill of the prompts and the first token
+        for _ in range(warmup):
+            sched.step()
+        torch.cuda.synchronize()
+        clocks.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        ev0.record()
+        for _ in range(steps):
+            sched.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) / steps * 1e3
+        ms = ev0.elapsed_time(ev1) / steps
+        live = len(sched.active)
+        value = live / (ms * 1e-3)
+        print(json.dumps({
+            "impl": "reference", "metric": "decode tok/s at batch 8, context 4096 (upstream 0.9B model, random weights)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+            "config": {"model": "upstream_0.9B", "layers": cfg.NUM_LAYERS, "hidden": cfg.D_MODEL, "heads": cfg.N_HEAD,
+                       "kv_heads": kvh, "head_dim": hd, "ffn": cfg.FFN_HIDDEN_DIM, "vocab": cfg.VOCAB_SIZE,
+                       "mtp_heads_run": 0, "global_batch": live, "seq_len": CONTEXT, "page_size": 16,
+                       "parallelism": "single_gpu", "speculation": False},
+            # upstream's step takes host token ids and brings the sampled ids back (.tolist()): its
+            # device-timed step is already end to end; the wall clock over the same steps is given too
+            "e2e": {"value": round(live / (wall_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(wall_ms, 4)},
+            "clocks": clocks.stop()}))
+        return 0
+    except Exception as e:                         # noqa: BLE001 - any failure of upstream's code is reported, not raised
+        return unavailable(f"upstream's code did not run here: {type(e).__name__}: {e}")
 
 
 def main(argv=None):
@@ -211,7 +283,7 @@ def main(argv=None):
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     args = ap.parse_args(argv)
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
