@@ -402,3 +402,37 @@ def test_attention_splits_plan():
         per, splits = plan_splits(tiles, kvh, max_kv, keys_mode)
         assert per % 64 == 0 and per >= 64 and splits >= 1
         assert per * splits >= max_kv and per * (splits - 1) < max_kv
+
+
+@pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (4, 4, 64, 8, None), (6, 2, 32, 16, None),
+                                                  (8, 2, 128, 32, 200)])
+def test_paged_attention_whole_long_prompt(H, KVH, hd, page, window):
+    """A prompt of 700 tokens in one step: the row-tile kernel with three key groups per CTA
+    (long prompts from their start), two requests side by side, one of them short."""
+    from tiny_inference_server_b200.engine.batch import infer_tiles
+    ops = _ops()
+    g = torch.Generator().manual_seed(14)
+    dtype = torch.bfloat16
+    lens = [700, 90]
+    plane, table = _fill_cache(dtype, lens, KVH, hd, page, g)
+    rows = [(0, p) for p in range(700)] + [(1, p) for p in range(90)]
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    q = _rand((n, (H + 2 * KVH) * hd), dtype, g)
+    fault = torch.zeros(4, dtype=torch.int32)
+    want = ref.paged_attention(q, torch.empty(n, H * hd, dtype=dtype), plane, table, positions, row_slot, H, KVH, hd,
+                               page, window, fault)
+
+    class Step:                      # what the attention operation reads of a step
+        max_position, min_position = 699, 0
+        tiles = infer_tiles(positions.cuda(), row_slot.cuda(), H // KVH)
+
+        def attn_tiles(self, group):
+            return self.tiles
+
+    fault_dev = fault.cuda()
+    got = ops.paged_attention(q.cuda(), torch.full((n, H * hd), 7.0, dtype=dtype, device="cuda"), plane.cuda(),
+                              table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault_dev, Step())
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert int(fault_dev[0]) == 0

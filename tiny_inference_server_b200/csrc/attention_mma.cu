@@ -179,31 +179,44 @@ __device__ __forceinline__ void load_tile(bf16* stage, unsigned long long* bar, 
 // NR: packed rows a thread keeps softmax state for.  2: rows g and g+8 of the 16 a warp owns.
 // 1: only row g -- the tile has at most 8 packed rows (a decode row with up to 8 query heads per
 // kv head), rows 8..15 are padding and all their bookkeeping is left out.
-template <int MODE, int NR>
-__global__ void __launch_bounds__(NTHREADS)
+// NG: key groups (rows mode only).  NG groups of four warps work on the same 64 packed rows;
+// group g walks the staged key tiles g, g + NG, ... with stages and barriers of its own, and the
+// groups' results are merged through shared memory at the end.  A long prompt's last tiles see
+// thousands of keys while its first see a few: three groups cut the longest CTA's path to a third,
+// and with one CTA of twelve warps per SM the heavy tiles, launched first, are followed by the
+// light ones as SMs fall free.
+template <int MODE, int NR, int NG>
+__global__ void __launch_bounds__(NTHREADS * NG)
 attn_mma_kernel(const AttnParams p) {
+    static_assert(NG == 1 || MODE == MODE_ROWS, "key groups are for row tiles");
     constexpr int NT = MODE == MODE_ROWS ? 8 : 2;        // n8 key tiles a warp scores per staged tile
     constexpr int KB = MODE == MODE_ROWS ? 4 : 1;        // k16 key blocks a warp multiplies with V
+    constexpr int STAGE_ELEMS = 2 * KT * RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* stages = reinterpret_cast<bf16*>(smem_raw);    // STAGES x (K[64][RS], V[64][RS])
     __shared__ int sh_first;
-    __shared__ __align__(8) unsigned long long bars[STAGES];
+    __shared__ __align__(8) unsigned long long bars_all[NG * STAGES];
 
     pdl_launch_dependents();         // tiles, slots, positions and block tables below are step metadata,
                                      // not written by the kernel before; pdl_wait() comes before q and the cache
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int grp = NG == 1 ? 0 : (int)threadIdx.x / NTHREADS;          // key group of this thread
+    const int tid = NG == 1 ? (int)threadIdx.x : (int)threadIdx.x % NTHREADS;   // thread inside its group
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw) + (size_t)grp * STAGES * STAGE_ELEMS;   // STAGES x (K[64][RS], V[64][RS])
+    unsigned long long* bars = bars_all + grp * STAGES;
+    // with key groups: heaviest tiles (the last rows of a prompt) first
+    const int tile = NG == 1 ? (int)blockIdx.x : (int)(gridDim.x - 1 - blockIdx.x);
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int warp = tid >> 5, lane = tid & 31;
     const int g_lane = lane >> 2, t_lane = lane & 3;
     const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
     const int G = p.G;
 
     // first valid row of the tile (rows of a stage that lags the trunk start with padding)
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int st = 0; st < STAGES; ++st) mbar_init(&bars[st], NTHREADS);
+        for (int st = 0; st < NG * STAGES; ++st) mbar_init(&bars_all[st], NTHREADS);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == 0 && grp == 0) {
         const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
         const bool v1 = lane + 32 < rows && p.row_slot[row0 + lane + 32] >= 0;
         const unsigned b0 = __ballot_sync(0xffffffffu, v0), b1 = __ballot_sync(0xffffffffu, v1);
@@ -247,11 +260,13 @@ attn_mma_kernel(const AttnParams p) {
     // block table and the first page ids are step metadata too: fetch them before the wait
     const int* bt = p.block_table + (size_t)(slot >= 0 ? slot : 0) * p.bt_stride;
     const int kt0 = (range_lo / KT) * KT;
-    const int ntiles = empty ? 0 : (range_hi - kt0 + KT - 1) / KT;
-    int page = empty ? -1 : fetch_page(p, bt, kt0, range_hi, tid);
+    const int ntiles_all = empty ? 0 : (range_hi - kt0 + KT - 1) / KT;
+    const int ntiles = ntiles_all > grp ? (ntiles_all - grp + NG - 1) / NG : 0;     // tiles of this group
+    // the group's j-th tile starts at position kt0 + (grp + j * NG) * KT
+    int page = ntiles == 0 ? -1 : fetch_page(p, bt, kt0 + grp * KT, range_hi, tid);
     pdl_wait();
 
-    if (!empty) {
+    if (ntiles > 0) {
         // query fragments straight from global memory: a0 (row g, k 2t..), a1 (row g+8), a2 (row g, k 2t+8..), a3
         unsigned qa[KSTEPS][4];
 #pragma unroll
@@ -268,29 +283,32 @@ attn_mma_kernel(const AttnParams p) {
                 qa[kk][2 + i] = w1;
             }
         }
-        constexpr int STAGE_ELEMS = 2 * KT * RS;
+        const int ktg = kt0 + grp * KT;        // the group's first tile; its tiles are NG * KT apart
+        constexpr int KSTRIDE = NG * KT;
 
         // prologue: order STAGES-1 tiles; the page id a thread needs for the tile after is
         // fetched one tile ahead, so its latency is off the path
 #pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
             if (st < ntiles) {
-                const int page_next = fetch_page(p, bt, kt0 + (st + 1) * KT, range_hi, tid);
-                load_tile(stages + st * STAGE_ELEMS, &bars[st], p, page, kvh, kt0 + st * KT, range_lo, range_hi, tid);
+                const int page_next = fetch_page(p, bt, ktg + (st + 1) * KSTRIDE, range_hi, tid);
+                load_tile(stages + st * STAGE_ELEMS, &bars[st], p, page, kvh, ktg + st * KSTRIDE, range_lo, range_hi, tid);
                 page = page_next;
             }
         }
         for (int it = 0; it < ntiles; ++it) {
-            const int kt = kt0 + it * KT;
+            const int kt = ktg + it * KSTRIDE;
             const int stg = it % STAGES;
             bf16* cur = stages + stg * STAGE_ELEMS;
-            __syncthreads();                   // everyone is done reading the stage of tile it-1 ...
+            // everyone (of this group) is done reading the stage of tile it-1 ...
+            if (NG == 1) __syncthreads();
+            else asm volatile("bar.sync %0, 128;\n" ::"r"(grp + 1) : "memory");
             {
                 const int nx = it + STAGES - 1;    // ... which tile it+STAGES-1 takes
                 if (nx < ntiles) {
-                    const int page_next = fetch_page(p, bt, kt0 + (nx + 1) * KT, range_hi, tid);
+                    const int page_next = fetch_page(p, bt, ktg + (nx + 1) * KSTRIDE, range_hi, tid);
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                    load_tile(stages + (nx % STAGES) * STAGE_ELEMS, &bars[nx % STAGES], p, page, kvh, kt0 + nx * KT,
+                    load_tile(stages + (nx % STAGES) * STAGE_ELEMS, &bars[nx % STAGES], p, page, kvh, ktg + nx * KSTRIDE,
                               range_lo, range_hi, tid);
                     page = page_next;
                 }
@@ -395,6 +413,40 @@ attn_mma_kernel(const AttnParams p) {
                     mma_bf16(o[d + 1], pa, b[2], b[3]);
                 }
             }
+        }
+    }
+
+    // ---- key groups: groups 1.. hand their maxima, sums and outputs to group 0
+    if (NG > 1) {
+        constexpr int PER = 4 + DTILES * 4;            // floats a thread hands over
+        float* xg = reinterpret_cast<float*>(smem_raw);    // [NG-1][PER][128], element-major: no bank conflicts
+        __syncthreads();                               // every group is done with its stages
+        if (grp > 0) {
+            float* dst = xg + (size_t)(grp - 1) * PER * NTHREADS + tid;
+            dst[0] = m_run[0]; dst[NTHREADS] = m_run[1]; dst[2 * NTHREADS] = l_run[0]; dst[3 * NTHREADS] = l_run[1];
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dst[(4 + d * 4 + e) * NTHREADS] = o[d][e];
+        }
+        __syncthreads();
+        if (grp > 0) return;                           // only group 0 writes the output (no barrier follows)
+        for (int g2 = 1; g2 < NG; ++g2) {
+            const float* src = xg + (size_t)(g2 - 1) * PER * NTHREADS + tid;
+            float fa[2], fb[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float mg = src[i * NTHREADS], lg = src[(2 + i) * NTHREADS];
+                const float mn = fmaxf(m_run[i], mg);
+                fa[i] = (m_run[i] == -INFINITY) ? 0.f : fast_exp2(m_run[i] - mn);
+                fb[i] = (mg == -INFINITY) ? 0.f : fast_exp2(mg - mn);
+                l_run[i] = l_run[i] * fa[i] + lg * fb[i];
+                m_run[i] = mn;
+            }
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[d][e] = o[d][e] * fa[e >> 1] + src[(4 + d * 4 + e) * NTHREADS] * fb[e >> 1];
         }
     }
 
@@ -657,14 +709,14 @@ TIS_API int tis_attn_resident_ctas(int mode, int half) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const size_t smem = smem_bytes(mode);
     if (mode == MODE_ROWS) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_ROWS, 2>, NTHREADS, smem);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_ROWS, 2, 1>, NTHREADS, smem);
     } else if (half) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 1>, NTHREADS, smem);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 1, 1>, NTHREADS, smem);
     } else {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 2>, NTHREADS, smem);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 2, 1>, NTHREADS, smem);
     }
     cudaGetLastError();
     return per_sm > 0 && sms > 0 ? per_sm * sms : 148 * 2;
@@ -724,12 +776,15 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     dim3 grid(num_tiles, KVH, num_splits);
     static bool configured = false;          // once per process (and before any stream capture)
     if (!configured) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_ROWS));
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_KEYS));
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_KEYS));
+        if (3 * smem_bytes(MODE_ROWS) <= 227 * 1024)
+            cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(3 * smem_bytes(MODE_ROWS)));
         configured = true;
     }
     {
@@ -755,9 +810,16 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         }
         cfg.attrs = attrs;
         cfg.numAttrs = na;
-        if (mode == MODE_ROWS) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2>, p);
-        else if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1>, p);
-        else cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2>, p);
+        // a long prompt from (near) its start: three key groups per CTA, heaviest tiles first
+        const bool groups3 = mode == MODE_ROWS && num_splits == 1 && keys_per_split >= 512 &&
+                             3 * smem_bytes(MODE_ROWS) <= 227 * 1024;
+        if (groups3) {
+            cfg.blockDim = dim3(3 * NTHREADS);
+            cfg.dynamicSmemBytes = 3 * smem_bytes(MODE_ROWS);
+            cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 3>, p);
+        } else if (mode == MODE_ROWS) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 1>, p);
+        else if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1, 1>, p);
+        else cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2, 1>, p);
     }
     int st = tis_check_launch("attn_mma");
     if (st != TIS_OK) return st;

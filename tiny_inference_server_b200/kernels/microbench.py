@@ -1,0 +1,175 @@
+"""Runs single kernels at the shapes of a model, for timing and for profiler captures.
+
+    python -m tiny_inference_server_b200.kernels.microbench attention --batch 8 --context 4096
+    python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8
+    python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
+    python -m tiny_inference_server_b200.kernels.microbench all
+
+``--reps N --no-timing`` launches the kernel N times and exits (a profiler attaches to that);
+without it the kernels are timed with CUDA events, replayed from a CUDA graph that holds 40
+launches over buffers larger than L2 (so a time includes the gap between dependent kernels,
+as inside a decode step).  Default sizes are the upstream 0.9B model's: width 1536, 12 query
+and 3 kv heads of 128, SwiGLU 4096.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import tempfile
+
+import torch
+
+from . import ops
+
+
+def _graph_time(fn, n=40):
+    fn(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n * 1e3
+
+
+class _Step:
+    """The little of a StepContext that the attention operation reads."""
+
+    def __init__(self, tiles, max_position):
+        self._tiles = tiles
+        self.max_position = max_position
+        self.min_position = max_position
+
+    def attn_tiles(self, g):
+        return self._tiles
+
+
+def attention(args):
+    from ..engine.batch import infer_tiles
+    dev = "cuda"
+    H, KVH, hd, page, ctx, B = args.heads, args.kv_heads, args.head_dim, args.page_size, args.context, args.batch
+    pages_per = (ctx + page - 1) // page
+    num_pages = B * pages_per
+    n_planes = max(2, min(12, (400 << 20) // max(1, B * ctx * 2 * KVH * hd * 2)))
+    planes = [torch.randn(num_pages, 2, KVH, page, hd, device=dev, dtype=torch.bfloat16) for _ in range(n_planes)]
+    table = torch.arange(num_pages, dtype=torch.int32, device=dev).reshape(B, pages_per).contiguous()
+    positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    slots = torch.arange(B, dtype=torch.int32, device=dev)
+    qkv = torch.randn(B, (H + 2 * KVH) * hd, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(B, H * hd, device=dev, dtype=torch.bfloat16)
+    fault = torch.zeros(4, dtype=torch.int32, device=dev)
+    step = _Step(infer_tiles(positions, slots, H // KVH), ctx - 1)
+
+    def run(i):
+        ops.paged_attention(qkv, out, planes[i % n_planes], table, positions, slots, H, KVH, hd, page, None, fault, step)
+
+    kv_bytes = B * ctx * 2 * KVH * hd * 2
+    if args.no_timing:
+        for i in range(args.reps):
+            run(i)
+        torch.cuda.synchronize()
+        print(f"attention batch {B} context {ctx}: {args.reps} launches, fault {int(fault[0])}")
+        return
+    t = _graph_time(run)
+    print(f"attention decode  batch {B:3d} context {ctx}: {t:8.2f} us  {kv_bytes / t / 1e3:8.1f} GB/s of keys and values")
+
+
+def gemm(args):
+    dev = "cuda"
+    d, F, H, KVH, hd, n = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.rows
+    x = torch.randn(n, d, device=dev, dtype=torch.bfloat16)
+    hm = torch.randn(n, F, device=dev, dtype=torch.bfloat16)
+    shapes = (("qkv", d, (H + 2 * KVH) * hd, x, False), ("o", H * hd, d, x[:, : H * hd].contiguous(), False),
+              ("gate_up+swiglu", d, 2 * F, x, True), ("down", F, d, hm, False))
+    for name, K, N, inp, fused in shapes:
+        if args.only and args.only != name:
+            continue
+        ws = [torch.randn(K, N, device=dev, dtype=torch.bfloat16) for _ in range(12)]
+
+        def mine(i):
+            ops.gemm_skinny(inp, ws[i % 12], swiglu=fused)
+
+        def lib(i):
+            torch.mm(inp, ws[i % 12])
+
+        if args.no_timing:
+            for i in range(args.reps):
+                mine(i)
+            torch.cuda.synchronize()
+            print(f"gemm {name} rows {n}: {args.reps} launches")
+            continue
+        a, b = _graph_time(mine), _graph_time(lib)
+        mb = K * N * 2 / 1e6
+        print(f"gemm {name:15s} rows {n:3d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s)   "
+              f"library {b:7.2f} us")
+
+
+def prefill(args):
+    """One step of ``--tokens`` prompt tokens through ``--layers`` layers of the model."""
+    from ..config import EngineConfig
+    from ..engine import ModelRunner, StepEntry
+    from ..registry import config_from_dict
+    from ..weights import write_random_model
+    cfg = config_from_dict(dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=args.width,
+                                num_layers=args.layers, num_heads=args.heads, num_kv_heads=args.kv_heads,
+                                head_dim=args.head_dim, ffn_hidden=args.ffn, max_context=4096, num_mtp_heads=0))
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(tmp, cfg, seed=0)
+        r = ModelRunner.from_folder(folder, EngineConfig(dtype="bfloat16", page_size=args.page_size,
+                                                         num_pages=(args.tokens // args.page_size + 2) * 2,
+                                                         max_batch=2, max_tokens_per_step=args.tokens))
+    g = torch.Generator().manual_seed(0)
+    for rep in range(max(3, args.reps)):
+        ids = torch.randint(0, cfg.vocab_size, (args.tokens,), generator=g).tolist()
+        s = r.add_request()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r.step([StepEntry(s, ids, [args.tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"prefill {args.tokens} tokens, {args.layers} layers: {e0.elapsed_time(e1):.3f} ms", flush=True)
+        r.release(s)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("what", choices=["attention", "gemm", "prefill", "all"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--only", default=None, help="gemm: one of qkv, o, gate_up+swiglu, down")
+    ap.add_argument("--width", type=int, default=1536)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--kv-heads", type=int, default=3)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--ffn", type=int, default=4096)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--no-timing", action="store_true")
+    args = ap.parse_args(argv)
+    ops.library()
+    if args.what in ("attention", "all"):
+        for b in ([args.batch] if args.what == "attention" else [1, 8, 64]):
+            args.batch = b
+            attention(args)
+    if args.what in ("gemm", "all"):
+        for n in ([args.rows] if args.what == "gemm" else [1, 8, 16]):
+            args.rows = n
+            gemm(args)
+    if args.what in ("prefill", "all"):
+        prefill(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
