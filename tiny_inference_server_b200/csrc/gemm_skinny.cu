@@ -255,7 +255,11 @@ TIS_API int tis_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
+#ifdef TIS_GEMM_NO_EARLY
+    cfg.numAttrs = 1;
+#else
     cfg.numAttrs = tis_pdl_enabled() ? 2 : 1;
+#endif
     cudaError_t e;
     static bool configured = false;
     if (!configured) {

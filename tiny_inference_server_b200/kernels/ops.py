@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -83,8 +84,12 @@ def _f(x: float):
 # main_models_new.py:20,29,226)
 # ---------------------------------------------------------------------------------------
 
-#: rows up to which bfloat16 products go to the weight-streaming kernel instead of the library
-SKINNY_MAX_ROWS = 16
+#: rows up to which bfloat16 products go to the weight-streaming kernel of this library instead of
+#: the library product.  Measured inside the decode step of the 0.9B model on a B200: at one row the
+#: kernel wins (706 against 658 tok/s), at eight rows the library's split-K kernels do (4989 against
+#: 4867 tok/s), so the switch is at four.  TIS_SKINNY_MAX_ROWS in the environment overrides it
+#: (0 sends everything to the library; the kernel itself takes up to 64 rows).
+SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "4"))
 EPI_STORE, EPI_SWIGLU = 0, 1
 
 
@@ -98,7 +103,7 @@ def _ksplit(n_cols: int, k: int) -> int:
     """CTAs that share a 64-column strip of the weights (a cluster adding up over K): as many as
     keep the grid near two CTAs per SM, each with at least 128 rows of K."""
     strips = (n_cols + 63) // 64
-    ks = 8
+    ks = int(os.environ.get("TIS_KSPLIT_MAX", "8"))
     while ks > 1 and (strips * ks > 2 * 148 * 2 or k // ks < 128):
         ks //= 2
     return ks
