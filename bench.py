@@ -152,6 +152,7 @@ def e2e_run(engine, batch, start_len, steps, warmup):
                           SamplingParams(max_new_tokens=warmup + steps + 8, temperature=0.0, ignore_eos=True))
             for _ in range(batch)]
     engine.step()                                        # prefill of the short prompts
+    engine.drain()
     for r in reqs:                                       # lengthen every request's context
         extra = start_len - engine.runner.cache.length[r.slot]
         engine.runner.cache.extend(r.slot, extra)
@@ -164,7 +165,8 @@ def e2e_run(engine, batch, start_len, steps, warmup):
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(steps):
-        engine.step()
+        engine.step()                                    # launches one step, reads the tokens of the one before
+    engine.drain()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     return batch * steps / dt, dt / steps * 1e3

@@ -43,3 +43,45 @@ def test_greedy_equals_plain(name, lengths, new, tmp_path, ref_ops):
     assert eng.scheduler.preempts > 0 and eng.scheduler.replays > 0
     eng.runner.cache.check()
     assert eng.runner.cache.drained()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_step_in_flight_changes_nothing(name, tmp_path, ref_ops):
+    """With one step kept in flight the tokens are those of the step-by-step engine, also when
+    requests end at different steps, on the end-of-sequence token (noticed a step late) or on
+    their length, and when pages are short."""
+    cfg, page, seed = tiny_configs.ALL[name]
+    folder = tiny_configs.make_model_folder(cfg, seed, str(tmp_path / "m"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], [3, 11, 20, 6], seed=11)
+    full = [plain_model.plain_greedy(c, W, p, 14) for p in prompts]
+    news = [14, 9, 12, 5]
+    sps = [SamplingParams(max_new_tokens=n, temperature=0.0, ignore_eos=True) for n in news]
+    want = [f[:n] for f, n in zip(full, news)]
+    for pipeline in (False, True):
+        eng = _engine(folder, page)
+        eng.pipeline = pipeline
+        assert eng.generate(prompts, sps) == want
+        assert (eng.steps_behind > 0) == pipeline
+        assert eng.runner.cache.drained()
+        eng.runner.cache.check()
+
+    # the end-of-sequence token: the seventh token of the first request
+    eos = full[0][6]
+    want = [f[: f.index(eos) + 1] if eos in f else f for f in full]
+    sp = SamplingParams(max_new_tokens=14, temperature=0.0)
+    for pipeline in (False, True):
+        eng = _engine(folder, page)
+        eng.pipeline = pipeline
+        eng.scheduler.eos_token_id = eos
+        assert eng.generate(prompts, sp) == want
+        assert eng.runner.cache.drained()
+        eng.runner.cache.check()
+
+    # short of pages while a step is in flight: the engine falls back to deciding step by step
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], [page - 1] * 4, seed=8)
+    want = [plain_model.plain_greedy(c, W, p, 12) for p in prompts]
+    eng = _engine(folder, page, num_pages=6, admission="cur", max_tokens_per_step=64)
+    assert eng.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0, ignore_eos=True)) == want
+    assert eng.scheduler.preempts > 0 and eng.steps_behind > 0
+    assert eng.runner.cache.drained()

@@ -45,6 +45,41 @@ def test_greedy_generation_equals_plain_float32(name, lengths, new, tmp_path):
     assert eng.generate(prompts, SamplingParams(max_new_tokens=new, temperature=1.0, top_k=1, ignore_eos=True)) == want
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_step_in_flight_float32(name, graphs, tmp_path):
+    """One decode step kept in flight (tokens fed on the device, read back a step late): the
+    same tokens as step by step and as the plain implementation; requests of different
+    lengths, the end-of-sequence token, sampling with a seed."""
+    from tiny_inference_server_b200.api import SamplingParams
+    cfg, page, folder, c, W = _model(name, tmp_path)
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], [3, 11, 20, 6, 40], seed=11)
+    full = [plain_model.plain_greedy(c, W, p, 30) for p in prompts]
+    news = [30, 9, 22, 5, 17]
+    sps = [SamplingParams(max_new_tokens=n, temperature=0.0, ignore_eos=True) for n in news]
+    eng = _engine(folder, page, max_batch=8, cuda_graphs=graphs)
+    assert eng.generate(prompts, sps) == [f[:n] for f, n in zip(full, news)]
+    assert eng.steps_behind > 10 and eng.runner.cache.drained()
+
+    eos = full[0][12]
+    want = [f[: f.index(eos) + 1] if eos in f else f for f in full]
+    eng = _engine(folder, page, max_batch=8, cuda_graphs=graphs)
+    eng.scheduler.eos_token_id = eos
+    assert eng.generate(prompts, SamplingParams(max_new_tokens=30, temperature=0.0)) == want
+    assert eng.steps_behind > 5 and eng.runner.cache.drained()
+    eng.runner.cache.check()
+
+    # drawn tokens: the same seed gives the same tokens with and without the step in flight
+    sp = SamplingParams(max_new_tokens=20, temperature=0.9, top_k=12, top_p=0.95, rep_penalty=1.2, seed=5,
+                        ignore_eos=True)
+    outs = []
+    for pipeline in (True, False):
+        eng = _engine(folder, page, max_batch=8, cuda_graphs=graphs)
+        eng.pipeline = pipeline
+        outs.append(eng.generate(prompts, sp))
+    assert outs[0] == outs[1]
+
+
 def test_greedy_generation_with_preemption_float32(tmp_path):
     from tiny_inference_server_b200.api import SamplingParams
     cfg, page, folder, c, W = _model("A", tmp_path)

@@ -93,7 +93,10 @@ class CacheManager:
         start = self.length[slot]
         need = 0
         for g in self.groups:
-            need = max(need, g.pages_to_grow(slot, start + n_new) - g.pages_freed_by(slot, start))
+            grow = g.pages_to_grow(slot, start + n_new)
+            if g.window is not None:
+                grow -= g.pages_freed_by(slot, start)
+            need = max(need, grow)
         return max(0, need)
 
     def pages_for_tokens(self, n_tokens: int) -> int:
@@ -109,12 +112,14 @@ class CacheManager:
         if new_len > self.max_positions:
             raise CacheError(f"slot {slot}: {new_len} tokens exceed the context limit {self.max_positions}")
         for g in self.groups:
-            if g.pages_to_grow(slot, new_len) - g.pages_freed_by(slot, start) > g.pool.free:
-                raise OutOfPages(f"group {g.gid}: {g.pages_to_grow(slot, new_len)} pages needed, "
-                                 f"{g.pool.free} free")
+            grow = g.pages_to_grow(slot, new_len)
+            if grow and grow - g.pages_freed_by(slot, start) > g.pool.free:
+                raise OutOfPages(f"group {g.gid}: {grow} pages needed, {g.pool.free} free")
         for g in self.groups:
-            g.trim(slot, start)
-            g.grow(slot, new_len)
+            if g.window is not None:
+                g.trim(slot, start)
+            if new_len > g.end[slot] * g.page_size:
+                g.grow(slot, new_len)
         self.length[slot] = new_len
         return start
 

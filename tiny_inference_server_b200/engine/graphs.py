@@ -12,6 +12,7 @@ and their logits are not returned.  Logits are computed for every row of the buc
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -40,7 +41,7 @@ class GraphedDecode:
         self.out: Optional[StepOutput] = None
         self.kernels = 0                # launches of this library's kernels inside the graph
 
-    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepOutput:
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int], feed=None) -> StepOutput:
         r = self.runner
         lay = layout_decode(entries, starts, r.lags, r.vocab_size, self.bucket, r.group_sizes,
                             max_position=self.kv_bound - 1)
@@ -50,6 +51,10 @@ class GraphedDecode:
             lay.offsets["sampling"] = (len(lay.flat), WORDS_PER_ROW * self.bucket)
             lay.flat.extend(r.sampler.pack([e.sample for e in entries], [e.slot for e in entries], self.bucket))
         dev = self.static.upload(lay.flat, lay.offsets)
+        if feed is not None:
+            from .runner import feed_tokens
+            a, _ = lay.offsets["tokens"]
+            feed_tokens(dev[a:a + len(entries)], len(entries), feed)
         if self.graph is not None:
             self.graph.replay()
             ops.launches += self.kernels
@@ -73,8 +78,17 @@ class GraphedDecode:
         torch.cuda.synchronize(r.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph):
-            self.out = run_once()
+        # No garbage collection while the stream is capturing: the collector may destroy an
+        # older engine's graphs, and destroying a graph invalidates a capture in progress.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self.out = run_once()
+        finally:
+            if was_enabled:
+                gc.enable()
         self.kernels = ops.launches - before
         ops.launches = before           # captured, not run
         self.graph = graph
@@ -88,7 +102,7 @@ class DecodeGraphs:
         self.graphs: Dict[Tuple[int, int], GraphedDecode] = {}
         self.replays = 0
 
-    def step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepOutput:
+    def step(self, entries: Sequence[StepEntry], starts: Sequence[int], feed=None) -> StepOutput:
         r = self.runner
         n = len(entries)
         bucket = min(_next_pow2(n), max(n, r.engine.max_batch))
@@ -101,7 +115,7 @@ class DecodeGraphs:
             g = self.graphs[key] = GraphedDecode(r, bucket, kv_bound, sampled)
         else:
             self.replays += 1
-        full = g.run(entries, starts)
+        full = g.run(entries, starts, feed)
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         drawn = [i for i, e in enumerate(entries) if e.sample is not None]
         tokens = None

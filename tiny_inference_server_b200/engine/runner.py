@@ -29,6 +29,15 @@ class DeviceFault(RuntimeError):
     """A kernel met a page id outside its pool (the block tables and the batch disagree)."""
 
 
+def feed_tokens(dst: torch.Tensor, n: int, feed) -> None:
+    """dst[i] = tokens[index[i]] for the first ``n`` rows, on the device (stream-ordered)."""
+    src, index = feed
+    if list(index) == list(range(n)):
+        dst[:n].copy_(src[:n])
+    else:
+        dst[:n].copy_(src.index_select(0, torch.tensor(list(index), dtype=torch.int64, device=src.device)))
+
+
 class ModelRunner:
     def __init__(self, cfg, tensors: Dict[str, torch.Tensor], engine: Optional[EngineConfig] = None):
         self.engine = engine or EngineConfig()
@@ -83,35 +92,43 @@ class ModelRunner:
         return self.cache.length[slot]
 
     # ---- the step ---------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], pad_to: Optional[int] = None) -> StepOutput:
+    def step(self, entries: Sequence[StepEntry], pad_to: Optional[int] = None, feed=None) -> StepOutput:
+        """Run one step.  ``feed = (tokens, index)``: the step holds one token per entry and entry
+        i's token is not in ``entries`` (a placeholder stands there) but on the device, at
+        ``tokens[index[i]]`` — the tokens the step before drew, which the host has not read yet."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         slots = [e.slot for e in entries]
         if len(set(slots)) != len(slots):
             raise ValueError("a request appears twice in one step")
-        # pages: either every entry fits or nothing is changed
-        for g in range(len(self.cache.groups)):
-            grp = self.cache.groups[g]
-            need = 0
-            for e in entries:
-                start = self.cache.length[e.slot]
-                need += grp.pages_to_grow(e.slot, start + len(e.tokens)) - grp.pages_freed_by(e.slot, start)
-            if need > grp.pool.free:
-                raise OutOfPages(f"group {g}: the step needs {need} pages, {grp.pool.free} are free")
+        # pages and context: either every entry fits or nothing is changed
+        lengths = self.cache.length
         for e in entries:
-            if self.cache.length[e.slot] + len(e.tokens) > self.max_positions:
-                raise CacheError(f"slot {e.slot}: {self.cache.length[e.slot] + len(e.tokens)} tokens exceed "
+            if lengths[e.slot] + len(e.tokens) > self.max_positions:
+                raise CacheError(f"slot {e.slot}: {lengths[e.slot] + len(e.tokens)} tokens exceed "
                                  f"the context limit {self.max_positions}")
+        for grp in self.cache.groups:
+            need = 0
+            windowed = grp.window is not None
+            for e in entries:
+                start = lengths[e.slot]
+                need += grp.pages_to_grow(e.slot, start + len(e.tokens))
+                if windowed:
+                    need -= grp.pages_freed_by(e.slot, start)
+            if need > grp.pool.free:
+                raise OutOfPages(f"group {grp.gid}: the step needs {need} pages, {grp.pool.free} are free")
         starts = [self.cache.extend(e.slot, len(e.tokens)) for e in entries]
         self.cache.sync_tables()
         if self.graphs is not None and pad_to is None and all(len(e.tokens) == 1 for e in entries):
             self.steps_run += 1
             self.rows_run += len(entries)
-            return self.graphs.step(entries, starts)
+            return self.graphs.step(entries, starts, feed)
         ctx, want_rows, _ = build_step(entries, starts, self.lags,
                                        [g.table_dev for g in self.cache.groups],
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,
                                        self.vocab_size, pad_to=pad_to, group_sizes=self.group_sizes)
+        if feed is not None:
+            feed_tokens(ctx.tokens, len(entries), feed)
         out = self.model.forward(ctx, want_rows, aux=self.aux)
         self._sample(entries, out)
         self.steps_run += 1

@@ -122,6 +122,8 @@ class Scheduler:
 
     def admit(self) -> List[Request]:
         admitted = []
+        if not self.queue:
+            return admitted
         budget = self.cache.free_pages() - sum(self.grow_pages(r, 1) for r in self.active if r.remaining == 1)
         while self.queue and len(self.active) < self.max_batch and self.cache.has_free_slot():
             q = self.queue[0]
