@@ -124,6 +124,57 @@ def test_skinny_gemm_with_swiglu_epilogue(n, K, F):
         torch.testing.assert_close(ops.gemm_swiglu(a2.cuda(), w.cuda(), F, 32).cpu().double(), want2, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("M,K,N", [(128, 64, 128), (300, 72, 200), (1000, 264, 1544), (2048, 1536, 2304),
+                                   (513, 4096, 1536), (129, 40, 8), (640, 128, 448)])
+def test_tcgen05_gemm(M, K, N):
+    """The tcgen05 product for many rows: every tile width, rows, columns and K that do not fill
+    their tiles, operands and results that are slices of wider matrices."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(14)
+    a = _rand((M, K), torch.bfloat16, g)
+    w = _rand((K, N), torch.bfloat16, g, 0.05)
+    want = a.double() @ w.double()
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, float(want.abs().max()) / 4))
+    got = ops.gemm_tc(a.cuda(), w.cuda())
+    assert got.shape == (M, N) and got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.cpu().double(), want, **tol)
+    wide_a = torch.zeros(M, K + 24, dtype=torch.bfloat16).cuda()
+    wide_a[:, 8:8 + K] = a.cuda()
+    wide_w = _rand((K, N + 64), torch.bfloat16, g, 0.05).cuda()
+    wide_w[:, 16:16 + N] = w.cuda()
+    out = torch.full((M, N + 16), 7.0, dtype=torch.bfloat16).cuda()
+    ops.gemm_tc(wide_a[:, 8:8 + K], wide_w[:, 16:16 + N], out=out[:, 8:8 + N])
+    torch.testing.assert_close(out[:, 8:8 + N].cpu().double(), want, **tol)
+    assert bool((out[:, :8] == 7).all()) and bool((out[:, 8 + N:] == 7).all()), "wrote outside its columns"
+    assert int(ops.tc_fault()[0]) == 0
+
+
+@pytest.mark.parametrize("M,K,F", [(128, 64, 32), (130, 40, 96), (2048, 1536, 4096), (700, 200, 352)])
+def test_tcgen05_gemm_with_swiglu_epilogue(M, K, F):
+    ops = _ops()
+    g = torch.Generator().manual_seed(15)
+    a = _rand((M, K), torch.bfloat16, g)
+    w = _rand((K, 2 * F), torch.bfloat16, g, 0.05)
+    gu = (a.double() @ w.double()).reshape(M, F // 32, 2, 32)
+    want = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(M, F)
+    got = ops.gemm_tc(a.cuda(), w.cuda(), swiglu=True)
+    assert got.shape == (M, F)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2 * max(1.0, float(want.abs().max()) / 4))
+    assert int(ops.tc_fault()[0]) == 0
+
+
+def test_tcgen05_gemm_refuses_what_tma_cannot_address():
+    ops = _ops()
+    a = torch.zeros(128, 36, dtype=torch.bfloat16).cuda()          # K not a multiple of 8
+    w = torch.zeros(36, 64, dtype=torch.bfloat16).cuda()
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.gemm_tc(a, w)
+    a = torch.zeros(128, 64, dtype=torch.bfloat16).cuda()
+    w = torch.zeros(64, 96, dtype=torch.bfloat16).cuda()           # gated columns come in blocks of 64
+    with pytest.raises(ops.KernelError, match="multiple of 64"):
+        ops.gemm_tc(a, w, swiglu=True)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_residual_add(dtype):
     ops = _ops()

@@ -121,6 +121,24 @@ def test_replay_at_the_sizes_of_the_0_9b_model(mode, dtype, tmp_path, tmp_path_f
     print(f"worst error {worst:.3g} at logit scale {scale:.3g}")
 
 
+def test_replay_with_the_tcgen05_products(tmp_path, tmp_path_factory, monkeypatch):
+    """The same replay with every product of 128 rows or more on the tcgen05 kernel (by default
+    only very long portions go there): whole prompts of 150 and 200 tokens in one step."""
+    from tiny_inference_server_b200.kernels import ops
+    monkeypatch.setattr(ops, "TC_MIN_ROWS", 128)
+    monkeypatch.setattr(ops, "TC_PLAIN_MIN_ROWS", 128)
+    cfg, page, folder, seqs, plain = _setup("WIDE", tmp_path_factory)
+    steps = _steps("whole", seqs)
+    runner = make_runner(folder, "bfloat16", trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True)
+    before = ops.launches
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    runner.check_fault()
+    scale = float(max(plain[r]["main"].abs().max() for r in plain))
+    _compare(cfg, steps, out_dir, seqs, plain, 1.5e-2 * scale)
+    assert ops._tc_fault is not None, "no product went to the tcgen05 kernel"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_from_cuda_graphs_equal_plain_launches(dtype, tmp_path, tmp_path_factory):
     """Steps of single tokens are replayed from captured graphs; the same trace without

@@ -16,6 +16,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.pages import CacheError, OutOfPages
 from ..config.engine_config import EngineConfig
+from ..kernels import ops
 from ..models.base import Model, StepOutput
 from ..parts.base import BuildContext
 from ..registry import build_model, config_from_folder
@@ -159,3 +160,6 @@ class ModelRunner:
         if code:
             self.fault.zero_()
             raise DeviceFault(f"a kernel met an invalid page id (code {code})")
+        if self.device.type == "cuda" and ops._tc_fault is not None and int(ops._tc_fault[0].item()):
+            ops._tc_fault.zero_()
+            raise DeviceFault("a wait inside a tcgen05 matrix product ran out")

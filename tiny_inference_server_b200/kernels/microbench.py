@@ -1,7 +1,8 @@
 """Runs single kernels at the shapes of a model, for timing and for profiler captures.
 
     python -m tiny_inference_server_b200.kernels.microbench attention --batch 8 --context 4096
-    python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8
+    python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8        (weight-streaming kernel)
+    python -m tiny_inference_server_b200.kernels.microbench gemm --rows 4096     (tcgen05 kernel, above 64 rows)
     python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
     python -m tiny_inference_server_b200.kernels.microbench all
 
@@ -94,10 +95,19 @@ def gemm(args):
         ws = [torch.randn(K, N, device=dev, dtype=torch.bfloat16) for _ in range(12)]
 
         def mine(i):
-            ops.gemm_skinny(inp, ws[i % 12], swiglu=fused)
+            if n > 64:
+                ops.gemm_tc(inp, ws[i % 12], swiglu=fused)
+            else:
+                ops.gemm_skinny(inp, ws[i % 12], swiglu=fused)
+
+        gu = torch.empty(n, N, device=dev, dtype=torch.bfloat16) if fused else None
+        half = torch.empty(n, N // 2, device=dev, dtype=torch.bfloat16) if fused else None
 
         def lib(i):
-            torch.mm(inp, ws[i % 12])
+            if fused:
+                ops.swiglu(torch.mm(inp, ws[i % 12], out=gu), half, 32)
+            else:
+                torch.mm(inp, ws[i % 12])
 
         if args.no_timing:
             for i in range(args.reps):
@@ -107,8 +117,8 @@ def gemm(args):
             continue
         a, b = _graph_time(mine), _graph_time(lib)
         mb = K * N * 2 / 1e6
-        print(f"gemm {name:15s} rows {n:3d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s)   "
-              f"library {b:7.2f} us")
+        print(f"gemm {name:15s} rows {n:4d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s, "
+              f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us")
 
 
 def prefill(args):

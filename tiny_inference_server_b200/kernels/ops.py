@@ -123,14 +123,58 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+#: The tcgen05 kernel of this library (csrc/gemm_tc.cu) against the library product, measured on a
+#: B200 at the 0.9B model's shapes (replayed from CUDA graphs, weights rotated through more than L2):
+#: gate/up with the SwiGLU gating in its epilogue it wins from about 3000 rows (4096 rows: 78 against
+#: 94 us for the library product plus the gating kernel; 2048 rows: 52 against 49 us); plain products
+#: it loses (2048 x 1536 x 4096: 28 against 19.5 us — one CTA per tile moves more bytes from L2 per
+#: multiply-add than the library's two-CTA tiles).  So by default it takes gate/up products of at
+#: least TC_MIN_ROWS rows and no plain ones; TIS_TC_MIN_ROWS / TIS_TC_PLAIN_MIN_ROWS in the
+#: environment override the two limits (0 = never).
+TC_MIN_ROWS = int(os.environ.get("TIS_TC_MIN_ROWS", "3072"))
+TC_PLAIN_MIN_ROWS = int(os.environ.get("TIS_TC_PLAIN_MIN_ROWS", "0"))
+_tc_fault = None
+
+
+def tc_fault() -> torch.Tensor:
+    """The fault word of the tcgen05 products (non-zero after a wait inside one ran out)."""
+    global _tc_fault
+    if _tc_fault is None:
+        _tc_fault = torch.zeros(4, dtype=torch.int32, device="cuda")
+    return _tc_fault
+
+
+def _tc_ok(a: torch.Tensor, w: torch.Tensor, min_rows: int) -> bool:
+    return (min_rows > 0 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and a.shape[0] >= min_rows and w.stride(1) == 1 and a.stride(1) == 1
+            and a.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+    """``a (n, K) @ w (K, N)`` in bfloat16 on the tcgen05 tensor cores (TMA-fed, accumulator in
+    tensor memory); with ``swiglu`` the columns of ``w`` are [32 gate | 32 up] blocks and the
+    result is (n, N/2)."""
+    lib = library()
+    n, k = a.shape
+    cols = w.shape[1]
+    if out is None:
+        out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    _check(lib.tis_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                           EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()), _stream()), lib)
+    return out
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Up to 64
-    bfloat16 rows go to the weight-streaming kernel of this library, everything else to the
-    library product."""
+    """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Few bfloat16
+    rows go to the weight-streaming kernel of this library, many to its tcgen05 kernel,
+    everything else to the library product."""
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
     if _skinny_ok(a, w):
         return gemm_skinny(a, w, out)
+    if _tc_ok(a, w, TC_PLAIN_MIN_ROWS) and (out is None or (out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)):
+        return gemm_tc(a, w, out)
     if out is None:
         return torch.mm(a, w)
     return torch.mm(a, w, out=out)
@@ -142,6 +186,8 @@ def gemm_swiglu(a: torch.Tensor, w_gu: torch.Tensor, hidden: int, block: int) ->
     gating in its epilogue; else the product and the gating kernel."""
     if block == 32 and _skinny_ok(a, w_gu):
         return gemm_skinny(a, w_gu, swiglu=True)
+    if block == 32 and _tc_ok(a, w_gu, TC_MIN_ROWS) and w_gu.shape[1] % 64 == 0:
+        return gemm_tc(a, w_gu, swiglu=True)
     gu = torch.mm(a, w_gu)
     out = torch.empty((a.shape[0], hidden), dtype=a.dtype, device=a.device)
     return swiglu(gu, out, block)
