@@ -64,18 +64,31 @@ def _rotate(x, cos, sin, interleaved):
     return y
 
 
+def _chunk_places(nch, positions):
+    """physical chunk of logical chunk c for rows at ``positions``: (L, nch).  Rows of a multiple
+    of eight chunks: c XOR (position mod 8); other rows: (c + position) mod chunks."""
+    c = torch.arange(nch)[None, :]
+    pos = torch.as_tensor(positions).reshape(-1, 1)
+    return (c ^ (pos & 7)) if nch % 8 == 0 else (c + pos) % nch
+
+
 def cache_row(x, pos):
     """The cache's row format: a row of keys or values (last axis: head size) is stored as
-    16-byte chunks rotated by the position, logical chunk c at chunk (c + pos) mod chunks."""
+    16-byte chunks permuted by the position."""
     n = 16 // x.element_size()
     hd = x.shape[-1]
-    return x.reshape(*x.shape[:-1], hd // n, n).roll(pos % (hd // n), dims=-2).reshape(x.shape)
+    place = _chunk_places(hd // n, [pos])[0]
+    chunks = x.reshape(*x.shape[:-1], hd // n, n)
+    out = torch.empty_like(chunks)
+    out[..., place, :] = chunks
+    return out.reshape(x.shape)
 
 
 def cache_row_inverse(x, pos):
     n = 16 // x.element_size()
     hd = x.shape[-1]
-    return x.reshape(*x.shape[:-1], hd // n, n).roll(-(pos % (hd // n)), dims=-2).reshape(x.shape)
+    place = _chunk_places(hd // n, [pos])[0]
+    return x.reshape(*x.shape[:-1], hd // n, n)[..., place, :].reshape(x.shape)
 
 
 def rope_kv_write(qkv, positions, row_slot, cos, sin, plane, block_table, num_heads, kv_heads, head_dim,
@@ -117,7 +130,7 @@ def _unrotate_rows(x, positions):
     L, kvh, hd = x.shape
     nch = hd // n
     chunks = x.reshape(L, kvh, nch, n).permute(0, 2, 1, 3)                       # (L, nch, KVH, n)
-    phys = (torch.arange(nch)[None, :] + positions[:, None]) % nch               # logical c -> physical chunk
+    phys = _chunk_places(nch, positions)                                         # logical c -> physical chunk
     out = chunks[torch.arange(L)[:, None], phys]                                 # (L, nch, KVH, n)
     return out.permute(0, 2, 1, 3).reshape(L, kvh, hd)
 

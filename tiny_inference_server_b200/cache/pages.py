@@ -9,12 +9,14 @@ block table per request slot.  A page id addresses the same page in every plane 
 group, as upstream's does in every layer.
 
 Row format.  Inside a page the keys (and the values) of one kv head are ``page_size`` rows
-of ``head_dim`` elements.  Each row is stored as 16-byte chunks *rotated by the token's
-position*: logical chunk ``c`` lies at chunk ``(c + position) mod chunks_per_row``
-(``cache_chunk`` in ``csrc/common.cuh``).  The attention kernels copy a page's rows into
-shared memory unchanged, in one bulk copy, and the rotation is what lets them read the
-dense rows there without bank conflicts.  Only kernels read and write the pages; anything
-else that does (tests) has to apply the same rotation.
+of ``head_dim`` elements.  Each row is stored as 16-byte chunks *permuted by the token's
+position* (``cache_chunk`` in ``csrc/common.cuh``): rows of a multiple of eight chunks keep
+logical chunk ``c`` at chunk ``c XOR (position mod 8)`` — the 128-byte swizzle of the
+tensor-core operand layouts, applied in memory — other rows at chunk
+``(c + position) mod chunks_per_row``.  The attention kernels copy a page's rows into shared
+memory unchanged, in bulk copies, and the permutation is what lets them read the dense rows
+there without bank conflicts, or hand them to the tensor cores as they are.  Only kernels
+read and write the pages; anything else that does (tests) has to apply the same permutation.
 """
 from __future__ import annotations
 

@@ -16,7 +16,7 @@
 //
 // Keys and values of 64 positions are staged in shared memory by the TMA engine: one bulk
 // copy (cp.async.bulk) per page's share of the tile (any page size), counted on an mbarrier
-// per stage.  The cache stores each row with its 16-byte chunks rotated by the position
+// per stage.  The cache stores each row with its 16-byte chunks permuted by the position
 // (common.cuh), so the rows can lie dense in shared memory, exactly as copied, and ldmatrix
 // still meets no bank conflict (head sizes 64, 128, 256; a few two-way conflicts at others).
 // Every wait on an mbarrier is bounded; one that runs out sets the fault word.
@@ -45,7 +45,7 @@ constexpr int STAGES = TIS_ATTN_STAGES;
 #else
 constexpr int STAGES = 2;
 #endif
-constexpr int NCH = HD / 8;          // 16-byte chunks of a cache row (rotated by the position: common.cuh)
+constexpr int NCH = HD / 8;          // 16-byte chunks of a cache row (permuted by the position: common.cuh)
 constexpr int KSTEPS = HD / 16;      // k16 steps of Q.K^T
 constexpr int DTILES = HD / 8;       // n8 tiles of the output
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
@@ -329,7 +329,7 @@ attn_mma_kernel(const AttnParams p) {
                 for (int kk = 0; kk < KSTEPS; ++kk) {
                     unsigned b[4];
                     const int key = kofs + j * 8 + ((lane >> 4) << 3) + (lane & 7);
-                    const int chunk = (2 * kk + ((lane >> 3) & 1) + kt + key) % NCH;     // rotated by the position
+                    const int chunk = cache_chunk(2 * kk + ((lane >> 3) & 1), kt + key, NCH);   // permuted by the position
                     ldmatrix_x4(b, ks + key * RS + chunk * 8);
                     mma_bf16(s[j], qa[kk], b[0], b[1]);
                     mma_bf16(s[j + 1], qa[kk], b[2], b[3]);
@@ -408,7 +408,7 @@ attn_mma_kernel(const AttnParams p) {
 #pragma unroll
                 for (int d = 0; d < DTILES; d += 2) {
                     unsigned b[4];
-                    ldmatrix_x4_trans(b, vs + key * RS + ((d + (lane >> 4) + kt + key) % NCH) * 8);
+                    ldmatrix_x4_trans(b, vs + key * RS + cache_chunk(d + (lane >> 4), kt + key, NCH) * 8);
                     mma_bf16(o[d], pa, b[0], b[1]);
                     mma_bf16(o[d + 1], pa, b[2], b[3]);
                 }

@@ -7,26 +7,24 @@
 // Keys are taken 128 at a time: every thread scores one key, the CTA agrees on the new
 // running maximum, then the threads split the head dimension and add the 128 weighted
 // value rows (online softmax, as paged_attention_kernels.py:88-111 upstream, in base e).
-// Cache rows are stored with their 16-byte chunks rotated by the position (common.cuh).
+// Cache rows are stored with their 16-byte chunks permuted by the position (common.cuh).
 #include "common.cuh"
 
 #define SIMT_KEYS 128
 
-// q . k for one cache row of position `pos`: the row's 16-byte chunks are rotated by the
-// position (common.cuh), so physical chunk pc holds logical chunk (pc - pos) mod chunks.
+// q . k for one cache row of position `pos`: the row's 16-byte chunks are permuted by the
+// position (cache_chunk in common.cuh).
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd, int pos) {
     constexpr int N = Vec16<T>::N;
     const int nch = hd / N;
-    int c = (nch - pos % nch) % nch;           // logical chunk of physical chunk 0
     float acc = 0.f;
-    for (int pc = 0; pc < nch; ++pc) {
+    for (int c = 0; c < nch; ++c) {
         float v[N];
-        Vec16<T>::load(k + pc * N, v);
+        Vec16<T>::load(k + cache_chunk(c, pos, nch) * N, v);
         const float* qq = q + c * N;
 #pragma unroll
         for (int j = 0; j < N; ++j) acc += qq[j] * v[j];
-        c = (c + 1 == nch) ? 0 : c + 1;
     }
     return acc;
 }

@@ -65,11 +65,15 @@ template <> struct Vec16<bf16> {
 
 // ---- cache row format ---------------------------------------------------------------------
 // A cache row (keys or values of one position and kv head: hd elements) is stored as 16-byte
-// chunks rotated by the position: logical chunk c lies at chunk (c + position) mod (chunks per
-// row).  A run of rows copied unchanged into shared memory (one bulk copy per page) can then
-// be read by ldmatrix without bank conflicts, with no padding between rows.
+// chunks permuted by the position.  Rows of a multiple of eight chunks (head sizes that are
+// multiples of 64 in bfloat16): logical chunk c lies at chunk c XOR (position mod 8), the
+// 128-byte swizzle of the tensor-core operand layouts applied in memory.  Other rows: at chunk
+// (c + position) mod (chunks per row).  Either way a run of rows copied unchanged into shared
+// memory (one bulk copy per page) is read by ldmatrix without bank conflicts, with no padding
+// between rows; and a box of 64 elements x 8k rows of the first kind, copied by the TMA engine
+// without swizzling, is at once the canonical 128-byte-swizzled operand tile of tcgen05.mma.
 __device__ __forceinline__ int cache_chunk(int logical_chunk, int position, int chunks_per_row) {
-    return (logical_chunk + position) % chunks_per_row;
+    return (chunks_per_row & 7) == 0 ? (logical_chunk ^ (position & 7)) : (logical_chunk + position) % chunks_per_row;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

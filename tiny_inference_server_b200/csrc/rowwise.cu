@@ -123,7 +123,7 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
 // qkv row layout: [H*hd queries | KVH*hd keys | KVH*hd values] (keys before values, as
 // the upstream kv_proj: main_models_new.py:104-106).  q is rotated in place.
 // plane layout: [page][2 (k, v)][KVH][page_size][hd]; inside a row the 16-byte chunks are
-// rotated by the position (cache_chunk in common.cuh).
+// permuted by the position (cache_chunk in common.cuh).
 // pairing: half-split (i, i + rot/2) as upstream rotate_half (main_models_new.py:71-73),
 // or interleaved (2i, 2i+1); only the first `rot` entries of a head are rotated.
 // cos/sin tables: [positions][rot/2] float.
