@@ -29,9 +29,9 @@ def test_lagging_stages_mask_negative_positions():
 
 @pytest.mark.parametrize("g", [1, 2, 3, 4, 8, 16, 20, 64])
 def test_tiles_cover_every_row_once(g):
-    segs = [(0, 1), (1, 200), (201, 3), (204, 16), (220, 1), (221, 65)]
-    keys, rows = plan_tiles(segs, g)
-    seen = np.zeros(286, dtype=int)
+    segs = [(0, 1), (1, 200), (201, 3), (204, 16), (220, 1), (221, 65), (286, 300)]
+    keys, rows, wide, rows_in_wide = plan_tiles(segs, g)
+    seen = np.zeros(586, dtype=int)
     for r0, n in keys:
         assert n * g <= 16
         seen[r0:r0 + n] += 1
@@ -39,6 +39,17 @@ def test_tiles_cover_every_row_once(g):
         assert n * g <= 64 or n == 1
         seen[r0:r0 + n] += 1
     assert (seen == 1).all()
+    # the wide tiles cover the long segments once more, and exactly the leading rows tiles
+    again = np.zeros(586, dtype=int)
+    for r0, n in wide:
+        assert 0 < n <= 128
+        again[r0:r0 + n] += 1
+    lead = np.zeros(586, dtype=int)
+    for r0, n in rows[:rows_in_wide]:
+        lead[r0:r0 + n] += 1
+    assert (again == lead).all()
+    for r0, n in segs:
+        assert again[r0:r0 + n].sum() == (n if n >= 64 and not (g <= 16 and n * g <= 16) else 0)
 
 
 def test_token_ids_outside_the_vocabulary_are_refused():

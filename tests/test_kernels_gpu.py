@@ -487,3 +487,76 @@ def test_paged_attention_whole_long_prompt(H, KVH, hd, page, window):
                               table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault_dev, Step())
     torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
     assert int(fault_dev[0]) == 0
+
+
+@pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (4, 1, 64, 16, None), (6, 2, 128, 64, None),
+                                                  (2, 2, 64, 128, None), (8, 2, 128, 32, 150), (5, 5, 64, 16, 70)])
+def test_tcgen05_attention(H, KVH, hd, page, window):
+    """The tcgen05 kernel for long portions (tiles of up to 128 rows): a prompt from its start,
+    a portion deep inside a context, a tile of a single key tile, leading padding rows of a
+    stage that runs behind (slot -1), and one key made to stand out far back; compared with the
+    plain reference and with the mma.sync kernel on the same rows."""
+    from tiny_inference_server_b200.engine.batch import infer_tiles, TileSet
+    ops = _ops()
+    g = torch.Generator().manual_seed(21)
+    dtype = torch.bfloat16
+    lens = [1400, 100, 300]
+    plane, table = _fill_cache(dtype, lens, KVH, hd, page, g)
+    # one key of slot 0 far back that every later row of head 0 must find: scale its key up
+    far = 5 * page
+    pg = int(table[0, far // page])
+    marker = torch.zeros(hd)
+    marker[3] = 40.0
+    plane[pg, 0, 0, far % page] = ref.cache_row(marker.to(dtype), far)
+    rows = [(0, p) for p in range(1000, 1300)]             # a portion of 300 rows deep inside: tiles 128+128+44
+    rows += [(1, p) for p in range(100)]                   # a prompt from its start: one tile, one key tile
+    rows += [(-1, 0), (-1, 0)] + [(2, p) for p in range(298)]   # a stage two positions behind: padding first
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    q = _rand((n, (H + 2 * KVH) * hd), dtype, g)
+    q[:300, 3] = 8.0                                       # head 0 of the deep portion looks along the marker
+    fault = torch.zeros(4, dtype=torch.int32)
+    want = ref.paged_attention(q, torch.empty(n, H * hd, dtype=dtype), plane, table, positions, row_slot, H, KVH, hd,
+                               page, window, fault)
+    # the tiles as the engine makes them: the padding rows belong to the segment that follows them
+    tiles = infer_tiles(positions.cuda(), row_slot.cuda(), H // KVH)
+    segs = [(0, 300), (300, 100), (400, 300)]
+    from tiny_inference_server_b200.engine.batch import plan_tiles
+    keys, rws, wide, rows_in_wide = plan_tiles(segs, H // KVH)
+
+    def t(v):
+        return torch.tensor(v, dtype=torch.int32, device="cuda")
+
+    tiles = TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
+                    (t([k[0] for k in rws]), t([k[1] for k in rws]), len(rws)), max((k[1] for k in keys), default=0),
+                    (t([k[0] for k in wide]), t([k[1] for k in wide]), len(wide)), rows_in_wide)
+    assert len(wide) == 7
+
+    class Step:
+        max_position, min_position = 1299, 0
+
+        def attn_tiles(self, group):
+            return tiles
+
+    outs = {}
+    for tc in (True, False):
+        ops.TC_ATTENTION = tc
+        try:
+            fault_dev = fault.cuda()
+            launches = ops.launches
+            got = ops.paged_attention(q.cuda(), torch.full((n, H * hd), 7.0, dtype=dtype, device="cuda"), plane.cuda(),
+                                      table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window,
+                                      fault_dev, Step())
+            torch.cuda.synchronize()
+        finally:
+            ops.TC_ATTENTION = True
+        assert int(fault_dev[0]) == 0
+        outs[tc] = got.cpu().float()
+        valid = row_slot >= 0
+        torch.testing.assert_close(outs[tc][valid], want.float()[valid], rtol=2e-2, atol=2e-2)
+    if window is None:
+        # the far key wins for head 0 of the deep portion: its value row comes out
+        v_far = ref.cache_row_inverse(plane[pg, 1, 0, far % page], far).float()
+        torch.testing.assert_close(outs[True][:300, :hd], v_far.expand(300, hd), rtol=5e-2, atol=5e-2)
+    assert bool((outs[True][400:402] == 0).all()), "padding rows inside a tile are written as zeros"

@@ -35,32 +35,47 @@ class Segment:
     pos0: int
 
 
+#: rows from which a portion of a prompt is also cut into wide tiles
+WIDE_MIN_ROWS = 64
+WIDE_TILE_ROWS = 128
+
+
 class TileSet:
     """Attention work of one step for one group size G (query heads per kv head): tiles of
     consecutive rows of one request.  ``keys``: tiles of at most 16 // G rows (decode rows,
     tiny portions), whose keys are split over warps and CTAs; ``rows``: tiles of at most
     64 // G rows (portions of prompts).  Each is (first rows, row counts, number of tiles);
-    the first two are int32 device tensors."""
+    the first two are int32 device tensors.  ``wide``: the portions of at least WIDE_MIN_ROWS
+    rows once more, as tiles of up to 128 rows, for the kernel that takes those; their ``rows``
+    tiles are the first ``rows_in_wide`` of ``rows``, so a caller runs either ``wide`` and the
+    rest of ``rows``, or all of ``rows``."""
 
-    def __init__(self, keys, rows, keys_max_rows: int = 0):
+    def __init__(self, keys, rows, keys_max_rows: int = 0, wide=None, rows_in_wide: int = 0):
         self.keys = keys
         self.rows = rows
         self.keys_max_rows = keys_max_rows      # the most rows of any ``keys`` tile (0: not known)
+        self.wide = wide if wide is not None else (None, None, 0)
+        self.rows_in_wide = rows_in_wide
 
 
 def plan_tiles(segments: Sequence[Tuple[int, int]], group_size: int):
-    """Cut (row0, rows) segments into tiles.  Returns (keys tiles, rows tiles) as lists of
-    (row0, rows)."""
+    """Cut (row0, rows) segments into tiles.  Returns (keys tiles, rows tiles, wide tiles, number
+    of leading rows tiles that the wide tiles cover) with tiles as lists of (row0, rows)."""
     r_keys = 16 // group_size if group_size <= 16 else 0
     r_rows = max(1, 64 // group_size)
-    keys, rows = [], []
+    keys, rows_wide, rows_rest, wide = [], [], [], []
     for row0, n in segments:
         if r_keys and n <= r_keys:
             keys.append((row0, n))
-        else:
-            for a in range(0, n, r_rows):
-                rows.append((row0 + a, min(r_rows, n - a)))
-    return keys, rows
+            continue
+        into = rows_rest
+        if n >= WIDE_MIN_ROWS:
+            into = rows_wide
+            for a in range(0, n, WIDE_TILE_ROWS):
+                wide.append((row0 + a, min(WIDE_TILE_ROWS, n - a)))
+        for a in range(0, n, r_rows):
+            into.append((row0 + a, min(r_rows, n - a)))
+    return keys, rows_wide + rows_rest, wide, len(rows_wide)
 
 
 class StepContext:
@@ -186,12 +201,14 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
         put(f"slot{lag}", np.where(positions - lag >= 0, slots, -1))
     counts = {}
     for g in sorted(set(group_sizes)):
-        keys, rows = plan_tiles(seg_rows, g)
-        counts[g] = (len(keys), len(rows), max((t[1] for t in keys), default=0))
+        keys, rows, wide, rows_in_wide = plan_tiles(seg_rows, g)
+        counts[g] = (len(keys), len(rows), max((t[1] for t in keys), default=0), len(wide), rows_in_wide)
         put(f"k0_{g}", [t[0] for t in keys])
         put(f"kn_{g}", [t[1] for t in keys])
         put(f"r0_{g}", [t[0] for t in rows])
         put(f"rn_{g}", [t[1] for t in rows])
+        put(f"w0_{g}", [t[0] for t in wide])
+        put(f"wn_{g}", [t[1] for t in wide])
     if want_all:
         want_rows = list(range(n))
     put("want", want_rows)
@@ -238,17 +255,19 @@ def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seq
     ones = [1] * n
     for g in sorted(set(group_sizes)):
         if g <= 16:
-            counts[g] = (n, 0, 1)
+            counts[g] = (n, 0, 1, 0, 0)
             put(f"k0_{g}", rows)
             put(f"kn_{g}", ones)
             put(f"r0_{g}", [])
             put(f"rn_{g}", [])
         else:
-            counts[g] = (0, n, 0)
+            counts[g] = (0, n, 0, 0, 0)
             put(f"k0_{g}", [])
             put(f"kn_{g}", [])
             put(f"r0_{g}", rows)
             put(f"rn_{g}", ones)
+        put(f"w0_{g}", [])
+        put(f"wn_{g}", [])
     put("want", rows)
     max_pos = max(starts) if n_real else 0
     if max_position is not None:
@@ -265,8 +284,9 @@ def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[t
         a, k = lay.offsets[name]
         return dev[a:a + k]
 
-    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr), kmax)
-             for g, (nk, nr, kmax) in lay.tile_counts.items()}
+    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr), kmax,
+                        (view(f"w0_{g}"), view(f"wn_{g}"), nw), nrw)
+             for g, (nk, nr, kmax, nw, nrw) in lay.tile_counts.items()}
     stages: Dict[int, StepContext] = {}
     ctx = StepContext(lay.n, view("tokens"), view("positions"), view("slots"), view("last"), lay.segments,
                       block_tables, page_sizes, fault, lay.max_position, stages=stages,
@@ -346,7 +366,7 @@ def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int
             segs[-1] = (segs[-1][0], segs[-1][1] + 1)
         else:
             segs.append((r, 1))
-    keys, rows = plan_tiles(segs, group_size)
+    keys, rows, wide, rows_in_wide = plan_tiles(segs, group_size)
     dev = positions.device
 
     def t(v):
@@ -354,4 +374,5 @@ def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int
 
     return TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
                    (t([k[0] for k in rows]), t([k[1] for k in rows]), len(rows)),
-                   max((k[1] for k in keys), default=0))
+                   max((k[1] for k in keys), default=0),
+                   (t([k[0] for k in wide]), t([k[1] for k in wide]), len(wide)), rows_in_wide)

@@ -43,7 +43,7 @@ def _nvcc() -> str:
 
 
 #: sources compiled once per head size (-DTIS_HD=<hd>) into libraries of their own
-PER_HEAD_SIZE = ("attention_mma.cu",)
+PER_HEAD_SIZE = ("attention_mma.cu", "attention_tc.cu")
 
 
 def sources():
@@ -135,9 +135,9 @@ def build_attention(head_dim: int) -> str:
     work = tempfile.mkdtemp(prefix="tis_obj_", dir=root)
     try:
         _say(f"compiling the attention kernels for head size {head_dim} (first call only)")
-        jobs = [("attention_mma.cu", os.path.join(work, "attention_mma.o"), (f"-DTIS_HD={head_dim}",)),
-                ("errors.cu", os.path.join(work, "errors.o"), ())]
-        with ThreadPoolExecutor(max_workers=2) as ex:
+        jobs = [(src, os.path.join(work, src[:-3] + ".o"), (f"-DTIS_HD={head_dim}",)) for src in PER_HEAD_SIZE]
+        jobs.append(("errors.cu", os.path.join(work, "errors.o"), ()))
+        with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
             list(ex.map(lambda j: _compile_one(nvcc, *j), jobs))
         tmp_so = os.path.join(work, "lib.so")
         p = subprocess.run([nvcc, "-shared", "-o", tmp_so, *[j[1] for j in jobs]], capture_output=True, text=True)

@@ -1,6 +1,7 @@
 """Runs single kernels at the shapes of a model, for timing and for profiler captures.
 
     python -m tiny_inference_server_b200.kernels.microbench attention --batch 8 --context 4096
+    python -m tiny_inference_server_b200.kernels.microbench attention-prefill --tokens 2048
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8        (weight-streaming kernel)
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 4096     (tcgen05 kernel, above 64 rows)
     python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
@@ -82,6 +83,40 @@ def attention(args):
     print(f"attention decode  batch {B:3d} context {ctx}: {t:8.2f} us  {kv_bytes / t / 1e3:8.1f} GB/s of keys and values")
 
 
+def attention_prefill(args):
+    """Attention of one prompt of ``--tokens`` rows over its own keys (positions 0..tokens-1)."""
+    from ..engine.batch import infer_tiles
+    dev = "cuda"
+    H, KVH, hd, page, n = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
+    num_pages = (n + page - 1) // page
+    planes = [torch.randn(num_pages, 2, KVH, page, hd, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+    table = torch.arange(num_pages, dtype=torch.int32, device=dev).reshape(1, num_pages).contiguous()
+    positions = torch.arange(n, dtype=torch.int32, device=dev)
+    slots = torch.zeros(n, dtype=torch.int32, device=dev)
+    qkv = torch.randn(n, (H + 2 * KVH) * hd, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(n, H * hd, device=dev, dtype=torch.bfloat16)
+    fault = torch.zeros(4, dtype=torch.int32, device=dev)
+    step = _Step(infer_tiles(positions, slots, H // KVH), n - 1)
+    step.min_position = 0
+
+    def run(i):
+        ops.paged_attention(qkv, out, planes[i % 4], table, positions, slots, H, KVH, hd, page, None, fault, step)
+
+    flops = 4 * H * hd * n * (n + 1) / 2
+    if args.no_timing:
+        for i in range(args.reps):
+            run(i)
+        torch.cuda.synchronize()
+        print(f"attention prefill {n} rows: {args.reps} launches, fault {int(fault[0])}")
+        return
+    for tc in (True, False):
+        ops.TC_ATTENTION = tc
+        t = _graph_time(run, 10)
+        print(f"attention prefill {n:5d} rows, {'tcgen05 ' if tc else 'mma.sync'}: {t:8.2f} us  {flops / t / 1e6:7.1f} TFLOP/s  "
+              f"fault {int(fault[0])}")
+    ops.TC_ATTENTION = True
+
+
 def gemm(args):
     dev = "cuda"
     d, F, H, KVH, hd, n = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.rows
@@ -151,7 +186,7 @@ def prefill(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["attention", "gemm", "prefill", "all"])
+    ap.add_argument("what", choices=["attention", "attention-prefill", "gemm", "prefill", "all"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
@@ -172,6 +207,8 @@ def main(argv=None):
         for b in ([args.batch] if args.what == "attention" else [1, 8, 64]):
             args.batch = b
             attention(args)
+    if args.what in ("attention-prefill", "all"):
+        attention_prefill(args)
     if args.what in ("gemm", "all"):
         for n in ([args.rows] if args.what == "gemm" else [1, 8, 16]):
             args.rows = n

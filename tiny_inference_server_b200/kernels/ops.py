@@ -276,6 +276,11 @@ def attention_library(head_dim: int):
     return lib
 
 
+#: long prompt portions (tiles of up to 128 rows) go to the tcgen05 attention kernel where the head
+#: size (64, 128) and the page size (16..128) allow it; TIS_TC_ATTENTION=0 keeps them on the
+#: mma.sync kernel
+TC_ATTENTION = os.environ.get("TIS_TC_ATTENTION", "1") != "0"
+
 #: CTAs of the attention kernels that are resident at a time when the library cannot be asked
 #: (148 SMs, two CTAs each at head size 128)
 ATTN_RESIDENT_CTAS = 148 * 2
@@ -369,7 +374,17 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         from ..engine.batch import infer_tiles
         tiles = infer_tiles(positions, row_slot, g)
         max_kv = int(positions.max().item()) + 1 if n else 1
-    for mode, (row0, rows, count) in ((1, tiles.keys), (0, tiles.rows)):
+    rows_tiles = tiles.rows
+    w0, wn, wide_count = getattr(tiles, "wide", (None, None, 0))
+    if wide_count and TC_ATTENTION and page_size in (16, 32, 64, 128) and alib.tis_attn_tc_supported():
+        # long portions: the tcgen05 kernel takes them as tiles of 128 rows; the others stay below
+        _check(alib.tis_attn_tc(_p(q), q.stride(0), n, _p(out), out.stride(0), _p(plane), _p(block_table),
+                                block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(w0), _p(wn),
+                                wide_count, num_heads, kv_heads, page_size, int(window or 0), _f(scale), _p(fault),
+                                _stream()), alib)
+        skip = tiles.rows_in_wide
+        rows_tiles = (tiles.rows[0][skip:], tiles.rows[1][skip:], tiles.rows[2] - skip)
+    for mode, (row0, rows, count) in ((1, tiles.keys), (0, rows_tiles)):
         if count == 0:
             continue
         max_rows = tiles.keys_max_rows if mode == 1 else 0
