@@ -166,18 +166,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) {
             constexpr unsigned IDESC_S = instr_desc(BM, BN, false);
             constexpr unsigned IDESC_O = instr_desc(BM, HD, true);
-            const unsigned q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem), k0_addr = smem_u32(k_slots), v0_addr = smem_u32(v_slots);
+            const unsigned long long q_desc0 = smem_desc(smem_u32(q_smem), 16, 1024);
+            const unsigned long long p_desc0 = smem_desc(smem_u32(p_smem), 16, 1024);
+            const unsigned long long k_desc0 = smem_desc(smem_u32(k_slots), 16, 1024);
+            const unsigned long long v_desc0 = smem_desc(smem_u32(v_slots), HALF_BYTES, 1024);
             bool ok = mbar_wait(&q_full, 0, abort, p.fault, 6);
             auto scores = [&](int j) -> bool {            // S_j = Q K_j^T into score buffer j & 1
                 const int s = j % SLOTS;
                 if (!mbar_wait(&full_k[s], (j / SLOTS) & 1, abort, p.fault, 6)) return false;
-                fence_after();
-                const unsigned k_addr = k0_addr + s * SLOT_BYTES;
+                // descriptors differ from the tile's first one only in the start address (units of 16 bytes)
+                const unsigned long long kd = k_desc0 + (unsigned long long)((s * SLOT_BYTES) >> 4);
+                const unsigned d = tmem_base + COL_S + (j & 1) * BN;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const unsigned off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    umma(tmem_base + COL_S + (j & 1) * BN, smem_desc(q_addr + off, 16, 1024),
-                         smem_desc(k_addr + off, 16, 1024), IDESC_S, kk != 0);
+                    const unsigned long long off = (unsigned long long)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
+                    umma(d, q_desc0 + off, kd + off, IDESC_S, kk != 0);
                 }
                 umma_commit(&empty_k[s]);
                 umma_commit(&s_full[j & 1]);
@@ -191,11 +194,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (!mbar_wait(&p_full[g], i & 1, abort, p.fault, 6)) break;
                 if (!mbar_wait(&full_v[s], (j / SLOTS) & 1, abort, p.fault, 6)) break;
                 fence_after();
-                const unsigned v_addr = v0_addr + s * SLOT_BYTES, pg_addr = p_addr + g * P_BYTES;
+                const unsigned long long vd = v_desc0 + (unsigned long long)((s * SLOT_BYTES) >> 4);
+                const unsigned long long pd = p_desc0 + (unsigned long long)((g * P_BYTES) >> 4);
+                const unsigned d = tmem_base + COL_O + g * 128;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {    // 16 keys: 32 bytes along a row of P, 16 rows of V
-                    umma(tmem_base + COL_O + g * 128, smem_desc(pg_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024),
-                         smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), IDESC_O, (i | kk) != 0);
+                    umma(d, pd + (unsigned long long)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4),
+                         vd + (unsigned long long)((kk * 2048) >> 4), IDESC_O, (i | kk) != 0);
                 }
                 umma_commit(&empty_v[s]);
                 umma_commit(&o_done[g]);
