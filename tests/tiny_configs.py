@@ -34,6 +34,13 @@ TINY_D = dict(architecture="gqa_mtp_transformer", vocab_size=200, hidden_size=48
               cache_source=[None, None, 1])
 TINY_D_PAGE = 16
 
+# heads of 64 (the smaller of the two head sizes that the tcgen05 attention kernel takes), 3 query heads per kv
+# head, pages of 32, a window of 100 keys on the second layer: prompts of more than 64 tokens run that kernel
+TINY_E = dict(architecture="gqa_mtp_transformer", vocab_size=777, hidden_size=192, num_layers=2, num_heads=6,
+              num_kv_heads=2, head_dim=64, ffn_hidden=320, rms_norm_eps=1e-5, rope_theta=50000.0, max_context=512,
+              tie_word_embeddings=False, num_mtp_heads=1, sliding_window=100, full_attention_layers=[0])
+TINY_E_PAGE = 32
+
 # the layer sizes of the upstream 0.9B model (Config/config.py:11-23), two layers and one MTP head of them
 WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=2, num_heads=12,
             num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
@@ -41,7 +48,7 @@ WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=15
 WIDE_PAGE = 16
 
 ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
-       "D": (TINY_D, TINY_D_PAGE, 3), "WIDE": (WIDE, WIDE_PAGE, 4)}
+       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 5), "WIDE": (WIDE, WIDE_PAGE, 4)}
 
 
 def make_model_folder(cfg_dict: dict, seed: int, folder: str, std: float = 0.02) -> str:
