@@ -491,7 +491,7 @@ def test_paged_attention_whole_long_prompt(H, KVH, hd, page, window):
 
 @pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (4, 1, 64, 16, None), (6, 2, 128, 64, None),
                                                   (2, 2, 64, 128, None), (8, 2, 128, 32, 150), (5, 5, 64, 16, 70)])
-def test_tcgen05_attention(H, KVH, hd, page, window):
+def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
     """The tcgen05 kernel for long portions (tiles of up to 128 rows): a prompt from its start,
     a portion deep inside a context, a tile of a single key tile, leading padding rows of a
     stage that runs behind (slot -1), and one key made to stand out far back; compared with the
@@ -539,6 +539,7 @@ def test_tcgen05_attention(H, KVH, hd, page, window):
         def attn_tiles(self, group):
             return tiles
 
+    monkeypatch.setattr(ops, "TC_ATTENTION_MIN_TILES", 1)     # also where the mma.sync kernel would be chosen
     outs = {}
     for tc in (True, False):
         ops.TC_ATTENTION = tc

@@ -219,12 +219,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const unsigned lane_bits = (unsigned)(quarter * 32) << 16;
         const unsigned col_s = COL_S + g * BN, col_o = COL_O + g * 128;
         unsigned char* pg_smem = p_smem + g * P_BYTES;
+        const bool warp_has_rows = __any_sync(0xffffffffu, row_ok);
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true;
         int i = 0;                                        // tiles of this group so far
         for (int j = g; j < T; j += 2, ++i) {
             if (!__all_sync(0xffffffffu, mbar_wait(&s_full[g], i & 1, abort, p.fault, 6))) { ok = false; break; }
             fence_after();
+            if (!warp_has_rows) {
+                // a warp whose 32 rows are all beyond the tile: its rows of P are zero, once and for all
+                if (i == 0) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        *reinterpret_cast<uint4*>(pg_smem + r * 128 + (c >> 3) * HALF_BYTES + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[g]);
+                continue;
+            }
             const int kt = tile_begin + j * BN;
             // Two passes over the row of S, 64 columns at a time (the row stays in tensor memory until
             // this group hands P over): first the maximum, then the exponentials.

@@ -84,31 +84,33 @@ def attention(args):
 
 
 def attention_prefill(args):
-    """Attention of one prompt of ``--tokens`` rows over its own keys (positions 0..tokens-1)."""
+    """Attention of one portion of ``--tokens`` rows at positions start..start+tokens-1 of a prompt
+    (``--start 0``: a prompt over its own keys)."""
     from ..engine.batch import infer_tiles
     dev = "cuda"
     H, KVH, hd, page, n = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
-    num_pages = (n + page - 1) // page
+    num_pages = (args.start + n + page - 1) // page
     planes = [torch.randn(num_pages, 2, KVH, page, hd, device=dev, dtype=torch.bfloat16) for _ in range(4)]
     table = torch.arange(num_pages, dtype=torch.int32, device=dev).reshape(1, num_pages).contiguous()
-    positions = torch.arange(n, dtype=torch.int32, device=dev)
+    positions = torch.arange(args.start, args.start + n, dtype=torch.int32, device=dev)
     slots = torch.zeros(n, dtype=torch.int32, device=dev)
     qkv = torch.randn(n, (H + 2 * KVH) * hd, device=dev, dtype=torch.bfloat16)
     out = torch.empty(n, H * hd, device=dev, dtype=torch.bfloat16)
     fault = torch.zeros(4, dtype=torch.int32, device=dev)
-    step = _Step(infer_tiles(positions, slots, H // KVH), n - 1)
-    step.min_position = 0
+    step = _Step(infer_tiles(positions, slots, H // KVH), args.start + n - 1)
+    step.min_position = args.start
 
     def run(i):
         ops.paged_attention(qkv, out, planes[i % 4], table, positions, slots, H, KVH, hd, page, None, fault, step)
 
-    flops = 4 * H * hd * n * (n + 1) / 2
+    flops = 4 * H * hd * (n * (n + 1) / 2 + n * args.start)
     if args.no_timing:
         for i in range(args.reps):
             run(i)
         torch.cuda.synchronize()
         print(f"attention prefill {n} rows: {args.reps} launches, fault {int(fault[0])}")
         return
+    ops.TC_ATTENTION_MIN_TILES = 1            # time both kernels whatever the choice would be
     for tc in (True, False):
         ops.TC_ATTENTION = tc
         t = _graph_time(run, 10)
@@ -191,6 +193,7 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--start", type=int, default=0, help="attention-prefill: first position of the portion")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--only", default=None, help="gemm: one of qkv, o, gate_up+swiglu, down")
     ap.add_argument("--width", type=int, default=1536)

@@ -280,6 +280,8 @@ def attention_library(head_dim: int):
 #: size (64, 128) and the page size (16..128) allow it; TIS_TC_ATTENTION=0 keeps them on the
 #: mma.sync kernel
 TC_ATTENTION = os.environ.get("TIS_TC_ATTENTION", "1") != "0"
+TC_ATTENTION_MIN_TILES = 2
+TC_ATTENTION_SHORT_CONTEXT = 1024
 
 #: CTAs of the attention kernels that are resident at a time when the library cannot be asked
 #: (148 SMs, two CTAs each at head size 128)
@@ -376,7 +378,12 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         max_kv = int(positions.max().item()) + 1 if n else 1
     rows_tiles = tiles.rows
     w0, wn, wide_count = getattr(tiles, "wide", (None, None, 0))
-    if wide_count and TC_ATTENTION and page_size in (16, 32, 64, 128) and alib.tis_attn_tc_supported():
+    # One CTA of the tcgen05 kernel walks all keys of its 128 rows (no key splits yet).  Measured at the
+    # 0.9B sizes: with two or more such tiles in the step it wins (256 rows ending at 4096: 51 against
+    # 84 us), a single tile deep inside a long context is faster on the mma.sync kernel, which splits
+    # the keys over a cluster (128 rows ending at 4096: 51 against 34 us; ending at 1024: a tie).
+    tc_pays = wide_count >= TC_ATTENTION_MIN_TILES or max_kv <= TC_ATTENTION_SHORT_CONTEXT
+    if wide_count and TC_ATTENTION and tc_pays and page_size in (16, 32, 64, 128) and alib.tis_attn_tc_supported():
         # long portions: the tcgen05 kernel takes them as tiles of 128 rows; the others stay below
         _check(alib.tis_attn_tc(_p(q), q.stride(0), n, _p(out), out.stride(0), _p(plane), _p(block_table),
                                 block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(w0), _p(wn),
