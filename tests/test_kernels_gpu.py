@@ -41,7 +41,8 @@ def test_embed_rows(dtype, n, d, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,d", [(1, 48), (7, 120), (19, 1536), (3, 4100), (2, 16384)])
+@pytest.mark.parametrize("n,d", [(1, 48), (7, 120), (19, 1536), (3, 4100), (2, 16384), (1024, 1536), (1203, 120), (1030, 2048),
+                                 (1025, 264), (1026, 2056), (1100, 8)])
 @pytest.mark.parametrize("with_delta", [False, True])
 def test_add_rmsnorm(dtype, n, d, with_delta):
     ops = _ops()
@@ -229,6 +230,23 @@ def test_rope_kv_write(dtype, H, KVH, hd, page, rot, inter):
     assert int(fault_dev[0]) == 0
     # the padding row wrote nothing and was not rotated
     assert torch.equal(qkv_dev.cpu()[9], qkv[9])
+
+    # many rows (a warp per row): 70 rows of one request at positions 3..72, a padding row in the middle
+    n2 = 71
+    table2 = _scattered_tables(1, 80 // page + 1, 80 // page + 4, g)
+    qkv2 = _rand((n2, (H + 2 * KVH) * hd), dtype, g)
+    pos2 = torch.tensor(list(range(3, 40)) + [0] + list(range(40, 73)), dtype=torch.int32)
+    slot2 = torch.tensor([0] * 37 + [-1] + [0] * 33, dtype=torch.int32)
+    plane2 = torch.zeros(80 // page + 4, 2, KVH, page, hd, dtype=dtype)
+    q_ref, p_ref = qkv2.clone(), plane2.clone()
+    ref.rope_kv_write(q_ref, pos2, slot2, cos, sin, p_ref, table2, H, KVH, hd, page, fault, interleaved=inter)
+    q_dev, p_dev = qkv2.cuda(), plane2.cuda()
+    ops.rope_kv_write(q_dev, pos2.cuda(), slot2.cuda(), cos.cuda(), sin.cuda(), p_dev, table2.cuda(), H, KVH, hd, page,
+                      fault_dev, interleaved=inter)
+    ok = slot2 >= 0
+    torch.testing.assert_close(q_dev.cpu()[ok].float(), q_ref[ok].float(), **tol)
+    torch.testing.assert_close(p_dev.cpu().float(), p_ref.float(), **tol)
+    assert torch.equal(q_dev.cpu()[37], qkv2[37]) and int(fault_dev[0]) == 0
 
 
 def test_rope_kv_write_reports_bad_page():

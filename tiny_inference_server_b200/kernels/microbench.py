@@ -2,6 +2,7 @@
 
     python -m tiny_inference_server_b200.kernels.microbench attention --batch 8 --context 4096
     python -m tiny_inference_server_b200.kernels.microbench attention-prefill --tokens 2048
+    python -m tiny_inference_server_b200.kernels.microbench rowwise --tokens 2048
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8        (weight-streaming kernel)
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 4096     (tcgen05 kernel, above 64 rows)
     python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
@@ -119,6 +120,38 @@ def attention_prefill(args):
     ops.TC_ATTENTION = True
 
 
+def rowwise(args):
+    """The memory-bound kernels between the products, at ``--tokens`` rows of the model's widths."""
+    dev = "cuda"
+    n, d, F, H, KVH, hd, page = args.tokens, args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size
+    bufs = 6                                                   # rotate buffers so that not everything stays in L2
+    res = [torch.randn(n, d, device=dev) for _ in range(bufs)]
+    delta = [torch.randn(n, d, device=dev, dtype=torch.bfloat16) for _ in range(bufs)]
+    normed = torch.empty(n, d, device=dev, dtype=torch.bfloat16)
+    scale = torch.ones(d, device=dev)
+    t = _graph_time(lambda i: ops.add_rmsnorm(res[i % bufs], delta[i % bufs], scale, 1e-6, normed), 12)
+    mb = n * d * (4 + 2 + 4 + 2) / 1e6
+    print(f"add_rmsnorm    {n} x {d}: {t:7.2f} us  {mb / t * 1e3:7.1f} GB/s")
+    gu = [torch.randn(n, 2 * F, device=dev, dtype=torch.bfloat16) for _ in range(bufs)]
+    hid = torch.empty(n, F, device=dev, dtype=torch.bfloat16)
+    t = _graph_time(lambda i: ops.swiglu(gu[i % bufs], hid, 32), 12)
+    mb = n * F * 6 / 1e6
+    print(f"swiglu         {n} x {F}: {t:7.2f} us  {mb / t * 1e3:7.1f} GB/s")
+    qkv = [torch.randn(n, (H + 2 * KVH) * hd, device=dev, dtype=torch.bfloat16) for _ in range(bufs)]
+    num_pages = (n + page - 1) // page
+    plane = torch.zeros(num_pages, 2, KVH, page, hd, device=dev, dtype=torch.bfloat16)
+    table = torch.arange(num_pages, dtype=torch.int32, device=dev).reshape(1, num_pages).contiguous()
+    positions = torch.arange(n, dtype=torch.int32, device=dev)
+    slots = torch.zeros(n, dtype=torch.int32, device=dev)
+    cos = torch.ones(n, hd // 2, device=dev)
+    sin = torch.zeros(n, hd // 2, device=dev)
+    fault = torch.zeros(4, dtype=torch.int32, device=dev)
+    t = _graph_time(lambda i: ops.rope_kv_write(qkv[i % bufs], positions, slots, cos, sin, plane, table, H, KVH, hd, page,
+                                                fault), 12)
+    mb = n * ((H + 2 * KVH) * hd * 2 + (H + 2 * KVH) * hd * 2) / 1e6
+    print(f"rope_kv_write  {n} rows: {t:7.2f} us  {mb / t * 1e3:7.1f} GB/s")
+
+
 def gemm(args):
     dev = "cuda"
     d, F, H, KVH, hd, n = args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.rows
@@ -188,7 +221,7 @@ def prefill(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["attention", "attention-prefill", "gemm", "prefill", "all"])
+    ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "all"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
@@ -212,6 +245,8 @@ def main(argv=None):
             attention(args)
     if args.what in ("attention-prefill", "all"):
         attention_prefill(args)
+    if args.what in ("rowwise", "all"):
+        rowwise(args)
     if args.what in ("gemm", "all"):
         for n in ([args.rows] if args.what == "gemm" else [1, 8, 16]):
             args.rows = n
