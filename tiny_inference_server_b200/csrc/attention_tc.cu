@@ -10,9 +10,10 @@
 //            and half of the head (lanes order the pages of a tile side by side).  The cache
 //            keeps rows XOR-swizzled by the position, so the boxes, copied as the bytes lie, are
 //            at once the swizzled operand tiles;
-//   warp 1   owns the tensor memory; one lane issues tcgen05.mma: S = Q K^T into one of two
-//            score buffers in tensor memory (keys as the K-major operand), and O += P V
-//            (values as the MN-major operand, P from shared memory);
+//   warps 1 and 11   issue the products (one lane each; warp 1 also owns the tensor memory):
+//            warp 1 S = Q K^T into one of two score buffers in tensor memory (keys as the K-major
+//            operand), warp 11 O += P V (values as the MN-major operand, P from shared memory);
+//            two issuing threads, so that one's wait for a barrier does not idle the tensor cores;
 //   warps 2-5 and 6-9: two softmax groups, one thread per query row each.  Even key tiles go
 //            to the first group, odd ones to the second, each with a score buffer, a P buffer,
 //            an output accumulator in tensor memory and running maximum and sum of its own, so
@@ -40,7 +41,7 @@ constexpr int HD = TIS_HD;
 constexpr int HALVES = HD / 64;             // 128-byte column blocks of a row
 constexpr int BM = 128;                     // query rows of a CTA
 constexpr int BN = 128;                     // keys of a tile
-constexpr int NTH = 352;
+constexpr int NTH = 384;
 constexpr int HALF_BYTES = 128 * 128;       // 128 rows x 128 bytes: one swizzled column block
 constexpr int Q_BYTES = HALVES * HALF_BYTES;
 constexpr int P_BYTES = 2 * HALF_BYTES;     // 128 rows x 128 keys, bfloat16 (one per softmax group)
@@ -162,35 +163,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        // ---- products ---------------------------------------------------------------------
+        // ---- products, first kind: S_j = Q K_j^T into score buffer j & 1 ----------------------------
         if (lane == 0) {
             constexpr unsigned IDESC_S = instr_desc(BM, BN, false);
-            constexpr unsigned IDESC_O = instr_desc(BM, HD, true);
             const unsigned long long q_desc0 = smem_desc(smem_u32(q_smem), 16, 1024);
-            const unsigned long long p_desc0 = smem_desc(smem_u32(p_smem), 16, 1024);
             const unsigned long long k_desc0 = smem_desc(smem_u32(k_slots), 16, 1024);
-            const unsigned long long v_desc0 = smem_desc(smem_u32(v_slots), HALF_BYTES, 1024);
             bool ok = mbar_wait(&q_full, 0, abort, p.fault, 6);
-            auto scores = [&](int j) -> bool {            // S_j = Q K_j^T into score buffer j & 1
-                const int s = j % SLOTS;
-                if (!mbar_wait(&full_k[s], (j / SLOTS) & 1, abort, p.fault, 6)) return false;
-                // descriptors differ from the tile's first one only in the start address (units of 16 bytes)
+            for (int j = 0; j < T && ok; ++j) {
+                const int g = j & 1, i = j >> 1, s = j % SLOTS;
+                // the group has read the scores of its tile before (it hands P over after that)
+                if (i > 0 && !mbar_wait(&p_full[g], (i - 1) & 1, abort, p.fault, 6)) break;
+                if (!mbar_wait(&full_k[s], (j / SLOTS) & 1, abort, p.fault, 6)) break;
+                fence_after();
+                // descriptors differ from the ring's first one only in the start address (units of 16 bytes)
                 const unsigned long long kd = k_desc0 + (unsigned long long)((s * SLOT_BYTES) >> 4);
-                const unsigned d = tmem_base + COL_S + (j & 1) * BN;
+                const unsigned d = tmem_base + COL_S + g * BN;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const unsigned long long off = (unsigned long long)(((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4);
                     umma(d, q_desc0 + off, kd + off, IDESC_S, kk != 0);
                 }
                 umma_commit(&empty_k[s]);
-                umma_commit(&s_full[j & 1]);
-                return true;
-            };
-            if (ok) ok = scores(0);
-            if (ok && T > 1) ok = scores(1);
-            for (int j = 0; j < T && ok; ++j) {
-                const int g = j & 1, i = j >> 1;          // softmax group and its tile count
-                const int s = j % SLOTS;
+                umma_commit(&s_full[g]);
+            }
+        }
+    } else if (warp == 11) {
+        // ---- products, second kind: O_g += P_j V_j.  An issuing thread of its own: while one thread
+        // waits for a barrier the other keeps the tensor cores fed. ------------------------------------
+        if (lane == 0) {
+            constexpr unsigned IDESC_O = instr_desc(BM, HD, true);
+            const unsigned long long p_desc0 = smem_desc(smem_u32(p_smem), 16, 1024);
+            const unsigned long long v_desc0 = smem_desc(smem_u32(v_slots), HALF_BYTES, 1024);
+            for (int j = 0; j < T; ++j) {
+                const int g = j & 1, i = j >> 1, s = j % SLOTS;
                 if (!mbar_wait(&p_full[g], i & 1, abort, p.fault, 6)) break;
                 if (!mbar_wait(&full_v[s], (j / SLOTS) & 1, abort, p.fault, 6)) break;
                 fence_after();
@@ -204,7 +209,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 umma_commit(&empty_v[s]);
                 umma_commit(&o_done[g]);
-                if (j + 2 < T && !scores(j + 2)) break;   // the group has read its score buffer
             }
         }
     } else {
