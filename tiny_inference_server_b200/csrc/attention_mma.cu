@@ -457,7 +457,61 @@ attn_mma_kernel(const AttnParams p) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
 
-    if (MODE == MODE_KEYS) {
+    if (MODE == MODE_KEYS && p.num_splits > 1 && p.cluster_merge) {
+        // The splits of this (tile, kv head) are the CTAs of one cluster.  Every warp of every split
+        // leaves its unnormalised partial result (maximum, sum, outputs) in its CTA's shared memory; after
+        // one cluster barrier every CTA merges its share of the output elements over all of them, reading
+        // the other CTAs' shared memory: one merge instead of one per CTA and one per cluster.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        constexpr int HDP = HD + 4;                              // padded rows: fewer bank conflicts on the way in
+        __syncthreads();                                         // the staging area is free
+        float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
+        float* mm = mo + 4 * 16 * HDP;                           // [4][16]
+        float* ml = mm + 4 * 16;                                 // [4][16]
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int m = g_lane + 8 * i;
+            if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
+            if (m_run[i] != -INFINITY) {
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d)
+                    *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+            }
+        }
+        cluster.sync();
+        const int ns = p.num_splits;
+        const int pairs = rows * G;
+        for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
+            const int m = idx / HD, d = idx - m * HD;
+            const int r = m / G, g = m - r * G;
+            float mt = -INFINITY;
+            for (int sp = 0; sp < ns; ++sp) {
+                const float* rm = cluster.map_shared_rank(mm, sp);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) mt = fmaxf(mt, rm[w * 16 + m]);
+            }
+            float acc = 0.f, lsum = 0.f;
+            if (mt != -INFINITY) {
+                for (int sp = 0; sp < ns; ++sp) {
+                    const float* rm = cluster.map_shared_rank(mm, sp);
+                    const float* rl = cluster.map_shared_rank(ml, sp);
+                    const float* ro = cluster.map_shared_rank(mo, sp);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float mw = rm[w * 16 + m];
+                        if (mw == -INFINITY) continue;
+                        const float f = fast_exp2(mw - mt);
+                        lsum += rl[w * 16 + m] * f;
+                        acc += ro[(w * 16 + m) * HDP + d] * f;
+                    }
+                }
+            }
+            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
+                __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        }
+        cluster.sync();                  // nobody leaves while its shared memory may still be read
+    } else if (MODE == MODE_KEYS) {
         // merge the four warps (each saw a quarter of the keys) through shared memory
         __syncthreads();
         float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HD]
@@ -695,7 +749,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 static size_t smem_bytes(int mode) {
     size_t stage = (size_t)STAGES * STAGE_BYTES;
-    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float)
+    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * (HD + 4) + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float)
                                      : (size_t)(64 * HD + 64) * sizeof(float);
     return stage > merge ? stage : merge;
 }
