@@ -165,6 +165,38 @@ def test_decode_steps_from_cuda_graphs_equal_plain_launches(dtype, tmp_path, tmp
             assert err < (2e-5 if dtype == "float32" else 3e-2), f"{rid} position {p}: {err}"
 
 
+@pytest.mark.parametrize("name,dtype", [("E", "bfloat16"), ("E", "float32"), ("B", "float32")])
+def test_portions_of_a_recurring_shape_from_cuda_graphs(name, dtype, tmp_path, tmp_path_factory):
+    """Prompts cut into portions of one fixed size: the shape of the step comes back, so from its
+    second occurrence on it is replayed from a captured graph (other positions, other pages, other
+    slots); every logit equals the plain implementation, as without graphs."""
+    from tiny_inference_server_b200.engine import StepEntry
+    cfg, page, folder, seqs, plain = _setup(name, tmp_path_factory)
+    chunk = 64
+    got = {}
+    for graphs in (True, False):
+        runner = make_runner(folder, dtype, 4096, page_size=page, mtp=False, cuda_graphs=graphs)
+        worst = 0.0
+        for rid, toks in seqs.items():
+            if len(toks) < 2 * chunk:
+                continue
+            slot = runner.add_request()
+            for a in range(0, len(toks) - chunk + 1, chunk):
+                out = runner.step([StepEntry(slot, toks[a:a + chunk], [0, chunk - 1])])
+                for k, pos in enumerate((a, a + chunk - 1)):
+                    err = float((out.main[k].float().cpu() - plain[rid]["main"][pos].float()).abs().max())
+                    worst = max(worst, err)
+                    got[(graphs, rid, pos)] = out.main[k].float().cpu().clone()
+            runner.release(slot)
+        runner.check_fault()
+        assert worst < TOL[dtype], f"graphs {graphs}: worst error {worst}"
+        if graphs:
+            assert runner.step_graphs is not None and runner.step_graphs.replays >= 3
+    for (graphs, rid, pos), v in got.items():
+        if graphs:
+            assert float((v - got[(False, rid, pos)]).abs().max()) < (2e-5 if dtype == "float32" else 3e-2)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(dtype, tmp_path, tmp_path_factory):
     """bin/trace_run over pipes: one step at a time, the next only after ``done <step>``."""

@@ -20,7 +20,7 @@ import torch
 from ..kernels import ops
 from ..models.base import StepOutput
 from ..sampling.sampler import WORDS_PER_ROW
-from .batch import StaticMeta, StepEntry, context_from_layout, layout_decode
+from .batch import StaticMeta, StepEntry, context_from_layout, layout_decode, layout_step
 
 
 def _next_pow2(x: int) -> int:
@@ -76,19 +76,8 @@ class GraphedDecode:
 
         out = run_once()
         torch.cuda.synchronize(r.device)
-        graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        # No garbage collection while the stream is capturing: the collector may destroy an
-        # older engine's graphs, and destroying a graph invalidates a capture in progress.
-        gc.collect()
-        was_enabled = gc.isenabled()
-        gc.disable()
-        try:
-            with torch.cuda.graph(graph):
-                self.out = run_once()
-        finally:
-            if was_enabled:
-                gc.enable()
+        graph, self.out = _capture(run_once)
         self.kernels = ops.launches - before
         ops.launches = before           # captured, not run
         self.graph = graph
@@ -129,3 +118,101 @@ class DecodeGraphs:
         idx = torch.tensor(wanted, dtype=torch.int64, device=r.device)
         return StepOutput(main=full.main.index_select(0, idx), aux=[a.index_select(0, idx) for a in full.aux],
                           aux_valid=[v.index_select(0, idx) for v in full.aux_valid], tokens=tokens)
+
+
+def _capture(run_once):
+    """Capture ``run_once`` into a CUDA graph; returns (graph, what run_once returned)."""
+    graph = torch.cuda.CUDAGraph()
+    # No garbage collection while the stream is capturing: the collector may destroy an
+    # older engine's graphs, and destroying a graph invalidates a capture in progress.
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            out = run_once()
+    finally:
+        if was_enabled:
+            gc.enable()
+    return graph, out
+
+
+class GraphedStep:
+    """One captured step of a fixed shape: the same number of entries with the same numbers of
+    tokens and the same wanted places, contexts up to ``kv_bound`` keys."""
+
+    def __init__(self, runner, kv_bound: int):
+        self.runner = runner
+        self.kv_bound = kv_bound
+        self.static: Optional[StaticMeta] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.out: Optional[StepOutput] = None
+        self.kernels = 0
+
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepOutput:
+        r = self.runner
+        lay = layout_step(entries, starts, r.lags, r.vocab_size, group_sizes=r.group_sizes,
+                          max_position=self.kv_bound - 1)
+        if self.static is None:
+            self.static = StaticMeta(len(lay.flat) + 16, r.device)
+        dev = self.static.upload(lay.flat, lay.offsets)
+        if self.graph is not None:
+            self.graph.replay()
+            ops.launches += self.kernels
+            return self.out
+        # first time: run the step as it is (this is the real step), then capture it
+        lay.min_position = 0            # planned for any positions up to the bound, not for this step's
+        ctx, want = context_from_layout(lay, dev, [g.table_dev for g in r.cache.groups],
+                                        [g.page_size for g in r.cache.groups], r.fault)
+
+        def run_once() -> StepOutput:
+            return r.model.forward(ctx, want, aux=r.aux)
+
+        out = run_once()
+        torch.cuda.synchronize(r.device)
+        before = ops.launches
+        self.graph, self.out = _capture(run_once)
+        self.kernels = ops.launches - before
+        ops.launches = before           # captured, not run
+        return out
+
+
+class StepGraphs:
+    """Graphs for steps other than decode-only ones (portions of prompts, mixed steps) whose shape
+    comes back: a server that cuts prompts into portions of its token budget runs the same shape
+    again and again.  A shape is captured when it is seen for the second time; the least recently
+    used graphs beyond ``capacity`` are dropped (each holds the step's activations)."""
+
+    def __init__(self, runner, capacity: int = 6, min_kv: int = 512):
+        self.runner = runner
+        self.capacity = capacity
+        self.min_kv = min_kv
+        self.seen: Dict[tuple, int] = {}
+        self.graphs: Dict[tuple, GraphedStep] = {}
+        self.replays = 0
+
+    def key(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> tuple:
+        r = self.runner
+        max_kv = max(s + len(e.tokens) for e, s in zip(entries, starts))
+        kv_bound = min(max(self.min_kv, _next_pow2(max_kv)), max(r.max_positions, max_kv))
+        return (kv_bound,) + tuple((len(e.tokens), tuple(e.want)) for e in entries)
+
+    def step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> Optional[StepOutput]:
+        """The step's output from a graph, or None: the caller runs the step eagerly."""
+        key = self.key(entries, starts)
+        g = self.graphs.get(key)
+        if g is None:
+            n = self.seen.get(key, 0) + 1
+            self.seen[key] = n
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            if n < 2:
+                return None
+            while len(self.graphs) >= self.capacity:
+                self.graphs.pop(next(iter(self.graphs)))
+            g = GraphedStep(self.runner, key[0])
+        else:
+            self.graphs.pop(key)        # re-inserted below: most recently used last
+            self.replays += 1
+        self.graphs[key] = g
+        return g.run(entries, starts)

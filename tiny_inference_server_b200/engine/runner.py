@@ -69,9 +69,11 @@ class ModelRunner:
         from ..sampling.sampler import Sampler
         self.sampler = Sampler(self.vocab_size, self.engine.max_batch, self.device, seed=self.engine.seed)
         self.graphs = None
+        self.step_graphs = None
         if self.engine.cuda_graphs and self.device.type == "cuda" and all(p.graph_safe for p in self.model.walk_parts()):
-            from .graphs import DecodeGraphs
+            from .graphs import DecodeGraphs, StepGraphs
             self.graphs = DecodeGraphs(self)
+            self.step_graphs = StepGraphs(self)
         self.steps_run = 0
         self.rows_run = 0
 
@@ -124,6 +126,13 @@ class ModelRunner:
             self.steps_run += 1
             self.rows_run += len(entries)
             return self.graphs.step(entries, starts, feed)
+        if self.step_graphs is not None and pad_to is None and feed is None and sum(len(e.tokens) for e in entries) >= 64:
+            out = self.step_graphs.step(entries, starts)
+            if out is not None:
+                self._sample(entries, out)
+                self.steps_run += 1
+                self.rows_run += sum(len(e.tokens) for e in entries)
+                return out
         ctx, want_rows, _ = build_step(entries, starts, self.lags,
                                        [g.table_dev for g in self.cache.groups],
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,

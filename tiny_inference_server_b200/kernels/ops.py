@@ -71,7 +71,14 @@ def _p(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """torch's current CUDA stream as a raw handle (the direct getter is 40 times cheaper than going
+    through a Stream object, and this runs once per launch)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -170,6 +177,40 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+#: bfloat16 library products go to cuBLAS directly (the same kernels as torch.mm, a third of the host
+#: time per call); TIS_LIBRARY_GEMM=torch sends them through torch.mm instead
+LIBRARY_GEMM_DIRECT = os.environ.get("TIS_LIBRARY_GEMM", "direct") != "torch"
+_blas_state = None          # None: not tried yet; False: unavailable; else the workspace tensor
+
+
+def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], f32_out: bool) -> Optional[torch.Tensor]:
+    """``a @ w`` by a direct cuBLAS call, or None when that is not possible (then torch.mm does it)."""
+    global _blas_state, launches
+    if not LIBRARY_GEMM_DIRECT or _blas_state is False:
+        return None
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or w.stride(1) != 1
+            or a.stride(0) < a.shape[1] or w.stride(0) < w.shape[1]):
+        return None
+    lib = library()
+    if _blas_state is None:
+        ws = torch.empty(32 << 20, dtype=torch.uint8, device=a.device)
+        _blas_state = ws if lib.tis_gemm_library_init(_p(ws), ctypes.c_size_t(ws.numel())) else False
+        if _blas_state is False:
+            return None
+    n, k = a.shape
+    cols = w.shape[1]
+    want = torch.float32 if f32_out else torch.bfloat16
+    if out is None:
+        out = torch.empty((n, cols), dtype=want, device=a.device)
+    elif out.dtype != want or out.stride(1) != 1 or out.stride(0) < cols:
+        return None
+    status = lib.tis_gemm_library(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                                  int(f32_out), _stream())
+    if status != 0:
+        raise KernelError(lib.tis_last_error().decode())
+    return out
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Few bfloat16
     rows go to the weight-streaming kernel of this library, many to its tcgen05 kernel,
@@ -180,6 +221,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -
         return gemm_skinny(a, w, out)
     if _tc_ok(a, w, TC_PLAIN_MIN_ROWS) and (out is None or (out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)):
         return gemm_tc(a, w, out)
+    direct = _library_gemm(a, w, out, False)
+    if direct is not None:
+        return direct
     if out is None:
         return torch.mm(a, w)
     return torch.mm(a, w, out=out)
@@ -193,7 +237,7 @@ def gemm_swiglu(a: torch.Tensor, w_gu: torch.Tensor, hidden: int, block: int) ->
         return gemm_skinny(a, w_gu, swiglu=True)
     if block == 32 and _tc_ok(a, w_gu, TC_MIN_ROWS) and w_gu.shape[1] % 64 == 0:
         return gemm_tc(a, w_gu, swiglu=True)
-    gu = torch.mm(a, w_gu)
+    gu = gemm(a, w_gu)
     out = torch.empty((a.shape[0], hidden), dtype=a.dtype, device=a.device)
     return swiglu(gu, out, block)
 
@@ -202,6 +246,9 @@ def gemm_f32_out(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``a (n, K) @ w (K, N)`` with a float32 result whatever the dtype of the operands."""
     if a.dtype == torch.float32:
         return gemm(a, w)
+    direct = _library_gemm(a, w, None, True)
+    if direct is not None:
+        return direct
     return torch.mm(a, w, out_dtype=torch.float32)
 
 
@@ -275,6 +322,7 @@ def attention_library(head_dim: int):
         lib.tis_last_error.restype = ctypes.c_char_p
         lib.tis_attn_scratch_floats.restype = ctypes.c_size_t
         lib.resident = {}
+        lib.tc_attention = bool(lib.tis_attn_tc_supported())
         if lib.tis_attn_head_dim() != head_dim:
             raise KernelError(f"attention library built for head size {lib.tis_attn_head_dim()}, wanted {head_dim}")
         _attn_libs[head_dim] = lib
@@ -388,14 +436,17 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     # 84 us), a single tile deep inside a long context is faster on the mma.sync kernel, which splits
     # the keys over a cluster (128 rows ending at 4096: 51 against 34 us; ending at 1024: a tie).
     tc_pays = wide_count >= TC_ATTENTION_MIN_TILES or max_kv <= TC_ATTENTION_SHORT_CONTEXT
-    if wide_count and TC_ATTENTION and tc_pays and page_size in (16, 32, 64, 128) and alib.tis_attn_tc_supported():
+    if wide_count and TC_ATTENTION and tc_pays and page_size in (16, 32, 64, 128) and alib.tc_attention:
         # long portions: the tcgen05 kernel takes them as tiles of 128 rows; the others stay below
         _check(alib.tis_attn_tc(_p(q), q.stride(0), n, _p(out), out.stride(0), _p(plane), _p(block_table),
                                 block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(w0), _p(wn),
                                 wide_count, num_heads, kv_heads, page_size, int(window or 0), _f(scale), _p(fault),
                                 _stream()), alib)
         skip = tiles.rows_in_wide
-        rows_tiles = (tiles.rows[0][skip:], tiles.rows[1][skip:], tiles.rows[2] - skip)
+        if skip == tiles.rows[2]:
+            rows_tiles = (None, None, 0)
+        else:
+            rows_tiles = (tiles.rows[0][skip:], tiles.rows[1][skip:], tiles.rows[2] - skip)
     for mode, (row0, rows, count) in ((1, tiles.keys), (0, rows_tiles)):
         if count == 0:
             continue
