@@ -167,18 +167,21 @@ class CacheGroup:
                              f"of {self.page_size})")
         if need_end - self.end[slot] > self.pool.free:
             raise OutOfPages(f"group {self.gid}: need {need_end - self.end[slot]} pages, {self.pool.free} free")
-        for lp in range(self.end[slot], need_end):
-            page = self.pool.allocate()
-            self.table_host[slot, lp] = page
-            self.pending.append((slot, lp, page))
+        first_new = self.end[slot]
+        if need_end > first_new:
+            # one write into the host table for all new pages (a prompt portion takes many at once)
+            pages = [self.pool.allocate() for _ in range(first_new, need_end)]
+            self.table_host[slot, first_new:need_end] = torch.tensor(pages, dtype=torch.int32)
+            self.pending.extend((slot, first_new + i, page) for i, page in enumerate(pages))
         self.end[slot] = max(self.end[slot], need_end)
 
     def release_slot(self, slot: int) -> None:
-        for lp in range(self.first[slot], self.end[slot]):
-            page = int(self.table_host[slot, lp])
-            self.pool.release(page)
-            self.table_host[slot, lp] = -1
-            self.pending.append((slot, lp, -1))
+        a, b = self.first[slot], self.end[slot]
+        if b > a:
+            for page in self.table_host[slot, a:b].tolist():
+                self.pool.release(page)
+            self.table_host[slot, a:b] = -1
+            self.pending.extend((slot, lp, -1) for lp in range(a, b))
         self.first[slot] = 0
         self.end[slot] = 0
 
