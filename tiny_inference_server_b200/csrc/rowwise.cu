@@ -357,20 +357,31 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     pdl_wait();
     constexpr int N = Vec16<T>::N;
     if (block % N == 0) {
-        const size_t nvec = total / N;
-        const int fv = F / N;
-        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec;
-             idx += (size_t)gridDim.x * blockDim.x) {
-            const size_t r = idx / fv;
-            const int j = (int)(idx - r * fv) * N;
-            const int b = j / block;
-            const T* src = gu + r * 2 * F + (size_t)b * 2 * block + (j - b * block);
-            float g[N], u[N], o[N];
-            Vec16<T>::load(src, g);
-            Vec16<T>::load(src + block, u);
+        // two 16-byte items per thread and trip, all four loads ordered before the first use
+        const unsigned nvec = (unsigned)(total / N);
+        const unsigned fv = (unsigned)(F / N);
+        const unsigned stride = gridDim.x * blockDim.x;
+        for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += 2 * stride) {
+            const unsigned idx2 = idx + stride;
+            const bool two = idx2 < nvec;
+            const unsigned r1 = idx / fv, r2 = two ? idx2 / fv : r1;
+            const int j1 = (int)(idx - r1 * fv) * N, j2 = two ? (int)(idx2 - r2 * fv) * N : j1;
+            const int b1 = j1 / block, b2 = j2 / block;
+            const T* s1 = gu + (size_t)r1 * 2 * F + (size_t)b1 * 2 * block + (j1 - b1 * block);
+            const T* s2 = gu + (size_t)r2 * 2 * F + (size_t)b2 * 2 * block + (j2 - b2 * block);
+            float g1[N], u1[N], g2[N], u2[N], o[N];
+            Vec16<T>::load(s1, g1);
+            Vec16<T>::load(s1 + block, u1);
+            Vec16<T>::load(s2, g2);
+            Vec16<T>::load(s2 + block, u2);
 #pragma unroll
-            for (int k = 0; k < N; ++k) o[k] = g[k] / (1.f + expf(-g[k])) * u[k];
-            Vec16<T>::store(out + r * F + j, o);
+            for (int k = 0; k < N; ++k) o[k] = g1[k] / (1.f + __expf(-g1[k])) * u1[k];
+            Vec16<T>::store(out + (size_t)r1 * F + j1, o);
+            if (two) {
+#pragma unroll
+                for (int k = 0; k < N; ++k) o[k] = g2[k] / (1.f + __expf(-g2[k])) * u2[k];
+                Vec16<T>::store(out + (size_t)r2 * F + j2, o);
+            }
         }
         return;
     }
@@ -393,7 +404,11 @@ TIS_API int tis_swiglu(int dtype, const void* gu, void* out, int n, int F, int b
         return TIS_BAD_SIZE;
     }
     const size_t total = (size_t)n * F;
-    size_t blocks = (total / 4 + 255) / 256;
+    if (total / 4 >= 0xffffffffu) {
+        tis_set_error("swiglu: %d x %d elements are more than this kernel indexes", n, F);
+        return TIS_BAD_SIZE;
+    }
+    size_t blocks = (total / 16 + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 16) blocks = 148 * 16;
     TIS_DISPATCH_DTYPE(dtype, T,
