@@ -233,3 +233,49 @@ def test_modes_agree_with_each_other_bitwise_close(tmp_path, tmp_path_factory):
             for p in range(len(toks)):
                 err = float(np.abs(outs[mode][rid][p] - outs["whole"][rid][p]).max())
                 assert err < 2e-5, f"{mode} vs whole: {rid} position {p}: {err}"
+
+
+def _random_configuration(seed):
+    """A small configuration drawn from a seed: every size that a kernel depends on varies."""
+    import random
+    rng = random.Random(seed)
+    hd = rng.choice([16, 32, 48, 64, 128])
+    kvh = rng.choice([1, 2, 3])
+    group = rng.choice([1, 2, 3, 4, 5, 8])
+    width = 8 * rng.randint(5, 40)
+    cfg = dict(architecture="gqa_mtp_transformer", vocab_size=rng.randint(50, 700), hidden_size=width,
+               num_layers=rng.randint(1, 3), num_heads=kvh * group, num_kv_heads=kvh, head_dim=hd,
+               ffn_hidden=8 * rng.randint(4, 60), rms_norm_eps=rng.choice([1e-5, 1e-6, 2e-8, 1e-3]),
+               rope_theta=rng.choice([1e4, 5e5, 123.0]), max_context=512,
+               tie_word_embeddings=rng.random() < 0.5, num_mtp_heads=rng.randint(0, 2))
+    if rng.random() < 0.4:
+        cfg["sliding_window"] = rng.randint(5, 150)
+        cfg["full_attention_layers"] = [0] if rng.random() < 0.5 else []
+    page = rng.choice([4, 8, 16, 32])
+    lengths = [rng.randint(1, 260) for _ in range(5)] + [rng.randint(130, 300)]
+    return cfg, page, lengths
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+def test_replay_of_random_configurations(seed, tmp_path):
+    """Configurations drawn at random (heads, groups, head sizes, widths and hidden sizes that are
+    no powers of two, vocabulary, eps, rotary base, window, MTP heads, page size): mixed replay in
+    float32 and bfloat16 against the plain implementation."""
+    cfg, page, lengths = _random_configuration(seed)
+    folder = tiny_configs.make_model_folder(cfg, seed, str(tmp_path / "model"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], lengths, seed=seed)
+    seqs = {f"r{i}": p for i, p in enumerate(prompts)}
+    plain = {rid: plain_model.plain_forward(c, W, toks) for rid, toks in seqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        for mode in ("whole", "mixed"):
+            steps = _steps(mode, seqs)
+            runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True)
+            out_dir = str(tmp_path / f"out_{dtype}_{mode}")
+            TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+            runner.check_fault()
+            runner.cache.check()
+            assert runner.cache.drained()
+            scale = max(1.0, float(max(plain[r]["main"].abs().max() for r in plain)))
+            tol = TOL["float32"] if dtype == "float32" else TOL["bfloat16"] * scale
+            _compare(cfg, steps, out_dir, seqs, plain, tol)
