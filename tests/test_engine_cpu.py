@@ -85,3 +85,34 @@ def test_step_in_flight_changes_nothing(name, tmp_path, ref_ops):
     assert eng.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0, ignore_eos=True)) == want
     assert eng.scheduler.preempts > 0 and eng.steps_behind > 0
     assert eng.runner.cache.drained()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_workloads_equal_plain(seed, tmp_path, ref_ops):
+    """Workloads drawn at random — number and lengths of prompts, tokens to generate, an
+    end-of-sequence token, pool size down to what one request needs, batch limit, token budget,
+    admission plan, with and without a step in flight: the tokens equal the plain implementation's
+    and every page comes back."""
+    import random
+    rng = random.Random(seed)
+    name = rng.choice(["A", "B", "D"])
+    cfg, page, mseed = tiny_configs.ALL[name]
+    folder = tiny_configs.make_model_folder(cfg, mseed, str(tmp_path / "m"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    nreq = rng.randint(1, 6)
+    lengths = [rng.randint(1, 40) for _ in range(nreq)]
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], lengths, seed=seed)
+    news = [rng.randint(1, 14) for _ in range(nreq)]
+    full = [plain_model.plain_greedy(c, W, p, n) for p, n in zip(prompts, news)]
+    use_eos = rng.random() < 0.5
+    eos = rng.choice(full[0]) if use_eos else None
+    want = [(f[: f.index(eos) + 1] if (eos is not None and eos in f) else f) for f in full]
+    max_need = max((l + n + page) // page + 1 for l, n in zip(lengths, news))
+    eng = _engine(folder, page, num_pages=rng.randint(max_need, max_need * nreq + 2), max_batch=rng.randint(1, 5),
+                  max_tokens_per_step=rng.choice([3, 7, 16, 64, 2048]), admission=rng.choice(["final", "cur"]))
+    eng.pipeline = rng.random() < 0.7
+    eng.scheduler.eos_token_id = eos
+    sps = [SamplingParams(max_new_tokens=n, temperature=0.0, ignore_eos=not use_eos) for n in news]
+    assert eng.generate(prompts, sps) == want
+    eng.runner.cache.check()
+    assert eng.runner.cache.drained()
