@@ -279,3 +279,34 @@ def test_replay_of_random_configurations(seed, tmp_path):
             scale = max(1.0, float(max(plain[r]["main"].abs().max() for r in plain)))
             tol = TOL["float32"] if dtype == "float32" else TOL["bfloat16"] * scale
             _compare(cfg, steps, out_dir, seqs, plain, tol)
+
+
+def test_step_graphs_are_bounded_and_reused(tmp_path, tmp_path_factory):
+    """A shape is captured at its second run and replayed from then on; no more than ``capacity``
+    graphs are kept (the least recently used go), and a dropped shape is captured again later."""
+    from tiny_inference_server_b200.engine import StepEntry
+    cfg, page, folder, seqs, plain = _setup("E", tmp_path_factory)
+    toks = seqs["r5"]                                      # 450 tokens
+    runner = make_runner(folder, "float32", 2048, page_size=page, mtp=False)
+    sg = runner.step_graphs
+    assert sg is not None and sg.capacity == 6
+
+    def run(n, tag):
+        slot = runner.add_request()
+        out = runner.step([StepEntry(slot, toks[:n], [n - 1])])
+        err = float((out.main[0].float().cpu() - plain["r5"]["main"][n - 1].float()).abs().max())
+        assert err < TOL["float32"], f"{n} tokens, {tag}: {err}"
+        runner.release(slot)
+
+    for rounds in range(3):                                # five shapes fit: eager, captured, replayed
+        for n in (64, 72, 80, 96, 112):
+            run(n, f"round {rounds}")
+    assert len(sg.graphs) == 5 and sg.replays == 5
+    for rounds in range(2):                                # eight shapes in turn: more than are kept
+        for n in (64, 72, 80, 96, 112, 128, 144, 160):
+            run(n, f"second part, round {rounds}")
+        assert len(sg.graphs) <= sg.capacity
+    run(160, "most recently used")                         # still there
+    assert sg.replays >= 6
+    runner.check_fault()
+    assert runner.cache.drained()
