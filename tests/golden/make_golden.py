@@ -10,6 +10,14 @@ names of ``main_models_new`` are rebound to plain torch stand-ins (a page write,
 attention over a page table, dense causal attention over packed prompts); everything
 else — norm form, weight layouts, the K/V split of ``kv_proj``, rotary encoding, the MTP
 wiring, ``prefill_rows`` / ``mtp_prefill_rows`` / ``trunk_rows`` — is upstream's code.
+
+The attention formula itself (scale 1/sqrt(head size), the causal rule, query head h reading
+kv head h // group) is pinned by a fourth array, ``dense_main``: the logits of upstream's own
+pure-torch dense oracle, ``dense_forward`` of its ``test_server.py`` (lines 23-45:
+``F.scaled_dot_product_attention(is_causal=True)`` after ``repeat_interleave``), with no
+stand-in on its path.  That file runs GPU tests when imported, so only the text of that one
+function is taken out of it and executed with the globals it reads (``NH, HD, KVH, GROUP, D``,
+``rotate_half``) set from this configuration.
 The weights are this repository's random weights (seeded), copied into upstream's
 parameters by name; upstream's eps buffers are set to the configuration's eps.
 """
@@ -30,6 +38,19 @@ SEED = 1234
 TOKENS = [5, 200, 17, 3, 99, 250, 0, 42, 42, 7, 131, 64, 8]
 NEXT = 77          # one decode row after the prompt, through upstream's paged path
 TPB = 16
+
+
+def upstream_dense_forward(upstream: str, M, c):
+    """Upstream's ``dense_forward`` (test_server.py:23-45), compiled from its own source text."""
+    import torch.nn.functional as F
+    src = open(os.path.join(upstream, "test_server.py")).read()
+    a = src.index("@torch.no_grad()\ndef dense_forward")
+    b = src.index("\ndef ", a + 30)
+    hd = c["hidden_size"] // c["num_heads"]
+    env = dict(torch=torch, F=F, rotate_half=M.rotate_half, NH=c["num_heads"], HD=hd, KVH=c["num_kv_heads"],
+               GROUP=c["num_heads"] // c["num_kv_heads"], D=c["hidden_size"])
+    exec(compile(src[a:b], os.path.join(upstream, "test_server.py"), "exec"), env)
+    return env["dense_forward"]
 
 
 def main(upstream: str):
@@ -133,10 +154,14 @@ def main(upstream: str):
                            torch.tensor([0], dtype=torch.int32), torch.tensor([T]),
                            torch.tensor([T + 1], dtype=torch.int32), w1, T + 1)
         decode = m.logits(hd1)
+        # upstream's dense oracle, no stand-in on its path; it must agree with upstream's own
+        # prefill path (which ran on the stand-ins) before it is written
+        dense = upstream_dense_forward(upstream, M, c)(m, toks)
+        assert float((dense - main).abs().max()) < 5e-6, float((dense - main).abs().max())
     out = os.path.join(HERE, "reference_tiny.npz")
     np.savez_compressed(out, main=main.numpy(), mtp0=mtp[0].numpy(), mtp1=mtp[1].numpy(), decode=decode.numpy(),
-                        tokens=np.array(TOKENS), next=np.array([NEXT]), seed=np.array([SEED]))
-    print("wrote", out, {k: v.shape for k, v in dict(main=main, mtp0=mtp[0], mtp1=mtp[1], decode=decode).items()})
+                        dense_main=dense.numpy(), tokens=np.array(TOKENS), next=np.array([NEXT]), seed=np.array([SEED]))
+    print("wrote", out, {k: v.shape for k, v in dict(main=main, mtp0=mtp[0], mtp1=mtp[1], decode=decode, dense_main=dense).items()})
 
 
 if __name__ == "__main__":

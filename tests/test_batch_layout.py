@@ -3,21 +3,23 @@ gives word for word what the general layout gives, and tiles cover every row onc
 import numpy as np
 import pytest
 
-from tiny_inference_server_b200.engine.batch import StepEntry, layout_decode, layout_step, plan_tiles
+from tiny_inference_server_b200.engine.batch import StepEntry, layout_decode, layout_step
+from tiny_inference_server_b200.kernels.attention_plan import plan_tiles, planner
 
 
 @pytest.mark.parametrize("n,pad", [(1, 1), (5, 8), (8, 8), (3, 4)])
 def test_decode_layout_equals_general_layout(n, pad):
     entries = [StepEntry(i, [5 + i], [0]) for i in range(n)]
     starts = [0, 1, 2, 4000, 17, 33, 2, 900][:n]
-    a = layout_step(entries, starts, [0, 1, 2], 49152, pad_to=pad, group_sizes=[4, 32], want_all=True, max_position=4095)
-    b = layout_decode(entries, starts, [0, 1, 2], 49152, pad, [4, 32], max_position=4095)
+    a = layout_step(entries, starts, [0, 1, 2], 49152, pad_to=pad, planners=[planner(4), planner(32)], want_all=True,
+                    max_position=4095)
+    b = layout_decode(entries, starts, [0, 1, 2], 49152, pad, [planner(4), planner(32)], max_position=4095)
     assert a.offsets == b.offsets and list(a.flat) == list(b.flat)
-    assert a.tile_counts == b.tile_counts and a.n == b.n and a.max_position == b.max_position and b.decode_only
+    assert a.plan_facts == b.plan_facts and a.n == b.n and a.max_position == b.max_position and b.decode_only
 
 
 def test_lagging_stages_mask_negative_positions():
-    lay = layout_step([StepEntry(3, [1, 2, 3, 4], [3]), StepEntry(1, [9], [0])], [0, 50], [0, 1, 2], 100, group_sizes=[2])
+    lay = layout_step([StepEntry(3, [1, 2, 3, 4], [3]), StepEntry(1, [9], [0])], [0, 50], [0, 1, 2], 100, planners=[planner(2)])
     def arr(name):
         a, k = lay.offsets[name]
         return list(lay.flat[a:a + k])
@@ -56,6 +58,6 @@ def test_token_ids_outside_the_vocabulary_are_refused():
     with pytest.raises(ValueError, match="outside the vocabulary"):
         layout_step([StepEntry(0, [5, 100], [])], [0], [0], 100)
     with pytest.raises(ValueError, match="outside the vocabulary"):
-        layout_decode([StepEntry(0, [-1], [0])], [0], [0], 100, 1, [4])
+        layout_decode([StepEntry(0, [-1], [0])], [0], [0], 100, 1, [planner(4)])
     with pytest.raises(ValueError, match="wanted place"):
         layout_step([StepEntry(0, [5, 6], [2])], [0], [0], 100)

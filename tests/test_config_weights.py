@@ -47,6 +47,20 @@ def test_config_errors_name_every_problem():
         config_from_dict(dict(base, layer_order=[0, 5]))
 
 
+def test_a_layer_may_not_see_further_back_than_the_cache_it_reads():
+    """Pages of a windowed layer's cache are given back as the window passes them; a layer that reads
+    that cache must not reach behind the window."""
+    base = dict(tiny_configs.TINY_A, num_layers=3, num_mtp_heads=0, layer_order=[0, 1, 2])
+    # layer 2 reads the cache of layer 1; both windowed: fine
+    config_from_dict(dict(base, sliding_window=8, cache_source=[None, None, 1]))
+    # both unwindowed, and a windowed reader of a full cache: fine
+    config_from_dict(dict(base, cache_source=[None, None, 1]))
+    config_from_dict(dict(base, sliding_window=8, full_attention_layers=[1], cache_source=[None, None, 1]))
+    # a full-attention reader of a windowed cache: refused, with both layers named
+    with pytest.raises(ConfigError, match=r"layer 2 sees every key but layer 1.*keeps only 8"):
+        config_from_dict(dict(base, sliding_window=8, full_attention_layers=[2], cache_source=[None, None, 1]))
+
+
 def test_config_json_round_trip(tmp_path):
     cfg = config_from_dict(dict(tiny_configs.TINY_C))
     folder = write_random_model(str(tmp_path / "m"), cfg, seed=3)

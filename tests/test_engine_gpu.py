@@ -238,7 +238,7 @@ def test_attention_part_in_two_portions(dtype, window):
         cache.sync_tables()
         ctx, _, _ = build_step([StepEntry(slot, [0] * (b - a))], [start], [0], [g.table_dev for g in cache.groups],
                                [page], fault, torch.device("cuda:0"), 10,
-                               group_sizes=att.tile_group_sizes())
+                               planners=att.step_planners())
         outs.append(att.forward(x[a:b].cuda(), ctx, binding).cpu())
     got = torch.cat(outs).double()
     xd = x.double()
@@ -274,7 +274,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
             self.w = None
 
         @classmethod
-        def from_config(cls, cfg, prefix, layer_index, lag):
+        def from_config(cls, cfg, prefix, layer_index, lag, position=None):
             return cls(cfg.hidden_size, prefix=prefix)
 
         def state_spec(self):

@@ -478,7 +478,7 @@ def test_attention_splits_plan():
 def test_paged_attention_whole_long_prompt(H, KVH, hd, page, window):
     """A prompt of 700 tokens in one step: the row-tile kernel with three key groups per CTA
     (long prompts from their start), two requests side by side, one of them short."""
-    from tiny_inference_server_b200.engine.batch import infer_tiles
+    from tiny_inference_server_b200.kernels.attention_plan import infer_tiles
     ops = _ops()
     g = torch.Generator().manual_seed(14)
     dtype = torch.bfloat16
@@ -497,7 +497,7 @@ def test_paged_attention_whole_long_prompt(H, KVH, hd, page, window):
         max_position, min_position = 699, 0
         tiles = infer_tiles(positions.cuda(), row_slot.cuda(), H // KVH)
 
-        def attn_tiles(self, group):
+        def plan(self, planner):
             return self.tiles
 
     fault_dev = fault.cuda()
@@ -514,7 +514,7 @@ def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
     a portion deep inside a context, a tile of a single key tile, leading padding rows of a
     stage that runs behind (slot -1), and one key made to stand out far back; compared with the
     plain reference and with the mma.sync kernel on the same rows."""
-    from tiny_inference_server_b200.engine.batch import infer_tiles, TileSet
+    from tiny_inference_server_b200.kernels.attention_plan import infer_tiles, TileSet
     ops = _ops()
     g = torch.Generator().manual_seed(21)
     dtype = torch.bfloat16
@@ -540,7 +540,7 @@ def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
     # the tiles as the engine makes them: the padding rows belong to the segment that follows them
     tiles = infer_tiles(positions.cuda(), row_slot.cuda(), H // KVH)
     segs = [(0, 300), (300, 100), (400, 300)]
-    from tiny_inference_server_b200.engine.batch import plan_tiles
+    from tiny_inference_server_b200.kernels.attention_plan import plan_tiles
     keys, rws, wide, rows_in_wide = plan_tiles(segs, H // KVH)
 
     def t(v):
@@ -554,7 +554,7 @@ def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
     class Step:
         max_position, min_position = 1299, 0
 
-        def attn_tiles(self, group):
+        def plan(self, planner):
             return tiles
 
     monkeypatch.setattr(ops, "TC_ATTENTION_MIN_TILES", 1)     # also where the mma.sync kernel would be chosen

@@ -37,6 +37,43 @@ def test_plain_equals_upstream_model_code(tmp_path):
     np.testing.assert_allclose(dec.numpy(), g["decode"], rtol=0, atol=5e-6)
 
 
+def test_plain_attention_equals_upstream_dense_oracle(tmp_path):
+    """``dense_main`` is the output of upstream's own dense oracle (test_server.py:23-45:
+    ``scaled_dot_product_attention(is_causal=True)`` after ``repeat_interleave``), with none of
+    this repository's attention code on its path: it pins the scale 1/sqrt(head size), the causal
+    rule and query head h -> kv head h // group.  Each of the three, got wrong, must fail."""
+    mg, folder = _golden_model(tmp_path)
+    g = np.load(GOLDEN)
+    c = plain_model.read_config(folder)
+    W = plain_model.read_weights(folder, torch.float64)
+    out = plain_model.plain_forward(c, W, mg.TOKENS, mtp=False)["main"].numpy()
+    np.testing.assert_allclose(out, g["dense_main"], rtol=0, atol=5e-6)
+
+    real = plain_model.plain_causal_attention
+
+    def differs(wrong):
+        plain_model.plain_causal_attention = wrong
+        try:
+            bad = plain_model.plain_forward(c, W, mg.TOKENS, mtp=False)["main"].numpy()
+        finally:
+            plain_model.plain_causal_attention = real
+        return float(np.abs(bad - g["dense_main"]).max())
+
+    H, KVH = c["num_heads"], c["num_kv_heads"]
+    # query head h -> kv head h % KVH instead of h // group
+    perm = [(h % KVH) * (H // KVH) + h // KVH for h in range(H)]
+    inv = [perm.index(h) for h in range(H)]
+    assert differs(lambda q, k, v, **kw: real(q[:, perm], k, v, **kw)[:, inv]) > 1e-4
+    # another scale
+    assert differs(lambda q, k, v, **kw: real(q * 1.5, k, v, **kw)) > 1e-4
+    # a row that also sees the key after it
+    def sees_next(q, k, v, **kw):
+        o = real(q, k, v, **kw)
+        o2 = real(q[:-1], k[1:], v[1:], **kw)       # row p over keys 1..p+1
+        return torch.cat([0.5 * (o[:-1] + o2), o[-1:]])
+    assert differs(sees_next) > 1e-4
+
+
 def test_rms_norm_form():
     x = torch.tensor([[3.0, 4.0]], dtype=torch.float64)
     y = plain_model.plain_rms_norm(x, torch.ones(2, dtype=torch.float64), 1.0)

@@ -12,7 +12,7 @@ import tiny_configs
 import trace_tools
 from tiny_inference_server_b200.trace import TraceReplayer, make_runner
 
-LENGTHS = {"A": [1, 7, 16, 33, 50], "B": [2, 9, 31, 64, 70], "C": [3, 40, 61, 90], "D": [5, 18, 47]}
+LENGTHS = {"A": [1, 7, 16, 33, 50], "B": [2, 9, 31, 64, 70], "C": [3, 40, 61, 90], "D": [5, 18, 47], "F": [4, 50, 73, 31]}
 
 
 def _setup(name, tmp_path):
@@ -55,7 +55,7 @@ def _compare(cfg, steps, out_dir, seqs, plain, tol):
                 assert err < tol, f"mtp head {i} of {rid} at position {hp}: max error {err}"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "F"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_replay_modes_match_plain(name, mode, tmp_path, ref_ops):
     cfg, page, folder, seqs, plain = _setup(name, tmp_path)

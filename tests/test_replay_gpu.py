@@ -24,7 +24,7 @@ ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)),
 LENGTHS_WIDE = [70, 33, 150, 5, 200, 90]
 LENGTHS = {"WIDE": LENGTHS_WIDE, "A": [1, 7, 16, 33, 50, 97, 64, 80, 120, 111, 70], "B": [2, 9, 31, 64, 100, 130, 77, 90, 128, 200],
            "C": [3, 40, 61, 90, 150, 70, 101, 64, 33, 88], "D": [5, 18, 47, 80, 33, 60, 90, 64, 71],
-           "E": [300, 64, 129, 7, 200, 450, 90, 33]}
+           "E": [300, 64, 129, 7, 200, 450, 90, 33], "F": [4, 50, 73, 120, 31, 150, 64, 97]}
 # float32: rounding of a float32 engine against a float64 oracle.
 # bfloat16: weights are the same bfloat16 numbers on both sides; activations are rounded
 # to bfloat16 between kernels (8 bits of mantissa) on logits of size ~0.1-1.
@@ -80,7 +80,7 @@ def _compare(cfg, steps, out_dir, seqs, plain, tol, mtp=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_replay_matches_plain(name, mode, dtype, tmp_path, tmp_path_factory):
     cfg, page, folder, seqs, plain = _setup(name, tmp_path_factory)

@@ -41,6 +41,14 @@ TINY_E = dict(architecture="gqa_mtp_transformer", vocab_size=777, hidden_size=19
               tie_word_embeddings=False, num_mtp_heads=1, sliding_window=100, full_attention_layers=[0])
 TINY_E_PAGE = 32
 
+# a windowed layer whose cache a later layer reads (with the same window: pages behind it are given back while
+# both still run), the first layer unwindowed, 5 query heads on one kv head, pages of 8
+TINY_F = dict(architecture="gqa_mtp_transformer", vocab_size=190, hidden_size=80, num_layers=3, num_heads=5,
+              num_kv_heads=1, head_dim=16, ffn_hidden=136, rms_norm_eps=2e-6, rope_theta=30000.0,
+              max_context=160, tie_word_embeddings=True, num_mtp_heads=1, sliding_window=19,
+              full_attention_layers=[0, 3], layer_order=[0, 1, 2], cache_source=[None, None, 1])
+TINY_F_PAGE = 8
+
 # the layer sizes of the upstream 0.9B model (Config/config.py:11-23), two layers and one MTP head of them
 WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=2, num_heads=12,
             num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
@@ -48,7 +56,8 @@ WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=15
 WIDE_PAGE = 16
 
 ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
-       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 5), "WIDE": (WIDE, WIDE_PAGE, 4)}
+       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 5), "F": (TINY_F, TINY_F_PAGE, 6),
+       "WIDE": (WIDE, WIDE_PAGE, 4)}
 
 
 def make_model_folder(cfg_dict: dict, seed: int, folder: str, std: float = 0.02) -> str:

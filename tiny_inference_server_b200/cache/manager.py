@@ -20,15 +20,15 @@ from .pages import CacheError, CacheGroup, OutOfPages, PlaneRef, group_planes
 class CacheManager:
     def __init__(self, kv_specs: Sequence[Optional[KVSpec]], state_specs: Dict[str, StateSpec], *,
                  page_size: int, num_pages: int, max_slots: int, max_positions: int, dtype: torch.dtype,
-                 device):
+                 device, debug_poison: bool = False):
         self.device = torch.device(device)
         self.page_size = page_size
         self.max_slots = max_slots
         self.max_positions = max_positions
         keys, lags, self.plane_refs = group_planes(kv_specs)
         self.groups: List[CacheGroup] = [
-            CacheGroup(g, k[0], k[1], k[2], lags[k], page_size, num_pages, max_slots, max_positions, dtype,
-                       self.device)
+            CacheGroup(g, k[0], k[1], k[3], lags[k], page_size, num_pages, max_slots, max_positions, dtype,
+                       self.device, v_dim=k[2], poison=debug_poison)
             for g, k in enumerate(keys)
         ]
         self.states: Dict[str, torch.Tensor] = {
@@ -44,7 +44,7 @@ class CacheManager:
     def bytes_per_page(kv_specs: Sequence[Optional[KVSpec]], page_size: int, elem_size: int) -> int:
         """Bytes that one page id costs over all groups (a request holds the same number of
         pages in each group unless a window gives some back)."""
-        return sum(2 * s.kv_heads * s.head_dim * page_size * elem_size for s in kv_specs if s is not None)
+        return sum(s.kv_heads * (s.key_dim + s.value_dim) * page_size * elem_size for s in kv_specs if s is not None)
 
     @property
     def num_pages(self) -> int:

@@ -2,8 +2,8 @@
 
 Upstream keeps one pool tensor for all layers, a deque of free page ids and a python
 list of page ids per request (``block_table.py:31-86``).  Here the planes (one per
-cached layer) are first grouped by what they need — kv heads, head size, and whether
-they keep every key or a window of them — and every group has pages of its own: a pool
+cached layer) are first grouped by what they need — kv heads, the widths of a key and of a
+value row, and whether they keep every key or a window of them — and every group has pages of its own: a pool
 tensor ``[planes, pages, 2, kv_heads, page_size, head_dim]``, a free list, and one
 block table per request slot.  A page id addresses the same page in every plane of its
 group, as upstream's does in every layer.
@@ -95,15 +95,25 @@ class PlaneRef:
     index: int        # plane inside the group's pool
 
 
+#: What a page is filled with when it is given back in the debugging mode: 2^100, large and finite.
+#: The attention kernels may multiply a masked key's probability (exactly 0) with whatever the page
+#: holds there, so the pattern must not be NaN or infinite; but a key read in earnest from a page that
+#: its request no longer holds — one key too many, a stale block-table entry — now gives a score of
+#: the order of 1e30, and the logits show it, instead of a drift in the third digit.
+POISON = 2.0 ** 100
+
+
 class CacheGroup:
     """Planes with the same needs: one pool of pages, one block table per slot."""
 
     def __init__(self, gid: int, kv_heads: int, head_dim: int, window: Optional[int], lags: Sequence[int],
                  page_size: int, num_pages: int, max_slots: int, max_positions: int, dtype: torch.dtype,
-                 device: torch.device):
+                 device: torch.device, v_dim: Optional[int] = None, poison: bool = False):
         self.gid = gid
+        self.poison = poison                      # fill pages with POISON when they are given back
         self.kv_heads = kv_heads
-        self.head_dim = head_dim
+        self.head_dim = head_dim                  # elements of a key row
+        self.v_dim = head_dim if v_dim is None else v_dim      # elements of a value row
         self.window = window
         self.lags = list(lags)                    # per plane: how far it is filled behind the trunk
         self.max_lag = max(self.lags) if self.lags else 0
@@ -113,8 +123,14 @@ class CacheGroup:
         self.max_pages_per_slot = (max_positions + page_size - 1) // page_size
         # zeros, not empty: an unwritten tail of a page must not hold NaN patterns
         # (upstream's reason too, block_table.py:40-41)
-        self.pages = torch.zeros((self.num_planes, num_pages, 2, kv_heads, page_size, head_dim),
-                                 dtype=dtype, device=device)
+        # A page is its key rows [kv_heads, page_size, k_dim] followed by its value rows
+        # [kv_heads, page_size, v_dim]; with keys and values of one width that is the 5-D shape below.
+        if self.v_dim == head_dim:
+            self.pages = torch.zeros((self.num_planes, num_pages, 2, kv_heads, page_size, head_dim),
+                                     dtype=dtype, device=device)
+        else:
+            self.pages = torch.zeros((self.num_planes, num_pages, kv_heads * page_size * (head_dim + self.v_dim)),
+                                     dtype=dtype, device=device)
         self.table_host = torch.full((max_slots, self.max_pages_per_slot), -1, dtype=torch.int32)
         self.table_dev = torch.full((max_slots, self.max_pages_per_slot), -1, dtype=torch.int32, device=device)
         # per slot: first logical page still held, and one past the last
@@ -124,10 +140,27 @@ class CacheGroup:
 
     @property
     def bytes_per_token(self) -> int:
-        return 2 * self.num_planes * self.kv_heads * self.head_dim * self.pages.element_size()
+        return self.num_planes * self.kv_heads * (self.head_dim + self.v_dim) * self.pages.element_size()
 
-    def plane(self, index: int) -> torch.Tensor:
-        return self.pages[index]
+    def plane(self, index: int) -> Optional[torch.Tensor]:
+        """[pages, 2, kv_heads, page_size, head_dim] — what the attention kernels of this library
+        take; None for a group whose keys and values differ in width (use ``key_pages`` /
+        ``value_pages``)."""
+        return self.pages[index] if self.v_dim == self.head_dim else None
+
+    def key_pages(self, index: int) -> torch.Tensor:
+        """[pages, kv_heads, page_size, k_dim]: a view of the key rows of every page of a plane."""
+        if self.v_dim == self.head_dim:
+            return self.pages[index][:, 0]
+        n = self.kv_heads * self.page_size * self.head_dim
+        return self.pages[index][:, :n].unflatten(1, (self.kv_heads, self.page_size, self.head_dim))
+
+    def value_pages(self, index: int) -> torch.Tensor:
+        """[pages, kv_heads, page_size, v_dim]: a view of the value rows of every page of a plane."""
+        if self.v_dim == self.head_dim:
+            return self.pages[index][:, 1]
+        n = self.kv_heads * self.page_size * self.head_dim
+        return self.pages[index][:, n:].unflatten(1, (self.kv_heads, self.page_size, self.v_dim))
 
     # ---- planning ---------------------------------------------------------------------
     def dead_before(self, start_pos: int) -> int:
@@ -151,13 +184,16 @@ class CacheGroup:
         """Give back pages wholly behind the window of a step that starts at ``start_pos``."""
         upto = min(self.dead_before(start_pos), self.end[slot])
         n = 0
+        freed: List[int] = []
         for lp in range(self.first[slot], upto):
             page = int(self.table_host[slot, lp])
             self.pool.release(page)
             self.table_host[slot, lp] = -1
             self.pending.append((slot, lp, -1))
+            freed.append(page)
             n += 1
         self.first[slot] = max(self.first[slot], upto)
+        self._poison(freed)
         return n
 
     def grow(self, slot: int, new_len: int) -> None:
@@ -178,12 +214,22 @@ class CacheGroup:
     def release_slot(self, slot: int) -> None:
         a, b = self.first[slot], self.end[slot]
         if b > a:
-            for page in self.table_host[slot, a:b].tolist():
+            freed = self.table_host[slot, a:b].tolist()
+            for page in freed:
                 self.pool.release(page)
             self.table_host[slot, a:b] = -1
             self.pending.extend((slot, lp, -1) for lp in range(a, b))
+            self._poison(freed)
         self.first[slot] = 0
         self.end[slot] = 0
+
+    def _poison(self, pages: List[int]) -> None:
+        """Debugging mode: overwrite pages that were just given back, in every plane.  The fill is
+        ordered on the stream after the steps that still read them and before any step that takes
+        them again."""
+        if self.poison and pages:
+            idx = torch.tensor(pages, dtype=torch.int64, device=self.pages.device)
+            self.pages.index_fill_(1, idx, POISON)
 
     def held(self, slot: int) -> int:
         return self.end[slot] - self.first[slot]
@@ -195,7 +241,7 @@ class CacheGroup:
 
 def group_planes(specs: Sequence[Optional[KVSpec]]):
     """Group the kv specs of the schedule entries: returns ([group key], [PlaneRef or None]).
-    Entries with equal (kv_heads, head_dim, window) share a group."""
+    Entries with equal (kv_heads, key width, value width, window) share a group."""
     keys: List[tuple] = []
     lags: Dict[tuple, List[int]] = {}
     refs: List[Optional[PlaneRef]] = []

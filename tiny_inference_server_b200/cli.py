@@ -52,6 +52,20 @@ def main(argv=None) -> int:
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
     args = ap.parse_args(argv)
 
+    from .config import ConfigError, EngineConfig
+    from .kernels.build import BuildError
+    from .kernels.ops import KernelError
+    from .weights import WeightError
+    try:
+        return _run(ap, args)
+    except (ConfigError, WeightError, KernelError, BuildError) as e:
+        # what a user can put right (a bad config.json, tensors that do not fit it, no B200, no
+        # compiler) is one line, not a traceback
+        print(f"{ap.prog}: error: {e}", file=sys.stderr)
+        return 2
+
+
+def _run(ap, args) -> int:
     from .config import EngineConfig
     from .registry import config_from_dict
     from .weights import write_random_model
@@ -65,15 +79,18 @@ def main(argv=None) -> int:
             write_random_model(args.write_model, cfg, args.seed)
             print(f"wrote {args.write_model}")
             return 0
-        tmp = tempfile.TemporaryDirectory()
-        folder = write_random_model(tmp.name, cfg, args.seed)
-
     prompts = [_ids(p) for p in args.prompt_ids]
     if args.prompt_file:
         with open(args.prompt_file) as f:
             prompts += [_ids(line) for line in f if line.strip()]
     if not prompts:
         ap.error("no prompt: give --prompt-ids or --prompt-file")
+
+    from .kernels import ops
+    ops.library()                   # no CUDA device, no sm_100 GPU or no compiler: KernelError / BuildError here
+    if args.random:
+        tmp = tempfile.TemporaryDirectory()
+        folder = write_random_model(tmp.name, cfg, args.seed)
 
     from .api import Engine, SamplingParams
 

@@ -23,6 +23,8 @@ class EngineConfig:
     max_context: Optional[int] = None  # cap below the model's max_context
     device: str = "cuda:0"
     seed: int = 0
+    debug_poison: bool = False         # fill pages with NaN patterns when they are given back (debugging aid)
+    profile: bool = False              # time the phases of every step (plan, upload, launch, read-back)
 
     def __post_init__(self):
         errs = []

@@ -114,6 +114,14 @@ class GqaMtpConfig:
                         errs.append(f"cache_source[{e}]={s!r} must name an earlier entry")
                     elif self.cache_source[s] is not None:
                         errs.append(f"cache_source[{e}]={s} names an entry that has no cache of its own")
+                    elif all(isinstance(l, int) and 0 <= l < self.num_layers for l in (order[e], order[s])):
+                        # pages of the source's group are given back by the source's window: a reader
+                        # that sees further back would walk pages that other requests hold by then
+                        mine, theirs = self.window_of(order[e]), self.window_of(order[s])
+                        if theirs is not None and (mine is None or mine > theirs):
+                            errs.append(f"cache_source[{e}]={s}: layer {order[e]} sees "
+                                        f"{'every key' if mine is None else f'{mine} keys'} but layer {order[s]}, "
+                                        f"whose cache it reads, keeps only {theirs}")
         for key in ("mixer_types", "ffn_types"):
             v = getattr(self, key)
             if v is not None and len(v) != self.num_layers:

@@ -6,7 +6,10 @@ write pointers, a flat page table with per-row starts, kv lengths (``server.py:1
 ``294-318``).  Here a step is described by four int32 arrays over its rows (token,
 position, slot, last row of the same request) and the device block tables of the cache
 groups, which persist between steps; kernels find pages from (slot, position)
-themselves.  All per-step arrays travel to the device in one copy.
+themselves.  What else a mixer's kernels want laid out per step (tiles of rows, for
+instance) comes from the planners the mixers declare (``parts.base.StepPlanner``); this
+module lays out whatever arrays they return and knows nothing of their meaning.  All
+per-step arrays travel to the device in one copy.
 """
 from __future__ import annotations
 
@@ -35,49 +38,6 @@ class Segment:
     pos0: int
 
 
-#: rows from which a portion of a prompt is also cut into wide tiles
-WIDE_MIN_ROWS = 64
-WIDE_TILE_ROWS = 128
-
-
-class TileSet:
-    """Attention work of one step for one group size G (query heads per kv head): tiles of
-    consecutive rows of one request.  ``keys``: tiles of at most 16 // G rows (decode rows,
-    tiny portions), whose keys are split over warps and CTAs; ``rows``: tiles of at most
-    64 // G rows (portions of prompts).  Each is (first rows, row counts, number of tiles);
-    the first two are int32 device tensors.  ``wide``: the portions of at least WIDE_MIN_ROWS
-    rows once more, as tiles of up to 128 rows, for the kernel that takes those; their ``rows``
-    tiles are the first ``rows_in_wide`` of ``rows``, so a caller runs either ``wide`` and the
-    rest of ``rows``, or all of ``rows``."""
-
-    def __init__(self, keys, rows, keys_max_rows: int = 0, wide=None, rows_in_wide: int = 0):
-        self.keys = keys
-        self.rows = rows
-        self.keys_max_rows = keys_max_rows      # the most rows of any ``keys`` tile (0: not known)
-        self.wide = wide if wide is not None else (None, None, 0)
-        self.rows_in_wide = rows_in_wide
-
-
-def plan_tiles(segments: Sequence[Tuple[int, int]], group_size: int):
-    """Cut (row0, rows) segments into tiles.  Returns (keys tiles, rows tiles, wide tiles, number
-    of leading rows tiles that the wide tiles cover) with tiles as lists of (row0, rows)."""
-    r_keys = 16 // group_size if group_size <= 16 else 0
-    r_rows = max(1, 64 // group_size)
-    keys, rows_wide, rows_rest, wide = [], [], [], []
-    for row0, n in segments:
-        if r_keys and n <= r_keys:
-            keys.append((row0, n))
-            continue
-        into = rows_rest
-        if n >= WIDE_MIN_ROWS:
-            into = rows_wide
-            for a in range(0, n, WIDE_TILE_ROWS):
-                wide.append((row0 + a, min(WIDE_TILE_ROWS, n - a)))
-        for a in range(0, n, r_rows):
-            into.append((row0 + a, min(r_rows, n - a)))
-    return keys, rows_wide + rows_rest, wide, len(rows_wide)
-
-
 class StepContext:
     """Everything a part may know about the step.  ``positions`` and ``row_slot`` are the
     ones of the *stage* the part runs in: a stage that lags the trunk by ``lag`` positions
@@ -86,7 +46,7 @@ class StepContext:
     def __init__(self, n: int, tokens, positions, row_slot, row_last, segments: List[Segment],
                  block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
                  max_position: int, trunk_slot=None, lag: int = 0, stages: Optional[dict] = None,
-                 decode_only: bool = False, tiles: Optional[Dict[int, TileSet]] = None):
+                 decode_only: bool = False, plans: Optional[Dict] = None):
         self.n = n
         self.tokens = tokens
         self.positions = positions
@@ -102,7 +62,7 @@ class StepContext:
         self.lag = lag
         self._stages = stages if stages is not None else {}
         self.decode_only = decode_only      # every request has exactly one row
-        self.tiles = tiles if tiles is not None else {}
+        self.plans = plans if plans is not None else {}     # planner key -> what its ``bind`` returned
         self.scratch: Dict = {}             # buffers that kernels of this step may share
 
     def stage(self, lag: int) -> "StepContext":
@@ -111,13 +71,13 @@ class StepContext:
             return self
         return self._stages[lag]
 
-    def attn_tiles(self, group_size: int) -> TileSet:
-        """Tiles for mixers with ``group_size`` query heads per kv head.  Planned with the step
-        for the group sizes the model declares; for any other it is derived here from the
-        device arrays (which synchronises)."""
-        if group_size not in self.tiles:
-            self.tiles[group_size] = infer_tiles(self.stage(0).positions, self.stage(0).row_slot, group_size)
-        return self.tiles[group_size]
+    def plan(self, planner):
+        """What ``planner`` (a ``parts.base.StepPlanner``) made of this step.  Planned with the
+        step for the planners the model's mixers declare; for any other it is derived here from
+        the device arrays (which synchronises)."""
+        if planner.key not in self.plans:
+            self.plans[planner.key] = planner.infer(self.stage(0).positions, self.stage(0).row_slot)
+        return self.plans[planner.key]
 
 
 @dataclass
@@ -128,7 +88,7 @@ class StepLayout:
     n: int
     segments: List[Segment]
     lags: List[int]
-    tile_counts: Dict[int, Tuple[int, int, int]]
+    plan_facts: Dict                 # planner key -> (index of the planner, array names, host-side facts)
     n_want: int
     max_position: int
     decode_only: bool
@@ -136,7 +96,7 @@ class StepLayout:
 
 
 def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
-                pad_to: Optional[int] = None, group_sizes: Sequence[int] = (), want_all: bool = False,
+                pad_to: Optional[int] = None, planners: Sequence = (), want_all: bool = False,
                 max_position: Optional[int] = None) -> StepLayout:
     """Lay the entries out as rows (host only, array arithmetic: no loop over tokens).
     ``starts[i]`` is the position of entry i's first token.  ``pad_to``: add padding rows
@@ -199,16 +159,12 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
     for lag in lags:
         put(f"pos{lag}", np.maximum(positions - lag, 0))
         put(f"slot{lag}", np.where(positions - lag >= 0, slots, -1))
-    counts = {}
-    for g in sorted(set(group_sizes)):
-        keys, rows, wide, rows_in_wide = plan_tiles(seg_rows, g)
-        counts[g] = (len(keys), len(rows), max((t[1] for t in keys), default=0), len(wide), rows_in_wide)
-        put(f"k0_{g}", [t[0] for t in keys])
-        put(f"kn_{g}", [t[1] for t in keys])
-        put(f"r0_{g}", [t[0] for t in rows])
-        put(f"rn_{g}", [t[1] for t in rows])
-        put(f"w0_{g}", [t[0] for t in wide])
-        put(f"wn_{g}", [t[1] for t in wide])
+    facts = {}
+    for i, pl in enumerate(planners):
+        arrays, fact = pl.plan(seg_rows)
+        facts[pl.key] = (i, tuple(arrays), fact)
+        for name, values in arrays.items():
+            put(f"plan{i}.{name}", values)
     if want_all:
         want_rows = list(range(n))
     put("want", want_rows)
@@ -216,12 +172,12 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
     if max_position is not None:
         max_pos = max(max_pos, max_position)
     flat = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
-    return StepLayout(flat, offsets, n, segments, lags, counts, len(want_rows), max_pos,
+    return StepLayout(flat, offsets, n, segments, lags, facts, len(want_rows), max_pos,
                       all(s.rows == 1 for s in segments), int(positions[:n_real].min()) if n_real else 0)
 
 
 def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
-                  pad_to: int, group_sizes: Sequence[int], max_position: Optional[int] = None) -> StepLayout:
+                  pad_to: int, planners: Sequence = (), max_position: Optional[int] = None) -> StepLayout:
     """``layout_step`` for the common case of a decode-only step (one token per entry, every
     row wanted, padded to ``pad_to`` rows), with plain lists: for a handful of rows that is
     several times faster than array arithmetic.  Same layout, word for word."""
@@ -251,51 +207,43 @@ def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seq
     for lag in lags:
         put(f"pos{lag}", [p - lag if p >= lag else 0 for p in positions])
         put(f"slot{lag}", [s if p >= lag else -1 for s, p in zip(slots, positions)])
-    counts = {}
-    ones = [1] * n
-    for g in sorted(set(group_sizes)):
-        if g <= 16:
-            counts[g] = (n, 0, 1, 0, 0)
-            put(f"k0_{g}", rows)
-            put(f"kn_{g}", ones)
-            put(f"r0_{g}", [])
-            put(f"rn_{g}", [])
-        else:
-            counts[g] = (0, n, 0, 0, 0)
-            put(f"k0_{g}", [])
-            put(f"kn_{g}", [])
-            put(f"r0_{g}", rows)
-            put(f"rn_{g}", ones)
-        put(f"w0_{g}", [])
-        put(f"wn_{g}", [])
+    facts = {}
+    for i, pl in enumerate(planners):
+        arrays, fact = pl.plan_decode(n)
+        facts[pl.key] = (i, tuple(arrays), fact)
+        for name, values in arrays.items():
+            put(f"plan{i}.{name}", list(values))
     put("want", rows)
     max_pos = max(starts) if n_real else 0
     if max_position is not None:
         max_pos = max(max_pos, max_position)
     segments = [Segment(e.slot, i, 1, starts[i]) for i, e in enumerate(entries)]
-    return StepLayout(flat, offsets, n, segments, lags, counts, n, max_pos, True, min(starts) if n_real else 0)
+    return StepLayout(flat, offsets, n, segments, lags, facts, n, max_pos, True, min(starts) if n_real else 0)
 
 
 def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[torch.Tensor],
-                        page_sizes: List[int], fault: torch.Tensor) -> Tuple[StepContext, torch.Tensor]:
-    """Views of the device copy of a layout as a StepContext; returns it and the wanted rows."""
+                        page_sizes: List[int], fault: torch.Tensor, planners: Sequence = ()
+                        ) -> Tuple[StepContext, torch.Tensor]:
+    """Views of the device copy of a layout as a StepContext; returns it and the wanted rows.
+    ``planners``: the ones the layout was made with, in the same order."""
 
     def view(name):
         a, k = lay.offsets[name]
         return dev[a:a + k]
 
-    tiles = {g: TileSet((view(f"k0_{g}"), view(f"kn_{g}"), nk), (view(f"r0_{g}"), view(f"rn_{g}"), nr), kmax,
-                        (view(f"w0_{g}"), view(f"wn_{g}"), nw), nrw)
-             for g, (nk, nr, kmax, nw, nrw) in lay.tile_counts.items()}
+    plans = {}
+    for pl in planners:
+        i, names, fact = lay.plan_facts[pl.key]
+        plans[pl.key] = pl.bind({name: view(f"plan{i}.{name}") for name in names}, fact)
     stages: Dict[int, StepContext] = {}
     ctx = StepContext(lay.n, view("tokens"), view("positions"), view("slots"), view("last"), lay.segments,
                       block_tables, page_sizes, fault, lay.max_position, stages=stages,
-                      decode_only=lay.decode_only, tiles=tiles)
+                      decode_only=lay.decode_only, plans=plans)
     ctx.min_position = lay.min_position
     for lag in lay.lags:
         st = StepContext(lay.n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), lay.segments,
                          block_tables, page_sizes, fault, max(0, lay.max_position - lag), trunk_slot=view("slots"),
-                         lag=lag, stages=stages, decode_only=lay.decode_only, tiles=tiles)
+                         lag=lag, stages=stages, decode_only=lay.decode_only, plans=plans)
         st.scratch = ctx.scratch
         st.min_position = max(0, lay.min_position - lag)
         stages[lag] = st
@@ -305,12 +253,12 @@ def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[t
 def build_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int],
                block_tables: List[torch.Tensor], page_sizes: List[int], fault: torch.Tensor,
                device: torch.device, vocab_size: int, pad_to: Optional[int] = None,
-               group_sizes: Sequence[int] = ()) -> Tuple[StepContext, torch.Tensor, int]:
+               planners: Sequence = ()) -> Tuple[StepContext, torch.Tensor, int]:
     """Rows, metadata and context of one step; all per-step arrays go to the device in one
     copy.  Returns the context, the device indices of the wanted rows, and their count."""
-    lay = layout_step(entries, starts, lags, vocab_size, pad_to=pad_to, group_sizes=group_sizes)
+    lay = layout_step(entries, starts, lags, vocab_size, pad_to=pad_to, planners=planners)
     dev = torch.from_numpy(lay.flat).to(device, non_blocking=True)
-    ctx, want = context_from_layout(lay, dev, block_tables, page_sizes, fault)
+    ctx, want = context_from_layout(lay, dev, block_tables, page_sizes, fault, planners)
     return ctx, want, lay.n_want
 
 
@@ -353,26 +301,3 @@ class StaticMeta:
             self.events[i].record()
             self.recorded[i] = True
         return self.dev
-
-
-def infer_tiles(positions: torch.Tensor, row_slot: torch.Tensor, group_size: int) -> TileSet:
-    """Tiles from the device arrays alone (synchronises; for calls outside a step, as in
-    kernel tests): consecutive rows with one slot and consecutive positions form a segment."""
-    pos = positions.tolist()
-    slot = row_slot.tolist()
-    segs: List[Tuple[int, int]] = []
-    for r in range(len(pos)):
-        if segs and slot[r] >= 0 and slot[r] == slot[r - 1] and pos[r] == pos[r - 1] + 1:
-            segs[-1] = (segs[-1][0], segs[-1][1] + 1)
-        else:
-            segs.append((r, 1))
-    keys, rows, wide, rows_in_wide = plan_tiles(segs, group_size)
-    dev = positions.device
-
-    def t(v):
-        return torch.tensor(v, dtype=torch.int32, device=dev)
-
-    return TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
-                   (t([k[0] for k in rows]), t([k[1] for k in rows]), len(rows)),
-                   max((k[1] for k in keys), default=0),
-                   (t([k[0] for k in wide]), t([k[1] for k in wide]), len(wide)), rows_in_wide)

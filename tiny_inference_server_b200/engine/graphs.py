@@ -35,15 +35,17 @@ class GraphedDecode:
         self.bucket = bucket
         self.kv_bound = kv_bound
         self.sampled = sampled            # the graph also draws a token for every row
-        n_arrays = 4 + 2 * len([l for l in runner.lags if l > 0]) + 4 * len(runner.group_sizes) + 1
-        self.static = StaticMeta((n_arrays + WORDS_PER_ROW) * bucket + 16, runner.device)
+        # tokens, positions, slots, last row; two arrays per lagging stage; the planners' arrays; wanted rows
+        words = (4 + 2 * len([l for l in runner.lags if l > 0]) + 1 + WORDS_PER_ROW) * bucket
+        words += sum(pl.max_words(bucket) for pl in runner.planners)
+        self.static = StaticMeta(words + 16, runner.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[StepOutput] = None
         self.kernels = 0                # launches of this library's kernels inside the graph
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int], feed=None) -> StepOutput:
         r = self.runner
-        lay = layout_decode(entries, starts, r.lags, r.vocab_size, self.bucket, r.group_sizes,
+        lay = layout_decode(entries, starts, r.lags, r.vocab_size, self.bucket, r.planners,
                             max_position=self.kv_bound - 1)
         if self.sampled:
             if len(lay.flat) % 2:
@@ -62,7 +64,7 @@ class GraphedDecode:
         # first time: run the step as it is (this is the real step), then capture it
         tables = [g.table_dev for g in r.cache.groups]
         sizes = [g.page_size for g in r.cache.groups]
-        ctx, want = context_from_layout(lay, dev, tables, sizes, r.fault)
+        ctx, want = context_from_layout(lay, dev, tables, sizes, r.fault, r.planners)
         words = None
         if self.sampled:
             a, k = lay.offsets["sampling"]
@@ -151,7 +153,7 @@ class GraphedStep:
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepOutput:
         r = self.runner
-        lay = layout_step(entries, starts, r.lags, r.vocab_size, group_sizes=r.group_sizes,
+        lay = layout_step(entries, starts, r.lags, r.vocab_size, planners=r.planners,
                           max_position=self.kv_bound - 1)
         if self.static is None:
             self.static = StaticMeta(len(lay.flat) + 16, r.device)
@@ -163,7 +165,7 @@ class GraphedStep:
         # first time: run the step as it is (this is the real step), then capture it
         lay.min_position = 0            # planned for any positions up to the bound, not for this step's
         ctx, want = context_from_layout(lay, dev, [g.table_dev for g in r.cache.groups],
-                                        [g.page_size for g in r.cache.groups], r.fault)
+                                        [g.page_size for g in r.cache.groups], r.fault, r.planners)
 
         def run_once() -> StepOutput:
             return r.model.forward(ctx, want, aux=r.aux)

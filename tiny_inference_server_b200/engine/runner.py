@@ -59,12 +59,17 @@ class ModelRunner:
             num_pages = max(1, self.engine.pool_bytes // max(1, page_bytes))
         self.cache = CacheManager(kv_specs, self.model.state_specs(self.build_ctx), page_size=self.engine.page_size,
                                   num_pages=num_pages, max_slots=self.engine.max_batch,
-                                  max_positions=self.max_positions, dtype=self.dtype, device=self.device)
+                                  max_positions=self.max_positions, dtype=self.dtype, device=self.device,
+                                  debug_poison=self.engine.debug_poison)
         self.model.bind(self.cache)
         self.fault = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.lags = self.model.lags()
-        self.group_sizes = sorted({g for p in self.model.walk_parts() if hasattr(p, "tile_group_sizes")
-                                   for g in p.tile_group_sizes()})
+        # what the mixers' kernels want planned with every step; one planner per key
+        self.planners = []
+        for p in self.model.walk_parts():
+            for pl in (p.step_planners() if hasattr(p, "step_planners") else ()):
+                if all(pl.key != q.key for q in self.planners):
+                    self.planners.append(pl)
         self.aux = bool(self.engine.mtp)
         from ..sampling.sampler import Sampler
         self.sampler = Sampler(self.vocab_size, self.engine.max_batch, self.device, seed=self.engine.seed)
@@ -136,7 +141,7 @@ class ModelRunner:
         ctx, want_rows, _ = build_step(entries, starts, self.lags,
                                        [g.table_dev for g in self.cache.groups],
                                        [g.page_size for g in self.cache.groups], self.fault, self.device,
-                                       self.vocab_size, pad_to=pad_to, group_sizes=self.group_sizes)
+                                       self.vocab_size, pad_to=pad_to, planners=self.planners)
         if feed is not None:
             feed_tokens(ctx.tokens, len(entries), feed)
         out = self.model.forward(ctx, want_rows, aux=self.aux)

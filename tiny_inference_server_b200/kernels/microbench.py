@@ -50,12 +50,12 @@ class _Step:
         self.max_position = max_position
         self.min_position = max_position
 
-    def attn_tiles(self, g):
+    def plan(self, planner):
         return self._tiles
 
 
 def attention(args):
-    from ..engine.batch import infer_tiles
+    from .attention_plan import infer_tiles
     dev = "cuda"
     H, KVH, hd, page, ctx, B = args.heads, args.kv_heads, args.head_dim, args.page_size, args.context, args.batch
     pages_per = (ctx + page - 1) // page
@@ -87,7 +87,7 @@ def attention(args):
 def attention_prefill(args):
     """Attention of one portion of ``--tokens`` rows at positions start..start+tokens-1 of a prompt
     (``--start 0``: a prompt over its own keys)."""
-    from ..engine.batch import infer_tiles
+    from .attention_plan import infer_tiles
     dev = "cuda"
     H, KVH, hd, page, n = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
     num_pages = (args.start + n + page - 1) // page

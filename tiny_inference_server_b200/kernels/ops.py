@@ -403,7 +403,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     p of slot s sees keys max(0, p-window+1)..p of ``plane`` through ``block_table[s]``.
 
     float32: CUDA-core kernel, everything in 32-bit.  bfloat16: tensor-core kernels over
-    tiles of rows (``step.attn_tiles``), keys of long contexts split over CTAs."""
+    tiles of rows (``kernels.attention_plan``), keys of long contexts split over CTAs."""
     lib = library()
     n = q.shape[0]
     scale = 1.0 / math.sqrt(head_dim)
@@ -420,14 +420,14 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         raise KernelError(f"paged_attention: {g} query heads per kv head; the bfloat16 kernels take up to 64")
     alib = attention_library(head_dim)
     min_kv = None
+    from . import attention_plan
     if step is not None:
-        tiles = step.attn_tiles(g)
+        tiles = step.plan(attention_plan.planner(g))
         max_kv = step.max_position + 1
         min_kv = getattr(step, "min_position", None)
         min_kv = None if min_kv is None else min_kv + 1
     else:
-        from ..engine.batch import infer_tiles
-        tiles = infer_tiles(positions, row_slot, g)
+        tiles = attention_plan.infer_tiles(positions, row_slot, g)
         max_kv = int(positions.max().item()) + 1 if n else 1
     rows_tiles = tiles.rows
     w0, wn, wide_count = getattr(tiles, "wide", (None, None, 0))

@@ -103,7 +103,10 @@ class Model:
             src = i if e.source is None else e.source
             ref = cache.plane_refs[src]
             if ref is not None:
-                e.binding.kv_plane = cache.groups[ref.group].plane(ref.index)
+                grp = cache.groups[ref.group]
+                e.binding.kv_plane = grp.plane(ref.index)
+                e.binding.k_pages = grp.key_pages(ref.index)
+                e.binding.v_pages = grp.value_pages(ref.index)
                 e.binding.kv_group = ref.group
             e.binding.kv_write = e.source is None
             e.binding.state = cache.states.get(f"entry{i}")

@@ -37,23 +37,17 @@ from .base import Model, ScheduleEntry, StepOutput
 
 def _make_block(cfg: GqaMtpConfig, prefix: str, layer_index: int, lag: int, mixer_type: str, ffn_type: str,
                 position) -> Block:
-    """One block of the architecture; every size and constant comes from ``cfg``."""
+    """One block of the architecture.  The parts are whatever classes the registries hold under
+    the names the configuration gives; each reads its sizes and constants from ``cfg`` itself
+    (``from_config``), so a part registered from outside is built the same way as a built-in one."""
     norm_cls = part("norm", cfg.norm_type)
-    mixer_cls = part("mixer", mixer_type)
-    ffn_cls = part("ffn", ffn_type)
-    if mixer_type == "gqa":
-        mixer = mixer_cls(cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, position,
-                          window=cfg.window_of(layer_index), lag=lag, prefix=prefix + "att.")
-    else:
-        mixer = mixer_cls.from_config(cfg, prefix=prefix + "att.", layer_index=layer_index, lag=lag)
-    if ffn_type == "swiglu":
-        ffn = ffn_cls(cfg.hidden_size, cfg.ffn_hidden, prefix=prefix + "ffn.")
-    else:
-        ffn = ffn_cls.from_config(cfg, prefix=prefix + "ffn.", layer_index=layer_index)
+    mixer = part("mixer", mixer_type).from_config(cfg, prefix=prefix + "att.", layer_index=layer_index, lag=lag,
+                                                  position=position)
+    ffn = part("ffn", ffn_type).from_config(cfg, prefix=prefix + "ffn.", layer_index=layer_index)
     return Block(
-        norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "att.rms_norm_att."),
+        norm_cls.from_config(cfg, prefix=prefix + "att.rms_norm_att."),
         mixer,
-        norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_norm_ffn."),
+        norm_cls.from_config(cfg, prefix=prefix + "rms_norm_ffn."),
         ffn,
         prefix=prefix,
     )
@@ -73,8 +67,8 @@ class MtpHead(Part):
         self.lag = 1 + index
         self.width = cfg.hidden_size
         self.embedding = embedding
-        self.rms_embed = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_embed.")
-        self.rms_out = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix + "rms_out.")
+        self.rms_embed = norm_cls.from_config(cfg, prefix=prefix + "rms_embed.")
+        self.rms_out = norm_cls.from_config(cfg, prefix=prefix + "rms_out.")
         self.block = _make_block(cfg, prefix + "trans_block.", cfg.num_layers + index, self.lag, "gqa", "swiglu",
                                  position)
         self.w_proj: Optional[torch.Tensor] = None
@@ -109,8 +103,7 @@ class GqaMtpModel(Model):
         self.config = cfg
         self.vocab_size = cfg.vocab_size
         self.max_positions = cfg.max_context
-        pos_cls = part("position", cfg.position_type)
-        self.position = pos_cls(cfg.head_dim, cfg.rope_theta, cfg.max_context)
+        self.position = part("position", cfg.position_type).from_config(cfg)
         self.embedding = Embedding(cfg.vocab_size, cfg.hidden_size)
         mixers = cfg.mixer_types or ["gqa"] * cfg.num_layers
         ffns = cfg.ffn_types or ["swiglu"] * cfg.num_layers
@@ -119,7 +112,7 @@ class GqaMtpModel(Model):
             for l in range(cfg.num_layers)
         ]
         norm_cls = part("norm", cfg.norm_type)
-        self.rms_out = norm_cls(cfg.hidden_size, cfg.rms_norm_eps, prefix="rms_out.")
+        self.rms_out = norm_cls.from_config(cfg, prefix="rms_out.")
         self.heads: List[MtpHead] = [MtpHead(cfg, i, self.embedding, self.position)
                                      for i in range(cfg.num_mtp_heads)]
         self.lm_head = LMHead(cfg.vocab_size, cfg.hidden_size, self.embedding if cfg.tie_word_embeddings else None)

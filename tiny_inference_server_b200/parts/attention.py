@@ -5,7 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import ops
+from ..kernels import attention_plan, ops
 from ..registry import register_part
 from .base import BuildContext, KVSpec, LayerBinding, Mixer, WeightSpec
 
@@ -48,14 +48,20 @@ class GqaAttention(Mixer):
         self.w_q = None
         self.w_o = None
 
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int, lag: int, position=None):
+        return cls(cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, position,
+                   window=cfg.window_of(layer_index), lag=lag, prefix=prefix)
+
     def children(self):
         return (self.position,)
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.kv_heads, self.head_dim, self.window, self.lag)
 
-    def tile_group_sizes(self):
-        return (self.num_heads // self.kv_heads,)
+    def step_planners(self):
+        # the tiles the bfloat16 attention kernels take, for this layer's group size
+        return (attention_plan.planner(self.num_heads // self.kv_heads),)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         hq, hkv = self.num_heads * self.head_dim, self.kv_heads * self.head_dim
@@ -79,9 +85,9 @@ class GqaAttention(Mixer):
         table = step.block_tables[g]
         page_size = step.page_sizes[g]
         qkv = ops.gemm(x, self.w_qkv if binding.kv_write else self.w_q)
-        ops.rope_kv_write(qkv, step.positions, step.row_slot, self.position.cos, self.position.sin,
-                          binding.kv_plane, table, self.num_heads, self.kv_heads, self.head_dim, page_size,
-                          step.fault, interleaved=self.position.interleaved, write_kv=binding.kv_write)
+        self.position.encode_and_store(qkv, step, num_heads=self.num_heads, kv_heads=self.kv_heads,
+                                       head_dim=self.head_dim, plane=binding.kv_plane if binding.kv_write else None,
+                                       block_table=table, page_size=page_size)
         out = torch.empty((n, hq), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, out, binding.kv_plane, table, step.positions, step.row_slot, self.num_heads,
                             self.kv_heads, self.head_dim, page_size, self.window, step.fault, step)

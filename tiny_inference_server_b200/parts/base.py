@@ -23,14 +23,28 @@ import torch
 @dataclass(frozen=True)
 class KVSpec:
     """What a mixer needs of the paged cache.  Planes with equal specs share a group:
-    one pool of pages, one block table per request."""
+    one pool of pages, one block table per request.
+
+    A page holds, for each kv head and each of its ``page_size`` positions, a key row of
+    ``k_dim`` elements and a value row of ``v_dim`` elements (both ``head_dim`` unless given:
+    a mixer with compressed keys, or keys and values of different widths, says so here)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every earlier key; W: keys p-W+1..p
     lag: int = 0                      # the plane is filled this many positions behind the trunk
+    k_dim: Optional[int] = None       # elements of a key row (default head_dim)
+    v_dim: Optional[int] = None       # elements of a value row (default head_dim)
+
+    @property
+    def key_dim(self) -> int:
+        return self.head_dim if self.k_dim is None else self.k_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
     def group_key(self):
-        return (self.kv_heads, self.head_dim, self.window)
+        return (self.kv_heads, self.key_dim, self.value_dim, self.window)
 
 
 @dataclass(frozen=True)
@@ -61,10 +75,55 @@ class BuildContext:
 @dataclass
 class LayerBinding:
     """What one entry of the layer schedule got from the cache manager."""
-    kv_plane: Optional[torch.Tensor] = None   # [pages, 2, kv_heads, page_size, head_dim]
+    kv_plane: Optional[torch.Tensor] = None   # [pages, 2, kv_heads, page_size, head_dim] (None when k_dim != v_dim)
     kv_group: Optional[int] = None            # index of the plane's group (block tables, page size)
     kv_write: bool = True                     # False: the entry reads a plane that another entry fills
     state: Optional[torch.Tensor] = None      # [slots, *StateSpec.shape]
+    k_pages: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, k_dim]: the key rows of every page
+    v_pages: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, v_dim]: the value rows of every page
+
+
+class StepPlanner:
+    """What a mixer's kernels want to know about a step beyond rows, positions and slots — for
+    instance how the rows are cut into the tiles its kernel takes.  The engine calls ``plan`` on
+    the host while it lays the step out, uploads the int32 arrays it returns in the same copy as
+    the step's own arrays, and hands their device views to ``bind``; the mixer gets the result
+    from ``step.plan(planner)``.  Planners with equal ``key`` are one planner: their arrays are
+    made once per step whatever number of layers asks for them."""
+
+    key = None
+
+    def max_words(self, rows: int) -> int:
+        """An upper bound on the total length of the arrays for a step of ``rows`` rows (sizes
+        the fixed metadata buffer of a captured step)."""
+        raise NotImplementedError
+
+    def plan(self, segments):
+        """``segments``: [(first row, rows)] of the step, one per request (padding rows as
+        segments of one row).  Returns ({array name: list of ints}, host-side facts)."""
+        raise NotImplementedError
+
+    def plan_decode(self, rows: int):
+        """``plan`` for a step of ``rows`` single-token segments (override when that is cheaper)."""
+        return self.plan([(r, 1) for r in range(rows)])
+
+    def bind(self, arrays: Dict[str, torch.Tensor], facts):
+        """What the mixer wants to get: by default the device arrays and the facts as they are."""
+        return arrays, facts
+
+    def infer(self, positions: torch.Tensor, row_slot: torch.Tensor):
+        """The plan from the device arrays alone (synchronises; for calls outside a step, as in
+        kernel tests): consecutive rows with one slot and consecutive positions form a segment."""
+        pos, slot = positions.tolist(), row_slot.tolist()
+        segs = []
+        for r in range(len(pos)):
+            if segs and slot[r] >= 0 and slot[r] == slot[r - 1] and pos[r] == pos[r - 1] + 1:
+                segs[-1] = (segs[-1][0], segs[-1][1] + 1)
+            else:
+                segs.append((r, 1))
+        arrays, facts = self.plan(segs)
+        dev = positions.device
+        return self.bind({k: torch.tensor(v, dtype=torch.int32, device=dev) for k, v in arrays.items()}, facts)
 
 
 class Part:
@@ -103,6 +162,10 @@ class Norm(Part):
     """``forward(x) -> y`` on the 32-bit residual stream; ``add_norm`` first adds a
     pending update to the stream in place, then normalises it."""
 
+    @classmethod
+    def from_config(cls, cfg, prefix: str):
+        raise NotImplementedError
+
     def forward(self, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -111,7 +174,24 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Turns positions into what a mixer applies to queries and keys."""
+    """Turns positions into what is applied to queries and keys before they meet.
+
+    ``encode_and_store(qkv, step, ...)``: ``qkv`` holds, per row, the queries of ``num_heads``
+    heads, then the keys and then the values of ``kv_heads`` heads (``head_dim`` each).  The
+    encoding is applied to queries (in place) and keys at the rows' positions
+    (``step.positions``), and — when ``plane`` is given — the encoded keys and the values of every
+    row are written into the row's page of the cache, in the cache's row format.  Keys are
+    stored *after* encoding, so an encoding must depend on the absolute position only.
+    One fused kernel does all of it for the rotary family; an encoding of another kind brings
+    its own way and still ends with the cache write."""
+
+    @classmethod
+    def from_config(cls, cfg):
+        raise NotImplementedError
+
+    def encode_and_store(self, qkv: torch.Tensor, step, *, num_heads: int, kv_heads: int, head_dim: int,
+                         plane: Optional[torch.Tensor], block_table: Optional[torch.Tensor], page_size: int) -> None:
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -133,8 +213,15 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
-    def tile_group_sizes(self) -> Tuple[int, ...]:
-        """Query heads per kv head for which the step should plan attention tiles."""
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int, lag: int, position=None):
+        """Build the mixer of layer ``layer_index`` from the model configuration.  ``lag``: the
+        layer belongs to a stage that runs this many positions behind the trunk; ``position``:
+        the model's position encoding (a mixer that needs none ignores it)."""
+        raise NotImplementedError
+
+    def step_planners(self) -> Tuple[StepPlanner, ...]:
+        """Planners whose arrays the engine should make and upload with every step."""
         return ()
 
     def forward(self, x, step, binding: LayerBinding):
@@ -143,6 +230,10 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """``forward(x, step) -> (n, width)``, row by row: no cache, no state."""
+
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int):
+        raise NotImplementedError
 
     def forward(self, x, step):
         raise NotImplementedError

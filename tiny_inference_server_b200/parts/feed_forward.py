@@ -29,6 +29,10 @@ class SwiGLU(FeedForward):
         self.w_down = None
         self.block = hidden
 
+    @classmethod
+    def from_config(cls, cfg, prefix: str, layer_index: int):
+        return cls(cfg.hidden_size, cfg.ffn_hidden, prefix=prefix)
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {
             self.names["gate"]: WeightSpec((self.width, self.hidden)),

@@ -23,6 +23,10 @@ class RMSNormL2(Norm):
         self.scale: Optional[torch.Tensor] = None
         self.out_dtype = torch.float32
 
+    @classmethod
+    def from_config(cls, cfg, prefix: str):
+        return cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix)
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {self.weight_name: WeightSpec((self.width,), init="ones_normal")}
 

@@ -5,6 +5,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from ..registry import register_part
 from .base import BuildContext, PositionEncoding
 
@@ -30,6 +31,10 @@ class RotaryHalf(PositionEncoding):
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
 
+    @classmethod
+    def from_config(cls, cfg):
+        return cls(cfg.head_dim, cfg.rope_theta, cfg.max_context)
+
     def tables(self):
         i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
         inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rotary_dim)
@@ -41,8 +46,18 @@ class RotaryHalf(PositionEncoding):
         self.cos = cos.to(ctx.device).contiguous()
         self.sin = sin.to(ctx.device).contiguous()
 
+    def encode_and_store(self, qkv, step, *, num_heads, kv_heads, head_dim, plane, block_table, page_size) -> None:
+        """One kernel: rotate queries (in place) and keys in float32 and write keys and values of
+        every row into its page (upstream does the three in turn: main_models_new.py:75-80,
+        108-112)."""
+        ops.rope_kv_write(qkv, step.positions, step.row_slot, self.cos, self.sin, plane, block_table, num_heads,
+                          kv_heads, head_dim, page_size, step.fault, interleaved=self.interleaved,
+                          write_kv=plane is not None)
+
 
 class RotaryInterleaved(RotaryHalf):
+    """Pairs (2i, 2i+1) instead of (i, i + rot/2); the same angles."""
+
     def __init__(self, head_dim: int, theta: float, max_positions: int, rotary_dim: Optional[int] = None,
                  prefix: str = ""):
         super().__init__(head_dim, theta, max_positions, rotary_dim, interleaved=True, prefix=prefix)

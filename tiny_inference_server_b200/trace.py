@@ -30,7 +30,7 @@ from .config.engine_config import EngineConfig
 from .engine.batch import StepEntry
 from .engine.runner import ModelRunner
 
-#: requests live at a time that a replay is sized for (a trace holds at most four)
+#: requests live at a time that a replay is sized for unless told otherwise
 MAX_LIVE = 8
 
 
@@ -84,14 +84,27 @@ class TraceReplayer:
                 done.flush()
 
 
+def pages_for(max_tokens: int, page_size: int, max_live: int) -> int:
+    """Pages that hold ``max_tokens`` tokens of live requests, each request's count having been
+    rounded up to a multiple of 64.  A page size that divides 64 wastes nothing.  Any other
+    needs up to ceil(64 / page_size) pages for each 64 tokens of a request when it is smaller
+    than 64, and one page more per live request when it is larger (the request's count is
+    then rounded up to whole pages instead)."""
+    if 64 % page_size == 0:
+        return max(1, max_tokens // page_size + (1 if max_tokens % page_size else 0))
+    if page_size < 64:
+        return max(1, (max_tokens + 63) // 64 * ((64 + page_size - 1) // page_size))
+    return max(1, (max_tokens + page_size - 1) // page_size + max_live)
+
+
 def make_runner(model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, mtp: bool = False,
-                device: str = "cuda:0", cuda_graphs: bool = True) -> ModelRunner:
-    """A runner whose cache pool is made for ``max_tokens`` tokens (each request's count
-    rounded up to whole pages), so that a trace which ends and starts requests uses pages
-    again."""
-    num_pages = max(1, (max_tokens + page_size - 1) // page_size)
-    eng = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, max_batch=MAX_LIVE, mtp=mtp,
-                       cuda_graphs=cuda_graphs, device=device)
+                device: str = "cuda:0", cuda_graphs: bool = True, max_live: int = MAX_LIVE,
+                debug_poison: bool = False) -> ModelRunner:
+    """A runner whose cache pool is made for ``max_tokens`` tokens (``pages_for``), so that a
+    trace which ends and starts requests uses pages again."""
+    eng = EngineConfig(dtype=dtype, page_size=page_size, num_pages=pages_for(max_tokens, page_size, max_live),
+                       max_batch=max_live, mtp=mtp, cuda_graphs=cuda_graphs, device=device,
+                       debug_poison=debug_poison)
     return ModelRunner.from_folder(model_dir, eng)
 
 
@@ -102,13 +115,14 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time; sizes the cache pool")
-    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--max-live", type=int, default=MAX_LIVE, help="most requests live at a time")
     ap.add_argument("--mtp", action="store_true", help="also run the MTP heads and write <step>.mtp<i>.f32")
     args = ap.parse_args(argv)
-    if 64 % args.page_size:
-        ap.error("--page-size must divide 64")
+    if args.page_size <= 0 or args.max_live <= 0:
+        ap.error("--page-size and --max-live must be positive")
     print("[trace_run] loading model and kernels ...", file=sys.stderr, flush=True)
-    runner = make_runner(args.model, args.dtype, args.max_tokens, args.page_size, args.mtp)
+    runner = make_runner(args.model, args.dtype, args.max_tokens, args.page_size, args.mtp, max_live=args.max_live)
     from .kernels import ops
     ops.library()
     print("[trace_run] ready", file=sys.stderr, flush=True)
