@@ -1,6 +1,6 @@
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--sizes 3b,8b]
     python bench.py --impl reference        (the upstream project's own code, if installed)
 
 A "step" is one decode step: every live request gets one token.  The default run has the
@@ -9,7 +9,10 @@ layer sizes of the upstream 0.9B model (30 layers, width 1536, 12 query and 3 kv
 8 requests that each hold about 4096 tokens of (synthetic) cache, bfloat16.  It prints
 one JSON line: decode tokens a second timed on the device with CUDA events (``value``),
 the same through the Python entry point with host tokens in and out (``e2e``), a prefill
-of 2048 tokens, the decode step's HBM roofline, and decode at batch 1 and 64.
+of 2048 tokens (replayed from the graph of its shape, and launched for the first time), the decode
+step's HBM roofline, decode at batch 1 and 64, at contexts 1024 and 8192 and with the two MTP heads
+running beside the trunk, and the same points for the 3B- and 8B-sized members of the family
+(``gqa_mtp_3b``, ``gqa_mtp_8b``: all their layers, context 8192, weights made on the device).
 The step reads ~1.6 GB of weights and ~1.5 GB of cache, far more than the 126 MB L2, so
 no L2 flush is needed between timed steps.
 """
@@ -28,16 +31,29 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# the upstream 0.9B model (Config/config.py:11-23; vocabulary rounded up as BASELINE.json configs[2] gives it)
+# the upstream 0.9B model (Config/config.py:11-23), its vocabulary rounded up to a multiple of 128
 MODEL = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=30, num_heads=12,
              num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
              tie_word_embeddings=True, num_mtp_heads=2)
+# two larger members of the same family (the layer sizes of Llama-3.2-3B and Llama-3-8B, with two MTP heads)
+MODEL_3B = dict(architecture="gqa_mtp_transformer", vocab_size=128256, hidden_size=3072, num_layers=28, num_heads=24,
+                num_kv_heads=8, head_dim=128, ffn_hidden=8192, rms_norm_eps=1e-5, rope_theta=500000.0,
+                max_context=8192, tie_word_embeddings=True, num_mtp_heads=2)
+MODEL_8B = dict(architecture="gqa_mtp_transformer", vocab_size=128256, hidden_size=4096, num_layers=32, num_heads=32,
+                num_kv_heads=8, head_dim=128, ffn_hidden=14336, rms_norm_eps=1e-5, rope_theta=500000.0,
+                max_context=8192, tie_word_embeddings=False, num_mtp_heads=2)
+SIZES = {"0.9b": (MODEL, 4096), "3b": (MODEL_3B, 8192), "8b": (MODEL_8B, 8192)}
 CONTEXT = 4096
 PAGE = 16
 PREFILL_TOKENS = 2048
 # upstream's published iteration time at batch 8 without speculation: 31.7 ms on an RTX A6000
 # (its README, "iteration time p50, batch 8") -> 8 / 0.0317 tokens a second
 BASELINE_TOK_S = 8 / 0.0317
+
+
+def metric_name(batch):
+    """The same words from both arms (the model each arm ran is named in its ``config``)."""
+    return f"decode tokens per second at batch {batch}, context {CONTEXT}, 0.9B GQA+MTP model, bf16, random weights"
 
 
 def peaks():
@@ -84,16 +100,34 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def model_bytes_and_flops(cfg, n_layers, batch, ctx, elem=2):
+def model_bytes_and_flops(cfg, n_layers, batch, ctx, elem=2, mtp_heads=0):
+    """Bytes a decode step has to read (every weight it uses once, the cache of the live requests;
+    upstream's formula, evals.py:143-153) and the flops of a 2048-token prefill that wants one row of
+    logits (products 2*T*weights, causal attention 4*T^2*H*hd/2 per layer)."""
     d, H, KVH, hd, F, V = (cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"],
                            cfg["ffn_hidden"], cfg["vocab_size"])
     per_layer = d * (H + 2 * KVH) * hd + H * hd * d + 2 * d * F + F * d
     weights = n_layers * (per_layer + 2 * d) + d + V * d            # blocks, norms, final norm, output matrix
-    kv_per_token = n_layers * 2 * KVH * hd
+    weights += mtp_heads * (2 * d * d + per_layer + 4 * d)          # per head: input projection, one block, norms
+    kv_per_token = (n_layers + mtp_heads) * 2 * KVH * hd
     decode_bytes = (weights + batch * ctx * kv_per_token) * elem
     t = PREFILL_TOKENS
     prefill_flops = 2 * t * n_layers * per_layer + n_layers * 4 * t * t * H * hd / 2 + 2 * d * V
     return decode_bytes, prefill_flops
+
+
+def device_random_tensors(specs, seed, device, std=0.02):
+    """Random weights made on the device (the random-weights mode of the package draws on the host and
+    writes a folder, which for billions of parameters takes minutes): N(0, std), norm scales 1 + N(0, std)."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    out = {}
+    for name, spec in specs.items():
+        t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=g)
+        if spec.init == "ones_normal":
+            t += 1.0
+        out[name] = t.to(spec.dtype or torch.bfloat16)
+    return out
 
 
 def fill_cache(runner, slots, length):
@@ -173,11 +207,15 @@ def e2e_run(engine, batch, start_len, steps, warmup):
 
 
 def prefill_run(runner, tokens, reps=3):
+    """A prompt of ``tokens`` tokens in one step.  Returns (best, first): the best of ``reps`` runs once
+    the step's shape has come back (from its second occurrence the engine replays it from a CUDA graph,
+    as a server that cuts prompts at its token budget would see), and the time of the first run that
+    is launched kernel by kernel after one warm-up run of the same shape with graphs off."""
     import torch
     from tiny_inference_server_b200.engine import StepEntry
     gen = torch.Generator().manual_seed(4)
-    best = None
-    for _ in range(reps + 1):
+
+    def once():
         ids = torch.randint(0, runner.vocab_size, (tokens,), generator=gen).tolist()
         s = runner.add_request()
         torch.cuda.synchronize()
@@ -186,10 +224,63 @@ def prefill_run(runner, tokens, reps=3):
         runner.step([StepEntry(s, ids, [tokens - 1])])
         ev1.record()
         torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1)
         runner.release(s)
-        best = ms if best is None else min(best, ms)     # the first pass warms up
-    return best
+        return ev0.elapsed_time(ev1)
+
+    graphs, runner.step_graphs = runner.step_graphs, None
+    once()                                               # warms up (library handles, autotuned products)
+    first = once()                                       # launched from Python, no graph
+    runner.step_graphs = graphs
+    best = min(once() for _ in range(reps + 1))          # the second run captures, later ones replay
+    return best, first
+
+
+def build_runner(cfg_dict, ctx, max_batch, mtp, seed=0):
+    """A runner for ``cfg_dict`` with random weights made on the device and a pool for ``max_batch``
+    requests of ``ctx`` tokens."""
+    import torch
+    from tiny_inference_server_b200.config import EngineConfig
+    from tiny_inference_server_b200.engine import ModelRunner
+    from tiny_inference_server_b200.registry import build_model, config_from_dict
+    cfg = config_from_dict(dict(cfg_dict))
+    tensors = device_random_tensors(build_model(cfg).expected_tensors(), seed, torch.device("cuda:0"))
+    eng_cfg = EngineConfig(dtype="bfloat16", page_size=PAGE, num_pages=max_batch * (ctx // PAGE) + 8,
+                           max_batch=max_batch, max_tokens_per_step=PREFILL_TOKENS, mtp=mtp)
+    runner = ModelRunner(cfg, tensors, eng_cfg)
+    del tensors
+    return cfg, runner
+
+
+def size_points(name, args, pk, count_ops):
+    """Decode at batch 1 / 8 / 64 and a 2048-token prefill for one of the larger members of the family,
+    each with its fraction of the roofline."""
+    import gc
+    import torch
+    from tiny_inference_server_b200.sampling import Sampler
+    cfg_dict, ctx = SIZES[name]
+    out = {"layers": cfg_dict["num_layers"], "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_heads"],
+           "kv_heads": cfg_dict["num_kv_heads"], "ffn": cfg_dict["ffn_hidden"], "vocab": cfg_dict["vocab_size"],
+           "tied": cfg_dict["tie_word_embeddings"], "seq_len": ctx, "mtp_heads_run": 0}
+    runner = None
+    try:
+        cfg, runner = build_runner(cfg_dict, ctx, 64, mtp=False)
+        steps = max(8, args.steps // 4)
+        start_len = ctx - (steps + args.warmup) - 2
+        for b in (1, 8, 64):
+            ms, _ = decode_run(runner, b, start_len, steps, args.warmup, Sampler, count_ops)
+            nbytes, flops = model_bytes_and_flops(cfg_dict, cfg_dict["num_layers"], b, ctx)
+            out[f"decode_b{b}"] = round(b / (ms * 1e-3), 1)
+            out[f"decode_b{b}_hbm_frac"] = round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        best, first = prefill_run(runner, PREFILL_TOKENS, reps=2)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / (best * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(best, 3), "first_run_ms": round(first, 3),
+                          "frac": round(flops / (best * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    except Exception as e:                               # noqa: BLE001 - an extra point must not cost the headline
+        out["error"] = f"{type(e).__name__}: {e}"[:200]
+    del runner
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
 
 
 def reference_arm(args):
@@ -257,7 +348,7 @@ def reference_arm(args):
         live = len(sched.active)
         value = live / (ms * 1e-3)
         print(json.dumps({
-            "impl": "reference", "metric": "decode tok/s at batch 8, context 4096 (upstream 0.9B model, random weights)",
+            "impl": "reference", "metric": metric_name(args.batch),
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
             "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
@@ -282,7 +373,8 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=MODEL["num_layers"], help="fewer layers than the model (named in config)")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, other contexts, MTP heads and prefill")
+    ap.add_argument("--sizes", default="3b,8b", help="larger members of the family to measure too (3b, 8b; '' = none)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
@@ -291,25 +383,16 @@ def main(argv=None):
         return 2
     args.warmup = max(args.warmup, 3)
 
+    import gc
     import torch
     from tiny_inference_server_b200.api import Engine
-    from tiny_inference_server_b200.config import EngineConfig
-    from tiny_inference_server_b200.engine import ModelRunner
     from tiny_inference_server_b200.kernels import ops
-    from tiny_inference_server_b200.registry import config_from_dict
     from tiny_inference_server_b200.sampling import Sampler
-    from tiny_inference_server_b200.weights import write_random_model
 
     cfg_dict = dict(MODEL, num_layers=args.layers)
-    cfg = config_from_dict(cfg_dict)
     pk = peaks()
-    tmp = tempfile.TemporaryDirectory()
-    folder = write_random_model(tmp.name, cfg, seed=0)
     max_batch = max(64, args.batch)
-    pages_per_req = CONTEXT // PAGE
-    eng_cfg = EngineConfig(dtype="bfloat16", page_size=PAGE, num_pages=max_batch * pages_per_req + 8,
-                           max_batch=max_batch, max_tokens_per_step=PREFILL_TOKENS, mtp=False)
-    runner = ModelRunner.from_folder(folder, eng_cfg)
+    cfg, runner = build_runner(cfg_dict, CONTEXT, max_batch, mtp=False)
     count_ops = lambda: ops.launches  # noqa: E731
     start_len = CONTEXT - (args.steps + args.warmup) - 2
 
@@ -322,7 +405,7 @@ def main(argv=None):
     decode_bytes, prefill_flops = model_bytes_and_flops(cfg_dict, args.layers, args.batch, CONTEXT)
     achieved = decode_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8, context 4096 (0.9B GQA+MTP model, random weights)",
+        "metric": metric_name(args.batch),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
@@ -353,16 +436,50 @@ def main(argv=None):
 
     if not args.no_points:
         points = {}
+        half = max(8, args.steps // 2)
         for b in (1, 64):
-            pms, _ = decode_run(runner, b, start_len, max(8, args.steps // 2), args.warmup, Sampler, count_ops)
+            pms, _ = decode_run(runner, b, start_len, half, args.warmup, Sampler, count_ops)
+            nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, b, CONTEXT)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            points[f"decode_b{b}_hbm_frac"] = round(nbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        # a shorter context on the same runner
+        pms, _ = decode_run(runner, args.batch, 1024 - (half + args.warmup) - 2, half, args.warmup, Sampler, count_ops)
+        nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, args.batch, 1024)
+        points[f"decode_b{args.batch}_ctx1024"] = round(args.batch / (pms * 1e-3), 1)
+        points[f"decode_b{args.batch}_ctx1024_hbm_frac"] = round(nbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         out["points"] = points
-        pf_ms = prefill_run(runner, PREFILL_TOKENS)
+        pf_ms, pf_first = prefill_run(runner, PREFILL_TOKENS)
         out["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
-                          "ms": round(pf_ms, 3),
+                          "ms": round(pf_ms, 3), "first_run_ms": round(pf_first, 3),
                           "frac": round(prefill_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        del engine, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        # a longer context, and the MTP heads beside the trunk (runners of their own)
+        try:
+            _, r2 = build_runner(dict(cfg_dict, max_context=8192), 8192, args.batch, mtp=False)
+            pms, _ = decode_run(r2, args.batch, 8192 - (half + args.warmup) - 2, half, args.warmup, Sampler, count_ops)
+            nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, args.batch, 8192)
+            points[f"decode_b{args.batch}_ctx8192"] = round(args.batch / (pms * 1e-3), 1)
+            points[f"decode_b{args.batch}_ctx8192_hbm_frac"] = round(nbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            del r2
+            gc.collect()
+            torch.cuda.empty_cache()
+            _, r3 = build_runner(cfg_dict, CONTEXT, args.batch, mtp=True)
+            pms, _ = decode_run(r3, args.batch, start_len, half, args.warmup, Sampler, count_ops)
+            nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, args.batch, CONTEXT, mtp_heads=cfg.num_mtp_heads)
+            points[f"decode_b{args.batch}_mtp{cfg.num_mtp_heads}"] = round(args.batch / (pms * 1e-3), 1)
+            points[f"decode_b{args.batch}_mtp{cfg.num_mtp_heads}_hbm_frac"] = \
+                round(nbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            del r3
+        except Exception as e:                           # noqa: BLE001 - an extra point must not cost the headline
+            points["error"] = f"{type(e).__name__}: {e}"[:200]
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name in [x for x in args.sizes.split(",") if x]:
+            if name in SIZES and name != "0.9b":
+                out[f"gqa_mtp_{name}"] = size_points(name, args, pk, count_ops)
     print(json.dumps(out))
-    tmp.cleanup()
     return 0
 
 

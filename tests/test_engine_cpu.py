@@ -87,6 +87,26 @@ def test_step_in_flight_changes_nothing(name, tmp_path, ref_ops):
     assert eng.runner.cache.drained()
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("how", ["plain", "chunked", "preempted", "step_by_step"])
+def test_mtp_heads_beside_the_trunk_through_the_engine(name, how, tmp_path, ref_ops):
+    """``EngineConfig.mtp``: every step also runs the MTP heads; their logits equal the plain
+    implementation's under chunked prompts, preemption with recomputation, and the step in flight."""
+    import engine_checks
+    cfg, page, _ = tiny_configs.ALL[name]
+    kw = {"plain": {}, "step_by_step": {},
+          "chunked": dict(max_tokens_per_step=5, max_batch=3),
+          "preempted": dict(num_pages=5 if name == "A" else 9, admission="cur", max_tokens_per_step=16)}[how]
+    lengths = [page - 1] * 4 if how == "preempted" else (3, 11, 20, 6)
+    eng, reqs, _ = engine_checks.check_mtp_logits_through_engine(
+        _engine, name, tmp_path, 2e-4, lengths=lengths, new=12, engine_kw=kw, pipeline=how != "step_by_step",
+        expect_preemption=how == "preempted")
+    c, W = plain_model.read_config(str(tmp_path / f"mtp{name}")), plain_model.read_weights(str(tmp_path / f"mtp{name}"))
+    for r in reqs:
+        assert r.out_ids() == plain_model.plain_greedy(c, W, r.ids[:r.prompt_len], 12)
+    assert (eng.steps_behind > 0) == (how != "step_by_step")
+
+
 @pytest.mark.parametrize("seed", range(12))
 def test_random_workloads_equal_plain(seed, tmp_path, ref_ops):
     """Workloads drawn at random — number and lengths of prompts, tokens to generate, an

@@ -80,6 +80,50 @@ def test_step_in_flight_float32(name, graphs, tmp_path):
     assert outs[0] == outs[1]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("name,how", [("A", "plain"), ("A", "chunked"), ("A", "preempted"), ("B", "plain"),
+                                      ("B", "chunked"), ("B", "preempted"), ("B", "step_by_step")])
+def test_mtp_heads_beside_the_trunk_through_the_engine(name, how, graphs, dtype, tmp_path):
+    """``EngineConfig.mtp``: the MTP heads run in every step of generation, inside the decode graph and
+    the step kept in flight (where the head's input reads tokens fed on the device); their logits equal
+    the plain implementation's under chunked prompts and under preemption with recomputation (upstream
+    checks its heads by speculative decoding giving the tokens of plain decoding, test_server.py:104-118)."""
+    import engine_checks
+    cfg, page, _ = tiny_configs.ALL[name]
+    kw = {"plain": {}, "step_by_step": {},
+          "chunked": dict(max_tokens_per_step=5, max_batch=3),
+          "preempted": dict(num_pages=5 if name == "A" else 9, admission="cur", max_tokens_per_step=16)}[how]
+    kw = dict(kw, dtype=dtype, cuda_graphs=graphs)
+    lengths = [page - 1] * 4 if how == "preempted" else (3, 11, 20, 6)
+    eng, reqs, worst = engine_checks.check_mtp_logits_through_engine(
+        _engine, name, tmp_path, 2e-4 if dtype == "float32" else 3e-2, lengths=lengths, new=14, engine_kw=kw,
+        pipeline=how != "step_by_step", expect_preemption=how == "preempted")
+    assert (eng.steps_behind > 0) == (how != "step_by_step")
+    if graphs:
+        assert eng.runner.graphs is not None and eng.runner.graphs.replays > 5
+    if dtype == "float32":
+        c, W = plain_model.read_config(str(tmp_path / f"mtp{name}")), plain_model.read_weights(str(tmp_path / f"mtp{name}"))
+        for r in reqs:
+            assert r.out_ids() == plain_model.plain_greedy(c, W, r.ids[:r.prompt_len], 14)
+
+
+def test_step_phases_are_timed_when_asked(tmp_path):
+    """``EngineConfig.profile``: host and device time per phase of the steps, in ``Engine.stats()``
+    (upstream's Probe, evals.py:42-83, gives admit / prefill / decode times the same way)."""
+    from tiny_inference_server_b200.api import SamplingParams
+    cfg, page, folder, c, W = _model("A", tmp_path)
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], [9, 30], seed=3)
+    eng = _engine(folder, page, profile=True)
+    eng.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0, ignore_eos=True))
+    ph = eng.stats()["phases"]
+    assert ph["steps"] >= 12
+    assert set(ph["host_ms"]) >= {"admit", "plan", "launch", "read_back"}
+    assert ph["device_ms"]["prefill"] > 0 and ph["device_ms"]["decode"] > 0
+    assert ph["calls"]["device:decode"] >= 10 and ph["calls"]["device:prefill"] >= 1
+    assert "phases" not in _engine(folder, page).stats()
+
+
 def test_greedy_generation_with_preemption_float32(tmp_path):
     from tiny_inference_server_b200.api import SamplingParams
     cfg, page, folder, c, W = _model("A", tmp_path)

@@ -563,7 +563,7 @@ def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
         ops.TC_ATTENTION = tc
         try:
             fault_dev = fault.cuda()
-            launches = ops.launches
+            tc_before = ops.calls["attn_tc"]
             got = ops.paged_attention(q.cuda(), torch.full((n, H * hd), 7.0, dtype=dtype, device="cuda"), plane.cuda(),
                                       table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window,
                                       fault_dev, Step())
@@ -571,6 +571,8 @@ def test_tcgen05_attention(H, KVH, hd, page, window, monkeypatch):
         finally:
             ops.TC_ATTENTION = True
         assert int(fault_dev[0]) == 0
+        # the first arm must have run the tcgen05 kernel (every size here is one it takes), the second not
+        assert ops.calls["attn_tc"] - tc_before == (1 if tc else 0)
         outs[tc] = got.cpu().float()
         valid = row_slot >= 0
         torch.testing.assert_close(outs[tc][valid], want.float()[valid], rtol=2e-2, atol=2e-2)

@@ -24,7 +24,8 @@ ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)),
 LENGTHS_WIDE = [70, 33, 150, 5, 200, 90]
 LENGTHS = {"WIDE": LENGTHS_WIDE, "A": [1, 7, 16, 33, 50, 97, 64, 80, 120, 111, 70], "B": [2, 9, 31, 64, 100, 130, 77, 90, 128, 200],
            "C": [3, 40, 61, 90, 150, 70, 101, 64, 33, 88], "D": [5, 18, 47, 80, 33, 60, 90, 64, 71],
-           "E": [300, 64, 129, 7, 200, 450, 90, 33], "F": [4, 50, 73, 120, 31, 150, 64, 97]}
+           "E": [300, 64, 129, 7, 200, 450, 90, 33], "F": [4, 50, 73, 120, 31, 150, 64, 97],
+           "G": [2100]}
 # float32: rounding of a float32 engine against a float64 oracle.
 # bfloat16: weights are the same bfloat16 numbers on both sides; activations are rounded
 # to bfloat16 between kernels (8 bits of mantissa) on logits of size ~0.1-1.
@@ -102,6 +103,103 @@ def test_replay_matches_plain(name, mode, dtype, tmp_path, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C", "E"])
+def test_replay_with_poisoned_free_pages(name, dtype, tmp_path, tmp_path_factory):
+    """The debugging mode that overwrites every page with a large pattern when it is given back (a request
+    ends, a window has passed): nothing reads a page that its request no longer holds, so the logits of the
+    mixed replay — pages used again, windows giving pages back — stay what they are."""
+    from tiny_inference_server_b200.cache.pages import POISON
+    cfg, page, folder, seqs, plain = _setup(name, tmp_path_factory)
+    steps = _steps("mixed", seqs)
+    runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True,
+                         debug_poison=True)
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    assert runner.cache.drained()
+    pool = runner.cache.groups[0].pool
+    assert pool.allocations > pool.num_pages
+    assert float(runner.cache.groups[0].pages.float().max()) == POISON       # the pool was poisoned
+    _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("A", 24), ("B", 5), ("D", 96)])
+def test_replay_with_page_sizes_that_do_not_divide_64(name, page, dtype, tmp_path, tmp_path_factory):
+    cfg, _, folder, seqs, plain = _setup(name, tmp_path_factory)
+    steps = _steps("mixed", seqs)
+    runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True,
+                         max_live=4)
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    runner.cache.check()
+    assert runner.cache.drained()
+    _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_of_up_to_64_rows(dtype, tmp_path, tmp_path_factory):
+    """Sixty requests live at once: decode steps of 33..60 rows (the graph bucket of 64 rows, 60 tiles in
+    keys mode, library products at that many rows, sampling-free logits of every row) against the plain
+    implementation, main and MTP logits at every position."""
+    cfg, page, seed = tiny_configs.ALL["A"]
+    folder = tiny_configs.make_model_folder(cfg, seed, str(tmp_path / "m"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    lengths = [3 + (7 * i) % 23 + 18 for i in range(60)]
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], lengths, seed=77)
+    seqs = {f"r{i}": p for i, p in enumerate(prompts)}
+    plain = {rid: plain_model.plain_forward(c, W, toks) for rid, toks in seqs.items()}
+    steps = trace_tools.trace_mixed(seqs, max_live=60, decode_from=0.3, skip_every=11)
+    assert max(len(s["entries"]) for s in steps) > 48
+    runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True,
+                         max_live=64)
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    runner.cache.check()
+    assert runner.cache.drained()
+    assert any(key[0] == 64 and g.graph is not None for key, g in runner.graphs.graphs.items()), \
+        "no decode step ran from the graph of 64 rows"
+    _compare(cfg, steps, out_dir, seqs, plain, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_across_the_context_bounds_of_the_graphs(dtype, tmp_path, tmp_path_factory):
+    """Decode graphs are kept per bound on the context (512, 1024, 2048 keys, ...), each with its own plan
+    of key splits.  One request decodes across three bounds — a new graph, another split plan, the same
+    pages — and every logit equals the plain implementation's and the run without graphs."""
+    from tiny_inference_server_b200.engine import StepEntry
+    cfg, page, folder, seqs, plain = _setup("G", tmp_path_factory)
+    toks, ref = seqs["r0"], plain["r0"]
+    # portions up to just below a bound, then single tokens across it
+    plan = [("portion", 500), ("decode", 530), ("portion", 1012), ("decode", 1040), ("portion", 2040),
+            ("decode", 2075)]
+    got = {}
+    for graphs in (True, False):
+        runner = make_runner(folder, dtype, 2304, page_size=page, mtp=True, cuda_graphs=graphs)
+        slot = runner.add_request()
+        fed, worst = 0, 0.0
+        for kind, upto in plan:
+            cuts = [upto - fed] if kind == "portion" else [1] * (upto - fed)
+            for n in cuts:
+                out = runner.step([StepEntry(slot, toks[fed:fed + n], [n - 1])])
+                p = fed + n - 1
+                worst = max(worst, float((out.main[0].float().cpu() - ref["main"][p].float()).abs().max()))
+                assert bool(out.aux_valid[0][0])
+                worst = max(worst, float((out.aux[0][0].float().cpu() - ref["mtp"][0][p - 1].float()).abs().max()))
+                if kind == "decode":
+                    got[(graphs, p)] = out.main[0].float().cpu().clone()
+                fed += n
+        runner.check_fault()
+        runner.release(slot)
+        assert worst < TOL[dtype], f"graphs {graphs}: worst error {worst}"
+        if graphs:
+            bounds = sorted({key[1] for key, g in runner.graphs.graphs.items() if g.graph is not None})
+            assert len(bounds) >= 3 and bounds[:3] == [512, 1024, 2048], bounds
+    for (graphs, p), v in got.items():
+        if graphs:
+            assert float((v - got[(False, p)]).abs().max()) < (2e-5 if dtype == "float32" else 3e-2), p
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mode", ["whole", "mixed"])
 def test_replay_at_the_sizes_of_the_0_9b_model(mode, dtype, tmp_path, tmp_path_factory):
     """Two layers and one MTP head with the 0.9B model's layer sizes (width 1536, 12 query
@@ -131,13 +229,15 @@ def test_replay_with_the_tcgen05_products(tmp_path, tmp_path_factory, monkeypatc
     cfg, page, folder, seqs, plain = _setup("WIDE", tmp_path_factory)
     steps = _steps("whole", seqs)
     runner = make_runner(folder, "bfloat16", trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True)
-    before = ops.launches
+    before = ops.calls["gemm_tc"]
     out_dir = str(tmp_path / "out")
     TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
     runner.check_fault()
     scale = float(max(plain[r]["main"].abs().max() for r in plain))
     _compare(cfg, steps, out_dir, seqs, plain, 1.5e-2 * scale)
-    assert ops._tc_fault is not None, "no product went to the tcgen05 kernel"
+    # the two whole prompts of 150 and 200 tokens: per layer and MTP block five products each
+    # (qkv, o, gate/up, down; the MTP input projection), none of which may have gone elsewhere
+    assert ops.calls["gemm_tc"] - before >= 2 * (4 * 3 + 1), "the products did not go to the tcgen05 kernel"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -45,7 +45,7 @@ def _call(lib, name, q, out, plane, table, positions, row_slot, tiles0, tilesn, 
             p(positions), p(row_slot), p(tiles0), p(tilesn), n]
     tail = [n, H, KVH, page, 0, scale, per, splits]
     if name == "tis_attn_mma":
-        return lib.tis_attn_mma(1, *head, 1, *tail, p(scratch), p(None), p(fault), stream)
+        return lib.tis_attn_mma(1, *head, 1, *tail, p(scratch), p(fault), stream)
     return lib.tis_attn_decode_noalloc(*head, *tail, p(fault), stream)
 
 

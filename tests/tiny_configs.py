@@ -49,6 +49,12 @@ TINY_F = dict(architecture="gqa_mtp_transformer", vocab_size=190, hidden_size=80
               full_attention_layers=[0, 3], layer_order=[0, 1, 2], cache_source=[None, None, 1])
 TINY_F_PAGE = 8
 
+# a context long enough to decode across the 512-, 1024- and 2048-key bounds that decode graphs are keyed by
+TINY_G = dict(architecture="gqa_mtp_transformer", vocab_size=320, hidden_size=96, num_layers=2, num_heads=4,
+              num_kv_heads=2, head_dim=64, ffn_hidden=160, rms_norm_eps=1e-6, rope_theta=100000.0,
+              max_context=2304, tie_word_embeddings=True, num_mtp_heads=1)
+TINY_G_PAGE = 16
+
 # the layer sizes of the upstream 0.9B model (Config/config.py:11-23), two layers and one MTP head of them
 WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=1536, num_layers=2, num_heads=12,
             num_kv_heads=3, head_dim=128, ffn_hidden=4096, rms_norm_eps=2e-8, rope_theta=10000.0, max_context=4096,
@@ -56,7 +62,7 @@ WIDE = dict(architecture="gqa_mtp_transformer", vocab_size=49152, hidden_size=15
 WIDE_PAGE = 16
 
 ALL = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2),
-       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 5), "F": (TINY_F, TINY_F_PAGE, 6),
+       "D": (TINY_D, TINY_D_PAGE, 3), "E": (TINY_E, TINY_E_PAGE, 5), "F": (TINY_F, TINY_F_PAGE, 6), "G": (TINY_G, TINY_G_PAGE, 7),
        "WIDE": (WIDE, WIDE_PAGE, 4)}
 
 

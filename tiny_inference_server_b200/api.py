@@ -18,6 +18,7 @@ from .engine.runner import ModelRunner
 from .engine.scheduler import PlannedEntry, PoolTooSmall, Request, Scheduler, StepPlan
 from .sampling.params import SamplingParams
 from .sampling.sampler import Sampler, SampleSpec
+from .engine.timers import PhaseTimers
 
 __all__ = ["Engine", "Request", "SamplingParams", "PoolTooSmall"]
 
@@ -44,7 +45,11 @@ class Engine:
         self.scheduler = Scheduler(runner.cache, max_batch=eng.max_batch, max_tokens_per_step=eng.max_tokens_per_step,
                                    max_context=runner.max_positions, admission=eng.admission, eos_token_id=eos)
         self.sampler = runner.sampler
-        self.last_aux = None
+        #: called after every model step with ([(request, position of its first token in the step,
+        #: number of its tokens)], StepOutput): the way to see the step's logits (main and MTP heads)
+        #: as generation goes; the step's rows wanted are the last row of every entry that is sampled
+        self.step_listener = None
+        self.timers = PhaseTimers(enabled=bool(eng.profile), cuda=runner.device.type == "cuda")
         #: keep one decode step in flight (see ``step``); off: every step is read back before the next
         self.pipeline = True
         self.steps_behind = 0            # steps launched before the one before them was read back
@@ -82,26 +87,35 @@ class Engine:
             done = self._collect(infl)
             self._inflight = nxt
             return done
-        for r in sch.admit():
-            self.sampler.start_request(r.slot, r.params, r.ids)
-        plan = sch.plan_step()
-        if not plan.entries:
-            return []
-        entries = []
-        for e in plan.entries:
-            r = e.request
-            spec = SampleSpec(r.params, self.sampler.request_seed(r.params, r.id), len(r.ids) - r.prompt_len) \
-                if e.sample else None
-            entries.append(StepEntry(r.slot, r.ids[r.fed:r.fed + e.n_tokens], [e.n_tokens - 1] if e.sample else [],
-                                     spec))
-        out = self.runner.step(entries)
-        self.last_aux = out.aux
+        tm = self.timers
+        tm.begin_step()
+        with tm.host("admit"):
+            for r in sch.admit():
+                self.sampler.start_request(r.slot, r.params, r.ids)
+        with tm.host("plan"):
+            plan = sch.plan_step()
+            if not plan.entries:
+                return []
+            entries = []
+            for e in plan.entries:
+                r = e.request
+                spec = SampleSpec(r.params, self.sampler.request_seed(r.params, r.id), len(r.ids) - r.prompt_len) \
+                    if e.sample else None
+                entries.append(StepEntry(r.slot, r.ids[r.fed:r.fed + e.n_tokens],
+                                         [e.n_tokens - 1] if e.sample else [], spec))
+        kind = "decode" if all(e.n_tokens == 1 for e in plan.entries) else "prefill"
+        with tm.host("launch"), tm.device(kind):
+            out = self.runner.step(entries)
+        if self.step_listener is not None:
+            self.step_listener([(e.request, e.request.fed, e.n_tokens) for e in plan.entries], out)
         if self.pipeline and self._may_stay_in_flight(plan):
             self._inflight = self._defer(plan, out)
             return []
         # the step's one device-to-host read (upstream: server.py:240)
-        tokens: List[int] = out.tokens.tolist() if out.tokens is not None else []
-        return sch.commit(plan, tokens)
+        with tm.host("read_back"):
+            tokens: List[int] = out.tokens.tolist() if out.tokens is not None else []
+        with tm.host("commit"):
+            return sch.commit(plan, tokens)
 
     # ---- one step in flight -------------------------------------------------------------
     def _may_stay_in_flight(self, plan: StepPlan) -> bool:
@@ -157,8 +171,12 @@ class Engine:
         entries = [StepEntry(r.slot, [0], [0],
                              SampleSpec(r.params, self.sampler.request_seed(r.params, r.id), len(r.ids) - r.prompt_len))
                    for r in reqs]
-        out = self.runner.step(entries, feed=(infl.device_tokens, index))
-        self.last_aux = out.aux
+        tm = self.timers
+        tm.begin_step()
+        with tm.host("launch"), tm.device("decode"):
+            out = self.runner.step(entries, feed=(infl.device_tokens, index))
+        if self.step_listener is not None:
+            self.step_listener([(r, r.fed, 1) for r in reqs], out)
         self.steps_behind += 1
         plan = StepPlan([PlannedEntry(r, 1, True) for r in reqs])
         return self._defer(plan, out)
@@ -166,11 +184,12 @@ class Engine:
     def _collect(self, infl: "_InFlight") -> List[Request]:
         """Read the tokens of a step that was left in flight and finish its bookkeeping."""
         sch = self.scheduler
-        if infl.event is not None:
-            infl.event.synchronize()
-            tokens = infl.host_tokens[: len(infl.requests)].tolist()
-        else:
-            tokens = infl.device_tokens.tolist()
+        with self.timers.host("read_back"):
+            if infl.event is not None:
+                infl.event.synchronize()
+                tokens = infl.host_tokens[: len(infl.requests)].tolist()
+            else:
+                tokens = infl.device_tokens.tolist()
         done = []
         for r, place, tok in zip(infl.requests, infl.places, tokens):
             if r.done:
@@ -222,4 +241,6 @@ class Engine:
         s = self.scheduler.stats()
         s.update(model_steps=self.runner.steps_run, steps_behind=self.steps_behind, rows_run=self.runner.rows_run,
                  pages=self.runner.cache.num_pages, free_pages=self.runner.cache.free_pages())
+        if self.timers.enabled:
+            s["phases"] = self.timers.summary()
         return s

@@ -22,9 +22,10 @@
 // Every wait on an mbarrier is bounded; one that runs out sets the fault word.
 // Scores, running maximum, sum and the output accumulate in float32; probabilities are
 // rounded to bfloat16 for the P.V product (as paged_attention_kernels.py:108 upstream).
-// With more than one key split a CTA writes a normalised partial output and its log2-sum
-// to scratch memory; the split that finishes last (a counter per tile and kv head) merges
-// them, or, when the caller gives no counters, `attn_merge_kernel` does.
+// With two to eight key splits the splits of a (tile, kv head) are one thread-block cluster
+// and merge through distributed shared memory.  With more (only callers that ask for them:
+// the engine plans at most eight) a CTA writes a normalised partial output and its log2-sum
+// to scratch memory and `attn_merge_kernel` merges them.
 #include "common.cuh"
 #include <cooperative_groups.h>
 
@@ -40,11 +41,7 @@ constexpr int NTHREADS = 128;
 // instruction stream, so CTAs per SM (three at head size 128 with two stages) count for more
 // than a deeper pipeline; measured on a B200.
 constexpr int STAGE_BYTES = 2 * KT * RS * 2;
-#ifdef TIS_ATTN_STAGES
-constexpr int STAGES = TIS_ATTN_STAGES;
-#else
 constexpr int STAGES = 2;
-#endif
 constexpr int NCH = HD / 8;          // 16-byte chunks of a cache row (permuted by the position: common.cuh)
 constexpr int KSTEPS = HD / 16;      // k16 steps of Q.K^T
 constexpr int DTILES = HD / 8;       // n8 tiles of the output
@@ -62,9 +59,8 @@ struct AttnParams {
     float scale_log2;
     int keys_per_split, num_splits;
     float* part_o; float* part_lse;
-    int* counters;          // per (tile, kv head): splits that have finished; null: merge in a kernel of its own
     int cluster_merge;      // the splits of a (tile, kv head) are one thread-block cluster and merge through
-                            // distributed shared memory: no scratch, no counters (keys mode, 2..8 splits)
+                            // distributed shared memory: no scratch (2..8 splits); else scratch + merge kernel
     int* fault;
 };
 
@@ -549,46 +545,11 @@ attn_mma_kernel(const AttnParams p) {
             const float val = lt > 0.f ? acc / lt : 0.f;
             if (p.num_splits == 1) {
                 p.out[(size_t)row * p.out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(val);
-            } else if (p.cluster_merge) {
-                float* cm_o = ml + 4 * 16;                       // [16][HD] this split's normalised output
-                float* cm_lse = cm_o + 16 * HD;                  // [16]
-                cm_o[m * HD + d] = val;
-                if (d == 0) cm_lse[m] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
             } else {
                 const size_t pr = ((size_t)row * p.H + hq) * p.num_splits + split;
                 p.part_o[pr * HD + d] = val;
                 if (d == 0) p.part_lse[pr] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
             }
-        }
-        if (p.num_splits > 1 && p.cluster_merge) {
-            // the splits of this (tile, kv head) are the CTAs of one cluster: every CTA merges its
-            // share of the outputs, reading all splits' results from their shared memory
-            namespace cg = cooperative_groups;
-            cg::cluster_group cluster = cg::this_cluster();
-            float* cm_o = ml + 4 * 16;
-            float* cm_lse = cm_o + 16 * HD;
-            cluster.sync();
-            const int ns = p.num_splits;
-            const int pairs = rows * G;
-            for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
-                const int m = idx / HD, d = idx - m * HD;
-                const int r = m / G, g = m - r * G;
-                float mt = -INFINITY;
-                for (int sp = 0; sp < ns; ++sp) mt = fmaxf(mt, cluster.map_shared_rank(cm_lse, sp)[m]);
-                float acc = 0.f, wsum = 0.f;
-                if (mt != -INFINITY) {
-                    for (int sp = 0; sp < ns; ++sp) {
-                        const float l = cluster.map_shared_rank(cm_lse, sp)[m];
-                        if (l == -INFINITY) continue;
-                        const float w = fast_exp2(l - mt);
-                        wsum += w;
-                        acc += w * cluster.map_shared_rank(cm_o, sp)[m * HD + d];
-                    }
-                }
-                p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
-                    __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
-            }
-            cluster.sync();              // nobody leaves while its shared memory may still be read
         }
     } else {
         if (p.num_splits > 1 && p.cluster_merge) __syncthreads();     // all warps are done with the last tile
@@ -654,70 +615,6 @@ attn_mma_kernel(const AttnParams p) {
             cluster.sync();
         }
     }
-
-    // ---- the split that finishes last merges all partial results of this (tile, kv head)
-    if (p.num_splits > 1 && p.counters != nullptr && !p.cluster_merge) {
-        __shared__ int sh_last;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int t = atomicAdd(&p.counters[tile * p.KVH + kvh], 1);
-            sh_last = (t == p.num_splits - 1);
-        }
-        __syncthreads();
-        if (sh_last) {
-            __threadfence();
-            // weights of every (row, head, split) first, into shared memory (the staging area is free now)
-            float* wgt = reinterpret_cast<float*>(smem_raw);
-            const int pairs = rows * G;
-            const int ns = p.num_splits;
-            const bool fits = (size_t)pairs * ns * sizeof(float) <= (size_t)STAGES * STAGE_BYTES;
-            for (int rg = warp; rg < pairs; rg += NTHREADS / 32) {
-                const int r = rg / G, g = rg - r * G;
-                const size_t pr = ((size_t)(row0 + r) * p.H + kvh * G + g) * ns;
-                float mt = -INFINITY;
-                for (int sp = lane; sp < ns; sp += 32) mt = fmaxf(mt, __ldcg(p.part_lse + pr + sp));
-                mt = warp_max(mt);
-                float ws = 0.f;
-                for (int sp = lane; sp < ns; sp += 32) {
-                    const float l = __ldcg(p.part_lse + pr + sp);
-                    ws += (l == -INFINITY) ? 0.f : exp2f(l - mt);
-                }
-                ws = warp_sum(ws);
-                const float inv = ws > 0.f ? 1.f / ws : 0.f;
-                if (fits)
-                    for (int sp = lane; sp < ns; sp += 32) {
-                        const float l = __ldcg(p.part_lse + pr + sp);
-                        wgt[rg * ns + sp] = (l == -INFINITY) ? 0.f : exp2f(l - mt) * inv;
-                    }
-            }
-            __syncthreads();
-            for (int idx = tid; idx < pairs * HD; idx += NTHREADS) {
-                const int rg = idx / HD, d = idx - rg * HD;
-                const int r = rg / G, g = rg - r * G;
-                const int row = row0 + r, hq = kvh * G + g;
-                const size_t pr = ((size_t)row * p.H + hq) * ns;
-                float acc = 0.f;
-                if (fits) {
-                    const float* w = wgt + rg * ns;
-#pragma unroll 4
-                    for (int sp = 0; sp < ns; ++sp) acc += w[sp] * __ldcg(p.part_o + (pr + sp) * HD + d);
-                } else {
-                    float mt = -INFINITY, ws = 0.f;
-                    for (int sp = 0; sp < ns; ++sp) mt = fmaxf(mt, __ldcg(p.part_lse + pr + sp));
-                    for (int sp = 0; sp < ns; ++sp) {
-                        const float l = __ldcg(p.part_lse + pr + sp);
-                        const float w = (l == -INFINITY) ? 0.f : exp2f(l - mt);
-                        ws += w;
-                        acc += w * __ldcg(p.part_o + (pr + sp) * HD + d);
-                    }
-                    acc = ws > 0.f ? acc / ws : 0.f;
-                }
-                p.out[(size_t)row * p.out_stride + (size_t)hq * HD + d] = __float2bfloat16_rn(acc);
-            }
-            if (tid == 0) p.counters[tile * p.KVH + kvh] = 0;      // ready for the next launch
-        }
-    }
 }
 
 // out[row, head] = sum_s w_s * part_o[row, head, s],  w_s = 2^(lse_s - max) / sum, for the rows of one tile
@@ -749,7 +646,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 static size_t smem_bytes(int mode) {
     size_t stage = (size_t)STAGES * STAGE_BYTES;
-    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * (HD + 4) + 2 * 4 * 16 + 16 * HD + 16) * sizeof(float)
+    size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * (HD + 4) + 2 * 4 * 16) * sizeof(float)
                                      : (size_t)(64 * HD + 64) * sizeof(float);
     return stage > merge ? stage : merge;
 }
@@ -789,8 +686,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
                          const int* block_table, int bt_stride, int num_pages, const int* positions,
                          const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
                          int max_tile_rows, int n_rows, int H, int KVH, int page_size, int window, float scale,
-                         int keys_per_split, int num_splits, float* scratch, int* counters, int* fault,
-                         cudaStream_t stream) {
+                         int keys_per_split, int num_splits, float* scratch, int* fault, cudaStream_t stream) {
     if (num_tiles <= 0) return TIS_OK;
     const int G = KVH > 0 ? H / KVH : 0;
     const int mpack = mode == MODE_ROWS ? 64 : 16;
@@ -823,7 +719,6 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.keys_per_split = keys_per_split; p.num_splits = num_splits;
     p.part_o = scratch;
     p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
-    p.counters = num_splits > 1 ? counters : nullptr;
     p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
     p.fault = fault;
     const size_t smem = smem_bytes(mode);
@@ -877,7 +772,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     }
     int st = tis_check_launch("attn_mma");
     if (st != TIS_OK) return st;
-    if (num_splits > 1 && counters == nullptr && !p.cluster_merge) {
+    if (num_splits > 1 && !p.cluster_merge) {
         dim3 mg(H, num_tiles);
         attn_merge_kernel<<<mg, HD < 128 ? (HD < 32 ? 32 : HD) : 128, 0, stream>>>(p.part_o, p.part_lse, (bf16*)out, out_stride,
                                                                                   tile_row0, tile_rows, H, num_splits);
@@ -934,5 +829,5 @@ TIS_API int tis_attn_decode_noalloc(const void* q, int q_stride, void* out, int 
     // one split needs no scratch at all; tis_attn_mma ignores the pointer then
     return tis_attn_mma(MODE_KEYS, q, q_stride, out, out_stride, plane, block_table, bt_stride, num_pages, positions,
                         row_slot, tile_row0, tile_rows, num_tiles, 0, n_rows, H, KVH, page_size, window, scale,
-                        keys_per_split, num_splits, g_noalloc_ptr[dev], nullptr, fault, stream);
+                        keys_per_split, num_splits, g_noalloc_ptr[dev], fault, stream);
 }

@@ -25,10 +25,7 @@ constexpr int BK = 64;            // rows of K per tile
 constexpr int NTH = 128;
 constexpr int WROW = BN + 8;      // padded shared-memory rows: conflict-free ldmatrix
 constexpr int XROW = BK + 8;
-#ifndef TIS_GEMM_MAX_STAGES
-#define TIS_GEMM_MAX_STAGES 4
-#endif
-constexpr int MAX_STAGES = TIS_GEMM_MAX_STAGES;   // W tiles a CTA keeps in shared memory (9 KB each), at most 8
+constexpr int MAX_STAGES = 4;     // W tiles a CTA keeps in shared memory (9 KB each), at most 8
 
 enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
 
@@ -255,11 +252,7 @@ TIS_API int tis_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
-#ifdef TIS_GEMM_NO_EARLY
-    cfg.numAttrs = 1;
-#else
     cfg.numAttrs = tis_pdl_enabled() ? 2 : 1;
-#endif
     cudaError_t e;
     static bool configured = false;
     if (!configured) {

@@ -26,8 +26,6 @@ NVCC_FLAGS = [
     "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-# further nvcc options (e.g. -D switches while tuning); part of the library's name hash
-NVCC_FLAGS += os.environ.get("TIS_NVCC_EXTRA", "").split()
 
 
 class BuildError(RuntimeError):

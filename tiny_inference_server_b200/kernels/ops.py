@@ -8,6 +8,7 @@ integer metadata is int32.  Launches go to torch's current CUDA stream.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import math
 import os
@@ -21,6 +22,9 @@ _lib = None
 ABI_VERSION = 2
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
+#: calls by kind, for tests that must know which kernel a product or an attention went to
+#: ("gemm_skinny", "gemm_tc", "gemm_library", "attn_tc", "attn_keys", "attn_rows", ...)
+calls: "collections.Counter[str]" = collections.Counter()
 
 
 class KernelError(RuntimeError):
@@ -115,7 +119,7 @@ def _ksplit(n_cols: int, k: int) -> int:
     """CTAs that share a 64-column strip of the weights (a cluster adding up over K): as many as
     keep the grid near two CTAs per SM, each with at least 128 rows of K."""
     strips = (n_cols + 63) // 64
-    ks = int(os.environ.get("TIS_KSPLIT_MAX", "8"))
+    ks = 8
     while ks > 1 and (strips * ks > 2 * 148 * 2 or k // ks < 128):
         ks //= 2
     return ks
@@ -130,6 +134,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     cols = w.shape[1]
     if out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    calls["gemm_skinny"] += 1
     _check(lib.tis_gemm_skinny(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
                                ksplit or _ksplit(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _stream()), lib)
     return out
@@ -172,6 +177,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     cols = w.shape[1]
     if out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    calls["gemm_tc"] += 1
     _check(lib.tis_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
                            EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()), _stream()), lib)
     return out
@@ -204,6 +210,7 @@ def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
         out = torch.empty((n, cols), dtype=want, device=a.device)
     elif out.dtype != want or out.stride(1) != 1 or out.stride(0) < cols:
         return None
+    calls["gemm_library"] += 1
     status = lib.tis_gemm_library(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
                                   int(f32_out), _stream())
     if status != 0:
@@ -299,19 +306,6 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, row_slot: torch.Te
 
 
 _attn_libs = {}
-_attn_counters = {}
-
-
-def _counters(device, need: int):
-    """Zeroed counters for the split-key merge (per tile and kv head); the kernel leaves them
-    zero again.  None when a launch needs more than are kept (it then merges in a second kernel)."""
-    if need > (1 << 16):
-        return None
-    t = _attn_counters.get(device)
-    if t is None:
-        t = _attn_counters[device] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-    return t
-
 
 def attention_library(head_dim: int):
     """The tensor-core attention kernels for one head size, compiled when first needed."""
@@ -438,6 +432,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
     tc_pays = wide_count >= TC_ATTENTION_MIN_TILES or max_kv <= TC_ATTENTION_SHORT_CONTEXT
     if wide_count and TC_ATTENTION and tc_pays and page_size in (16, 32, 64, 128) and alib.tc_attention:
         # long portions: the tcgen05 kernel takes them as tiles of 128 rows; the others stay below
+        calls["attn_tc"] += 1
         _check(alib.tis_attn_tc(_p(q), q.stride(0), n, _p(out), out.stride(0), _p(plane), _p(block_table),
                                 block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(w0), _p(wn),
                                 wide_count, num_heads, kv_heads, page_size, int(window or 0), _f(scale), _p(fault),
@@ -456,16 +451,12 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         if resident is None:
             resident = alib.resident[(mode, half)] = alib.tis_attn_resident_ctas(mode, half)
         per, splits = plan_splits(count, kv_heads, max_kv, mode == 1, resident, None if mode == 1 else min_kv)
-        scratch = None
-        if splits > 8:                         # up to 8 splits merge inside a cluster, without scratch
-            need = alib.tis_attn_scratch_floats(n, num_heads, splits)
-            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        calls["attn_keys" if mode == 1 else "attn_rows"] += 1
+        # at most eight splits (plan_splits): they merge inside a thread-block cluster, without scratch
         _check(alib.tis_attn_mma(mode, _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
                                  block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
                                  _p(rows), count, max_rows, n, num_heads, kv_heads, page_size, int(window or 0), _f(scale),
-                                 per, splits, _p(scratch),
-                                 _p(_counters(q.device, count * kv_heads) if splits > 8 else None),
-                                 _p(fault), _stream()), alib)
+                                 per, splits, _p(None), _p(fault), _stream()), alib)
     return out
 
 
