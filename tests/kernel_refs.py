@@ -135,8 +135,17 @@ def _unrotate_rows(x, positions):
     return out.permute(0, 2, 1, 3).reshape(L, kvh, hd)
 
 
+def rotary_fusable(q, step, num_heads, kv_heads, head_dim):
+    """On the CPU every decode step takes the path where attention does the rotary encoding and the
+    cache write itself, so that its plumbing runs in the CPU tests too."""
+    return step is not None and getattr(step, "decode_only", False)
+
+
 def paged_attention(q, out, plane, block_table, positions, row_slot, num_heads, kv_heads, head_dim, page_size,
-                    window, fault, step=None):
+                    window, fault, step=None, rotary=None, write_kv=True):
+    if rotary is not None:
+        rope_kv_write(q, positions, row_slot, rotary[0], rotary[1], plane, block_table, num_heads, kv_heads, head_dim,
+                      page_size, fault, write_kv=write_kv)
     n = q.shape[0]
     g = num_heads // kv_heads
     hq = num_heads * head_dim
@@ -274,7 +283,7 @@ def bitmap_set(bitmap_row, tokens):
         bitmap_row[t >> 5] = w - (1 << 32) if w >= (1 << 31) else w
 
 
-_NAMES = ["gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
+_NAMES = ["rotary_fusable", "gemm", "gemm_f32_out", "gemm_swiglu", "embed_rows", "add_rmsnorm", "residual_add", "rope_kv_write",
           "paged_attention", "swiglu", "mtp_input", "sample_rows", "bitmap_set"]
 
 

@@ -91,15 +91,28 @@ def test_greedy_generation_through_the_command_line(name, lengths, new, tmp_path
     assert r.returncode == 0, r.stderr
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["outputs"] == want
-    assert out["new_tokens"] == new * len(prompts) and out["stats"]["finished"] == len(prompts)
+    assert out["new_tokens"] == new * len(prompts) and out["stats"]["active"] == 0 and out["stats"]["queued"] == 0
 
-    # a token budget of five and so few pages that the scheduler cuts prompts and preempts
-    few = max(len(p) + new for p in prompts) // page + 3
-    r = _cli(*args, "--max-tokens-per-step", 5, "--num-pages", few, "--plan", "cur", "--max-batch", 4)
+    # a token budget of five: prompts are cut into portions beside decoding requests
+    r = _cli(*args, "--max-tokens-per-step", 5, "--max-batch", 3)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["outputs"] == want and out["stats"]["steps"] > sum(lengths) // 5
+
+    # so few pages that the scheduler preempts and recomputes: four prompts of a page less a token each, a pool
+    # that holds what they need now but not what they grow to, admission on current need
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], [page - 1] * 4, seed=22)
+    want = [plain_model.plain_greedy(c, W, p, new) for p in prompts]
+    args = ["--model", folder, "--greedy", "--ignore-eos", "--dtype", "float32", "--max-new-tokens", new,
+            "--tokens-per-block", page, "--json", "--num-pages", 4 + (new + page - 1) // page, "--plan", "cur",
+            "--max-batch", 4, "--max-tokens-per-step", 16]
+    for p in prompts:
+        args += ["--prompt-ids", _ids(p)]
+    r = _cli(*args)
     assert r.returncode == 0, r.stderr
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["outputs"] == want
-    assert out["stats"]["preempts"] > 0 and out["stats"]["min_free_pages"] == 0
+    assert out["stats"]["preempts"] > 0 and out["stats"]["replays"] > 0 and out["stats"]["min_free_pages"] == 0
 
 
 @pytest.mark.gpu

@@ -86,11 +86,18 @@ def test_swiglu(dtype, n, F, block):
     torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
 
 
+@pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("n", [1, 3, 8, 16, 17, 33, 64])
-@pytest.mark.parametrize("K,N", [(1536, 2304), (128, 64), (200, 120), (4096, 1536), (72, 8), (1000, 1096)])
-def test_skinny_gemm(n, K, N):
-    """The weight-streaming product for few rows, for every split of K over a cluster."""
+@pytest.mark.parametrize("K,N", [(1536, 2304), (128, 64), (200, 120), (4096, 1536), (72, 8), (1000, 1096),
+                                 (8192, 200)])
+def test_skinny_gemm(n, K, N, tma, monkeypatch):
+    """The weight-streaming products for few rows (weights as TMA boxes, a share at once — K of 8192 over
+    eight CTAs takes two rounds of boxes —; weights copied by the threads into a ring), for every split of K
+    over a cluster."""
     ops = _ops()
+    monkeypatch.setattr(ops, "STREAM_GEMM", tma)
+    monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)           # every product that fits goes to the boxes
+    before = ops.calls["gemm_stream"]
     g = torch.Generator().manual_seed(12)
     a = _rand((n, K), torch.bfloat16, g)
     w = _rand((K, N), torch.bfloat16, g, 0.05)
@@ -103,12 +110,20 @@ def test_skinny_gemm(n, K, N):
     wide = _rand((K, N + 64), torch.bfloat16, g, 0.05).cuda()
     got = ops.gemm_skinny(a.cuda(), wide[:, :N])
     torch.testing.assert_close(got.cpu().double(), a.double() @ wide[:, :N].cpu().double(), rtol=2e-2, atol=2e-2)
+    fits = sum(ops._stream_fits(n, K, ks or ops._ksplit(N, K)) for ks in (None, 1, 2, 4, 8, None))
+    assert ops.calls["gemm_stream"] - before == (fits if tma else 0) and (fits >= 4 or K == 8192)
+    if tma and ops._tc_fault is not None:
+        assert int(ops._tc_fault[0]) == 0, "a wait inside the kernel ran out"
 
 
+@pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("n", [1, 8, 40, 64])
 @pytest.mark.parametrize("K,F", [(1536, 4096), (120, 352), (64, 32)])
-def test_skinny_gemm_with_swiglu_epilogue(n, K, F):
+def test_skinny_gemm_with_swiglu_epilogue(n, K, F, tma, monkeypatch):
     ops = _ops()
+    monkeypatch.setattr(ops, "STREAM_GEMM", tma)
+    monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)
+    monkeypatch.setattr(ops, "SKINNY_SWIGLU_MAX_ROWS", 64)
     g = torch.Generator().manual_seed(13)
     a = _rand((n, K), torch.bfloat16, g)
     w = _rand((K, 2 * F), torch.bfloat16, g, 0.05)
@@ -462,6 +477,72 @@ def test_paged_attention_tensor_core_long_context_and_portions(H, KVH, hd, page,
                               table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault_dev)
     torch.testing.assert_close(got.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
     assert int(fault_dev[0]) == 0
+
+
+@pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (8, 2, 64, 16, None), (4, 4, 32, 8, None),
+                                                  (16, 1, 96, 32, None), (6, 2, 128, 64, 100), (32, 2, 64, 16, 40),
+                                                  (3, 1, 256, 16, None)])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_decode_attention_with_rotary_and_cache_write_inside(H, KVH, hd, page, window, write_kv):
+    """A decode step whose rotary encoding and cache write the attention kernel does itself, against the two
+    launches it replaces (rope_kv_write, then attention): the same outputs bit for bit and the same pages.
+    Contexts of one key, a page's edge, a tile's edge, thousands of keys (key splits), a padding row; with
+    write_kv off (a layer that reads another layer's cache) the plane must stay untouched."""
+    from tiny_inference_server_b200.kernels.attention_plan import infer_tiles
+    ops = _ops()
+    g = torch.Generator().manual_seed(41)
+    dtype = torch.bfloat16
+    lens = [1, page, page + 1, 64, 65, 700, 3000, 129]
+    plane, table = _fill_cache(dtype, lens, KVH, hd, page, g)
+    rows = [(s, L - 1) for s, L in enumerate(lens)]
+    rows.insert(3, (-1, 0))                                   # a padding row of the bucket
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    n = len(rows)
+    qkv = _rand((n, (H + 2 * KVH) * hd), dtype, g)
+    ang = torch.outer(torch.arange(3000, dtype=torch.float64),
+                      torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2) / hd))
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+
+    class Step:
+        decode_only = True
+        max_position, min_position = 2999, 0
+        tiles = infer_tiles(positions.cuda(), row_slot.cuda(), H // KVH)
+
+        def plan(self, planner):
+            return self.tiles
+
+    # the two launches
+    fault = torch.zeros(4, dtype=torch.int32, device="cuda")
+    q1, plane1 = qkv.cuda().clone(), plane.cuda().clone()
+    ops.rope_kv_write(q1, positions.cuda(), row_slot.cuda(), cos, sin, plane1, table.cuda(), H, KVH, hd, page, fault,
+                      write_kv=write_kv)
+    want = ops.paged_attention(q1, torch.empty(n, H * hd, dtype=dtype, device="cuda"), plane1, table.cuda(),
+                               positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault, Step())
+    # one launch
+    q2, plane2 = qkv.cuda().clone(), plane.cuda().clone()
+    assert ops.rotary_fusable(q2, Step(), H, KVH, hd)
+    before = ops.calls["attn_keys_rotary"]
+    got = ops.paged_attention(q2, torch.full((n, H * hd), 7.0, dtype=dtype, device="cuda"), plane2, table.cuda(),
+                              positions.cuda(), row_slot.cuda(), H, KVH, hd, page, window, fault, Step(),
+                              rotary=(cos, sin), write_kv=write_kv)
+    torch.cuda.synchronize()
+    assert ops.calls["attn_keys_rotary"] == before + 1 and int(fault[0]) == 0
+    assert torch.equal(q2, qkv.cuda()), "the projection's output is read only"
+    valid = row_slot >= 0
+    if write_kv:
+        assert torch.equal(plane2, plane1), "the pages differ from what rope_kv_write leaves"
+        assert torch.equal(got[valid.cuda()], want[valid.cuda()])
+    else:
+        assert torch.equal(plane2, plane.cuda()), "the plane was written with write_kv off"
+        torch.testing.assert_close(got[valid.cuda()].float(), want[valid.cuda()].float(), rtol=0, atol=0)
+    # and both equal the plain reference
+    ref_q, ref_plane = qkv.clone(), plane.clone()
+    ref.rope_kv_write(ref_q, positions, row_slot, cos.cpu(), sin.cpu(), ref_plane, table, H, KVH, hd, page,
+                      torch.zeros(4, dtype=torch.int32), write_kv=write_kv)
+    plain = ref.paged_attention(ref_q, torch.empty(n, H * hd, dtype=dtype), ref_plane, table, positions, row_slot, H,
+                                KVH, hd, page, window, torch.zeros(4, dtype=torch.int32))
+    torch.testing.assert_close(got.cpu().float()[valid], plain.float()[valid], rtol=2e-2, atol=2e-2)
 
 
 def test_attention_splits_plan():

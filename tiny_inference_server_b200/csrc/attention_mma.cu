@@ -37,11 +37,14 @@ constexpr int HD = TIS_HD;
 constexpr int KT = 64;               // keys per staged tile
 constexpr int RS = HD;               // shared-memory row stride (elements): rows lie dense, as in the cache
 constexpr int NTHREADS = 128;
-// stages of the copy pipeline: two.  The kernels are bound by the latency of a warp's own
-// instruction stream, so CTAs per SM (three at head size 128 with two stages) count for more
-// than a deeper pipeline; measured on a B200.
+// Stages of the copy pipeline: a launch parameter.  With many CTAs (prompt portions, large decode
+// batches) two stages leave room for three CTAs per SM at head size 128, which counts for more than a
+// deeper pipeline.  A decode step of few requests has fewer CTAs than the GPU has room for; what then
+// bounds the kernel is the bytes it has in flight, so each CTA takes as many stages as still let all
+// CTAs be resident at once (attn_launch).
 constexpr int STAGE_BYTES = 2 * KT * RS * 2;
-constexpr int STAGES = 2;
+constexpr int MAX_STAGES = 8;
+constexpr int MAX_CLUSTER = 16;      // key splits that merge inside one thread-block cluster (above 8: keys mode only)
 constexpr int NCH = HD / 8;          // 16-byte chunks of a cache row (permuted by the position: common.cuh)
 constexpr int KSTEPS = HD / 16;      // k16 steps of Q.K^T
 constexpr int DTILES = HD / 8;       // n8 tiles of the output
@@ -62,6 +65,10 @@ struct AttnParams {
     int cluster_merge;      // the splits of a (tile, kv head) are one thread-block cluster and merge through
                             // distributed shared memory: no scratch (2..8 splits); else scratch + merge kernel
     int* fault;
+    int stages;             // stages of the copy pipeline (2..MAX_STAGES)
+    // rotary encoding and cache write done by this kernel (decode rows; see FUSED below)
+    const float* rope_cos; const float* rope_sin;   // [positions][HD/2]
+    bf16* plane_w;          // the plane, writable: where the row's key and value go (null: another entry fills it)
 };
 
 // ---- mbarrier and bulk-copy (TMA) helpers --------------------------------------------
@@ -181,16 +188,26 @@ __device__ __forceinline__ void load_tile(bf16* stage, unsigned long long* bar, 
 // thousands of keys while its first see a few: three groups cut the longest CTA's path to a third,
 // and with one CTA of twelve warps per SM the heavy tiles, launched first, are followed by the
 // light ones as SMs fall free.
-template <int MODE, int NR, int NG>
+// FUSED (keys mode, tiles of exactly one row — a decode step): q of the row is still unrotated and its
+// key and value are not in the cache yet; they stand behind the queries in the row of `q`
+// ([H*HD queries | KVH*HD keys | KVH*HD values], the output of the q/kv projection).  The kernel rotates
+// the queries in registers as it loads them (half-split pairs, the whole head rotated: the launcher checks),
+// and the CTA whose key split holds the row's own position rotates the key, writes key and value into the
+// row's page for later steps, and puts them into its staged tile in place of what the copy brought.
+// This kernel is then the only one of the step that writes the plane, so with `plane_w` set it may
+// order its first key tiles before it waits for the kernel before it.
+template <int MODE, int NR, int NG, bool FUSED = false>
 __global__ void __launch_bounds__(NTHREADS * NG)
 attn_mma_kernel(const AttnParams p) {
     static_assert(NG == 1 || MODE == MODE_ROWS, "key groups are for row tiles");
+    static_assert(!FUSED || (MODE == MODE_KEYS && HD % 32 == 0), "the fused rotary path is for decode rows");
     constexpr int NT = MODE == MODE_ROWS ? 8 : 2;        // n8 key tiles a warp scores per staged tile
     constexpr int KB = MODE == MODE_ROWS ? 4 : 1;        // k16 key blocks a warp multiplies with V
     constexpr int STAGE_ELEMS = 2 * KT * RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int sh_first;
-    __shared__ __align__(8) unsigned long long bars_all[NG * STAGES];
+    __shared__ __align__(8) unsigned long long bars_all[NG * MAX_STAGES];
+    const int STAGES = p.stages;
 
     pdl_launch_dependents();         // tiles, slots, positions and block tables below are step metadata,
                                      // not written by the kernel before; pdl_wait() comes before q and the cache
@@ -208,7 +225,6 @@ attn_mma_kernel(const AttnParams p) {
 
     // first valid row of the tile (rows of a stage that lags the trunk start with padding)
     if (threadIdx.x == 0) {
-#pragma unroll
         for (int st = 0; st < NG * STAGES; ++st) mbar_init(&bars_all[st], NTHREADS);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -260,6 +276,30 @@ attn_mma_kernel(const AttnParams p) {
     const int ntiles = ntiles_all > grp ? (ntiles_all - grp + NG - 1) / NG : 0;     // tiles of this group
     // the group's j-th tile starts at position kt0 + (grp + j * NG) * KT
     int page = ntiles == 0 ? -1 : fetch_page(p, bt, kt0 + grp * KT, range_hi, tid);
+    // FUSED: does this CTA's split hold the row's own position?  Then it writes the row's key and value.
+    int own_pos = -1, own_page = -1;
+    if (FUSED && !empty && p.plane_w != nullptr) {
+        const int pos = p.positions[row0 + rows - 1];
+        if (pos >= range_lo && pos < range_hi) {
+            own_pos = pos;
+            own_page = bt[pos / p.page_size];
+            if (own_page < 0 || own_page >= p.num_pages) {
+                if (tid == 0) atomicExch(p.fault, 3);
+                own_page = -1;
+            }
+        }
+    }
+    const int ktg_early = kt0 + grp * KT;
+    const bool early = FUSED && p.plane_w != nullptr;      // nothing but this kernel writes the plane in this step
+    if (early && ntiles > 0) {
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < ntiles) {
+                const int page_next = fetch_page(p, bt, ktg_early + (st + 1) * NG * KT, range_hi, tid);
+                load_tile(stages + st * STAGE_ELEMS, &bars[st], p, page, kvh, ktg_early + st * NG * KT, range_lo, range_hi, tid);
+                page = page_next;
+            }
+        }
+    }
     pdl_wait();
 
     if (ntiles > 0) {
@@ -279,14 +319,35 @@ attn_mma_kernel(const AttnParams p) {
                 qa[kk][2 + i] = w1;
             }
         }
+        if (FUSED) {
+            // rotate the queries: column c of a head pairs with c + HD/2, which the same thread holds KSTEPS/2
+            // fragments further on; one position for the whole tile (it has one row)
+            const int pos = p.positions[row0 + rows - 1];
+            const float* cs = p.rope_cos + (size_t)pos * (HD / 2);
+            const float* sn = p.rope_sin + (size_t)pos * (HD / 2);
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {               // columns kk*16 + 2t (+1), and those + 8
+                    const float2 c2 = *reinterpret_cast<const float2*>(cs + kk * 16 + hf * 8 + 2 * t_lane);
+                    const float2 s2 = *reinterpret_cast<const float2*>(sn + kk * 16 + hf * 8 + 2 * t_lane);
+#pragma unroll
+                    for (int i = 0; i < NR; ++i) {
+                        const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk][2 * hf + i]));
+                        const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk + KSTEPS / 2][2 * hf + i]));
+                        qa[kk][2 * hf + i] = pack_bf16(x1.x * c2.x - x2.x * s2.x, x1.y * c2.y - x2.y * s2.y);
+                        qa[kk + KSTEPS / 2][2 * hf + i] = pack_bf16(x2.x * c2.x + x1.x * s2.x, x2.y * c2.y + x1.y * s2.y);
+                    }
+                }
+            }
+        }
         const int ktg = kt0 + grp * KT;        // the group's first tile; its tiles are NG * KT apart
         constexpr int KSTRIDE = NG * KT;
 
         // prologue: order STAGES-1 tiles; the page id a thread needs for the tile after is
         // fetched one tile ahead, so its latency is off the path
-#pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
-            if (st < ntiles) {
+            if (st < ntiles && !early) {
                 const int page_next = fetch_page(p, bt, ktg + (st + 1) * KSTRIDE, range_hi, tid);
                 load_tile(stages + st * STAGE_ELEMS, &bars[st], p, page, kvh, ktg + st * KSTRIDE, range_lo, range_hi, tid);
                 page = page_next;
@@ -310,6 +371,47 @@ attn_mma_kernel(const AttnParams p) {
                 }
             }
             mbar_wait(&bars[stg], (unsigned)((it / STAGES) & 1), p.fault);     // tile `it` has landed
+
+            if (FUSED && own_pos >= 0 && it == ntiles - 1) {
+                // the row's own key (rotated) and value: into the page, and into the staged tile in place of
+                // whatever the copy found at that position.  Warp 0: key chunk pairs; warp 1: value chunks.
+                const bf16* krow = p.q + (size_t)(row0 + rows - 1) * p.q_stride + (size_t)(p.H + kvh) * HD;
+                const bf16* vrow = krow + (size_t)p.KVH * HD;
+                const int in_tile = own_pos - kt;
+                bf16* k_sm = cur + in_tile * RS;
+                bf16* v_sm = cur + (KT + in_tile) * RS;
+                bf16* k_gl = own_page < 0 ? nullptr
+                    : p.plane_w + (((size_t)own_page * 2) * p.KVH + kvh) * (size_t)p.page_size * HD +
+                      (size_t)(own_pos % p.page_size) * HD;
+                bf16* v_gl = own_page < 0 ? nullptr : k_gl + (size_t)p.KVH * p.page_size * HD;
+                if (warp == 0 && lane < NCH / 2) {
+                    const int c = lane;
+                    float x1[8], x2[8], o1[8], o2[8];
+                    Vec16<bf16>::load(krow + c * 8, x1);
+                    Vec16<bf16>::load(krow + HD / 2 + c * 8, x2);
+                    const float* cs = p.rope_cos + (size_t)own_pos * (HD / 2) + c * 8;
+                    const float* sn = p.rope_sin + (size_t)own_pos * (HD / 2) + c * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
+                        o2[j] = x2[j] * cs[j] + x1[j] * sn[j];
+                    }
+                    const int ch1 = cache_chunk(c, own_pos, NCH) * 8, ch2 = cache_chunk(c + NCH / 2, own_pos, NCH) * 8;
+                    Vec16<bf16>::store(k_sm + ch1, o1);
+                    Vec16<bf16>::store(k_sm + ch2, o2);
+                    if (k_gl != nullptr) {
+                        Vec16<bf16>::store(k_gl + ch1, o1);
+                        Vec16<bf16>::store(k_gl + ch2, o2);
+                    }
+                } else if (warp == 1 && lane < NCH) {
+                    const int c = lane;
+                    const uint4 raw = *reinterpret_cast<const uint4*>(vrow + c * 8);
+                    const int ch = cache_chunk(c, own_pos, NCH) * 8;
+                    *reinterpret_cast<uint4*>(v_sm + ch) = raw;
+                    if (v_gl != nullptr) *reinterpret_cast<uint4*>(v_gl + ch) = raw;
+                }
+                __syncthreads();
+            }
 
             const bf16* ks = cur;
             const bf16* vs = cur + KT * RS;
@@ -644,8 +746,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     }
 }
 
-static size_t smem_bytes(int mode) {
-    size_t stage = (size_t)STAGES * STAGE_BYTES;
+static size_t smem_bytes(int mode, int stages = 2) {
+    size_t stage = (size_t)stages * STAGE_BYTES;
     size_t merge = mode == MODE_KEYS ? (size_t)(4 * 16 * (HD + 4) + 2 * 4 * 16) * sizeof(float)
                                      : (size_t)(64 * HD + 64) * sizeof(float);
     return stage > merge ? stage : merge;
@@ -663,10 +765,11 @@ TIS_API int tis_attn_resident_ctas(int mode, int half) {
         cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_ROWS, 2, 1>, NTHREADS, smem);
     } else if (half) {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        // (the keys-mode kernels may be launched with more stages than two: their limit stays at the most)
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 1, 1>, NTHREADS, smem);
     } else {
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<MODE_KEYS, 2, 1>, NTHREADS, smem);
     }
     cudaGetLastError();
@@ -682,12 +785,19 @@ TIS_API size_t tis_attn_scratch_floats(int n_rows, int H, int num_splits) {
 // max_tile_rows: the most rows any tile has (0: unknown); keys-mode tiles of at most 8 packed
 // rows take a kernel that keeps no state for the padding rows.
 // CTAs of a mode that one SM holds at a time: tis_attn_resident_ctas.
-TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
-                         const int* block_table, int bt_stride, int num_pages, const int* positions,
-                         const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
-                         int max_tile_rows, int n_rows, int H, int KVH, int page_size, int window, float scale,
-                         int keys_per_split, int num_splits, float* scratch, int* fault, cudaStream_t stream) {
+static int attn_launch(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
+                       const int* block_table, int bt_stride, int num_pages, const int* positions,
+                       const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                       int max_tile_rows, int n_rows, int H, int KVH, int page_size, int window, float scale,
+                       int keys_per_split, int num_splits, float* scratch, int* fault, cudaStream_t stream,
+                       const float* rope_cos, const float* rope_sin, int write_kv) {
     if (num_tiles <= 0) return TIS_OK;
+    const bool fused = rope_cos != nullptr;
+    if (fused && (mode != MODE_KEYS || max_tile_rows != 1 || HD % 32 != 0 || rope_sin == nullptr)) {
+        tis_set_error("attention: the rotary encoding is done inside the kernel only for tiles of one row (got %d) in "
+                      "keys mode and head sizes that are multiples of 32 (this library: %d)", max_tile_rows, HD);
+        return TIS_BAD_SIZE;
+    }
     const int G = KVH > 0 ? H / KVH : 0;
     const int mpack = mode == MODE_ROWS ? 64 : 16;
     if (KVH <= 0 || H % KVH) {
@@ -706,7 +816,7 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         tis_set_error("attention: %d kv heads or %d splits exceed the grid", KVH, num_splits);
         return TIS_BAD_SIZE;
     }
-    if (num_splits > 8 && scratch == nullptr) {
+    if (num_splits > (mode == MODE_KEYS ? MAX_CLUSTER : 8) && scratch == nullptr) {
         tis_set_error("attention: %d key splits need scratch memory", num_splits);
         return TIS_BAD_SIZE;
     }
@@ -719,18 +829,50 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
     p.keys_per_split = keys_per_split; p.num_splits = num_splits;
     p.part_o = scratch;
     p.part_lse = scratch ? scratch + (size_t)n_rows * H * num_splits * HD : nullptr;
-    p.cluster_merge = (num_splits > 1 && num_splits <= 8) ? 1 : 0;
+    p.cluster_merge = (num_splits > 1 && num_splits <= (mode == MODE_KEYS && scratch == nullptr ? MAX_CLUSTER : 8)) ? 1 : 0;
     p.fault = fault;
-    const size_t smem = smem_bytes(mode);
+    p.rope_cos = rope_cos; p.rope_sin = rope_sin;
+    p.plane_w = (fused && write_kv) ? (bf16*)plane : nullptr;
+    // stages: two; for decode tiles of a grid that leaves SMs empty anyway (fewer CTAs than SMs) as many as
+    // fit one CTA per SM and a split has tiles to fill.  Measured on a B200 inside the decode step of the
+    // 0.9B model: batch 1 (24 CTAs, six stages) 1.289 -> 1.235 ms a step; at batch 8 (192 CTAs) a third
+    // stage costs residency and the step gets slower (1.465 -> 1.486 ms), so there it stays at two.
+    int stages = 2;
+    if (mode == MODE_KEYS) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        const long long ctas = (long long)num_tiles * KVH * num_splits;
+        const int tiles_per_split = keys_per_split / KT;
+        for (int cand = 3; cand <= MAX_STAGES; ++cand) {
+            const size_t need = smem_bytes(MODE_KEYS, cand);
+            if (need > 220 * 1024 || cand - 1 > tiles_per_split) break;
+            if (ctas > (long long)sms) break;
+            stages = cand;
+        }
+    }
+    p.stages = stages;
+    const size_t smem = smem_bytes(mode, stages);
     dim3 grid(num_tiles, KVH, num_splits);
     static bool configured = false;          // once per process (and before any stream capture)
     if (!configured) {
         cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem_bytes(MODE_ROWS));
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem_bytes(MODE_KEYS));
-        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem_bytes(MODE_KEYS));
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+#if TIS_HD % 32 == 0
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+#endif
+        cudaGetLastError();
         if (3 * smem_bytes(MODE_ROWS) <= 227 * 1024)
             cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)(3 * smem_bytes(MODE_ROWS)));
@@ -767,6 +909,10 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
             cfg.dynamicSmemBytes = 3 * smem_bytes(MODE_ROWS);
             cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 3>, p);
         } else if (mode == MODE_ROWS) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 1>, p);
+#if TIS_HD % 32 == 0
+        else if (fused && G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1, 1, true>, p);
+        else if (fused) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2, 1, true>, p);
+#endif
         else if (max_tile_rows > 0 && max_tile_rows * G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1, 1>, p);
         else cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2, 1>, p);
     }
@@ -779,6 +925,39 @@ TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int o
         st = tis_check_launch("attn_merge");
     }
     return st;
+}
+
+TIS_API int tis_attn_mma(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
+                         const int* block_table, int bt_stride, int num_pages, const int* positions,
+                         const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                         int max_tile_rows, int n_rows, int H, int KVH, int page_size, int window, float scale,
+                         int keys_per_split, int num_splits, float* scratch, int* fault, cudaStream_t stream) {
+    return attn_launch(mode, q, q_stride, out, out_stride, plane, block_table, bt_stride, num_pages, positions, row_slot,
+                       tile_row0, tile_rows, num_tiles, max_tile_rows, n_rows, H, KVH, page_size, window, scale,
+                       keys_per_split, num_splits, scratch, fault, stream, nullptr, nullptr, 0);
+}
+
+// Decode rows (tiles of one row, keys mode) whose rotary encoding and cache write this kernel does itself:
+// `qkv` rows are [H*HD queries | KVH*HD keys | KVH*HD values] as the projection left them (only the queries
+// when write_kv is 0: another entry of the schedule fills the plane); cos/sin [positions][HD/2] float32,
+// half-split pairs, the whole head rotated.  At most eight key splits (they merge inside a cluster).
+TIS_API int tis_attn_decode_rope(const void* qkv, int q_stride, void* out, int out_stride, void* plane,
+                                 const int* block_table, int bt_stride, int num_pages, const int* positions,
+                                 const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
+                                 int n_rows, int H, int KVH, int page_size, int window, float scale,
+                                 int keys_per_split, int num_splits, const float* rope_cos, const float* rope_sin,
+                                 int write_kv, int* fault, cudaStream_t stream) {
+    if (rope_cos == nullptr || rope_sin == nullptr) {
+        tis_set_error("attn_decode_rope: no rotary tables");
+        return TIS_BAD_SIZE;
+    }
+    if (num_splits > MAX_CLUSTER) {
+        tis_set_error("attn_decode_rope: %d key splits; at most 16", num_splits);
+        return TIS_BAD_SIZE;
+    }
+    return attn_launch(MODE_KEYS, qkv, q_stride, out, out_stride, plane, block_table, bt_stride, num_pages, positions,
+                       row_slot, tile_row0, tile_rows, num_tiles, 1, n_rows, H, KVH, page_size, window, scale,
+                       keys_per_split, num_splits, nullptr, fault, stream, rope_cos, rope_sin, write_kv);
 }
 
 

@@ -24,6 +24,11 @@ struct Blas {
     SetWorkspaceFn set_workspace = nullptr;
     GemmExFn gemm_ex = nullptr;
     bool ok = false;
+    int device = -1;                 // the device that was current when the handle was made
+    void* workspace = nullptr;       // given once by the caller; set again after every change of stream
+    size_t workspace_bytes = 0;
+    cudaStream_t stream = nullptr;
+    bool stream_set = false;
 };
 
 Blas& blas() {
@@ -40,6 +45,7 @@ Blas& blas() {
         b.gemm_ex = reinterpret_cast<GemmExFn>(dlsym(lib, "cublasGemmEx"));
         if (!create || !b.set_stream || !b.set_workspace || !b.gemm_ex) return;
         if (create(&b.handle) != CUBLAS_STATUS_SUCCESS) return;
+        cudaGetDevice(&b.device);
         b.ok = true;
     });
     return b;
@@ -49,10 +55,13 @@ Blas& blas() {
 
 // 1 if the library was found and a handle made.  `workspace` (device memory that the caller keeps
 // alive) is what the library uses for split-K partial sums: with a fixed workspace its calls can be
-// captured into CUDA graphs.
+// captured into CUDA graphs.  cublasSetStream puts the handle's workspace back to the library's own
+// pool, so the workspace is remembered here and set again whenever the stream changes.
 TIS_API int tis_gemm_library_init(void* workspace, size_t bytes) {
     Blas& b = blas();
     if (!b.ok) return 0;
+    b.workspace = workspace;
+    b.workspace_bytes = bytes;
     if (workspace && bytes && b.set_workspace(b.handle, workspace, bytes) != CUBLAS_STATUS_SUCCESS) return 0;
     return 1;
 }
@@ -66,9 +75,24 @@ TIS_API int tis_gemm_library(const void* x, int ldx, const void* w, int ldw, voi
         tis_set_error("gemm_library: cuBLAS was not found in the process");
         return TIS_CUDA_ERROR;
     }
-    if (b.set_stream(b.handle, stream) != CUBLAS_STATUS_SUCCESS) {
-        tis_set_error("gemm_library: cublasSetStream failed");
+    int dev = -1;
+    cudaGetDevice(&dev);
+    if (dev != b.device) {
+        tis_set_error("gemm_library: the handle was made on device %d, device %d is current", b.device, dev);
         return TIS_CUDA_ERROR;
+    }
+    if (!b.stream_set || b.stream != stream) {
+        if (b.set_stream(b.handle, stream) != CUBLAS_STATUS_SUCCESS) {
+            tis_set_error("gemm_library: cublasSetStream failed");
+            return TIS_CUDA_ERROR;
+        }
+        if (b.workspace && b.workspace_bytes &&
+            b.set_workspace(b.handle, b.workspace, b.workspace_bytes) != CUBLAS_STATUS_SUCCESS) {
+            tis_set_error("gemm_library: cublasSetWorkspace failed");
+            return TIS_CUDA_ERROR;
+        }
+        b.stream = stream;
+        b.stream_set = true;
     }
     const float alpha = 1.f, beta = 0.f;
     const cublasStatus_t st = b.gemm_ex(b.handle, CUBLAS_OP_N, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, ldw, x,

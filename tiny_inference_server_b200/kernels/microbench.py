@@ -45,6 +45,8 @@ def _graph_time(fn, n=40):
 class _Step:
     """The little of a StepContext that the attention operation reads."""
 
+    decode_only = True
+
     def __init__(self, tiles, max_position):
         self._tiles = tiles
         self.max_position = max_position
@@ -69,9 +71,13 @@ def attention(args):
     out = torch.empty(B, H * hd, device=dev, dtype=torch.bfloat16)
     fault = torch.zeros(4, dtype=torch.int32, device=dev)
     step = _Step(infer_tiles(positions, slots, H // KVH), ctx - 1)
+    rotary = None
+    if args.rotary:          # as in a decode step: the kernel rotates q and k and writes the cache itself
+        rotary = (torch.ones(ctx, hd // 2, device=dev), torch.zeros(ctx, hd // 2, device=dev))
 
     def run(i):
-        ops.paged_attention(qkv, out, planes[i % n_planes], table, positions, slots, H, KVH, hd, page, None, fault, step)
+        ops.paged_attention(qkv, out, planes[i % n_planes], table, positions, slots, H, KVH, hd, page, None, fault, step,
+                            rotary=rotary)
 
     kv_bytes = B * ctx * 2 * KVH * hd * 2
     if args.no_timing:
@@ -187,8 +193,14 @@ def gemm(args):
             continue
         a, b = _graph_time(mine), _graph_time(lib)
         mb = K * N * 2 / 1e6
+        extra = ""
+        if n <= 64:
+            ops.STREAM_GEMM = not ops.STREAM_GEMM
+            c = _graph_time(mine)
+            ops.STREAM_GEMM = not ops.STREAM_GEMM
+            extra = f"   {'ring' if ops.STREAM_GEMM else 'TMA-fed'} kernel {c:7.2f} us"
         print(f"gemm {name:15s} rows {n:4d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s, "
-              f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us")
+              f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us{extra}")
 
 
 def prefill(args):
@@ -237,6 +249,7 @@ def main(argv=None):
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--reps", type=int, default=4)
     ap.add_argument("--no-timing", action="store_true")
+    ap.add_argument("--rotary", action="store_true", help="attention: rotary encoding and cache write inside the kernel")
     args = ap.parse_args(argv)
     ops.library()
     if args.what in ("attention", "all"):

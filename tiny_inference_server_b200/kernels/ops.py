@@ -125,10 +125,55 @@ def _ksplit(n_cols: int, k: int) -> int:
     return ks
 
 
+#: The weight-streaming product comes in two kernels: weights copied by the threads into a ring of four
+#: stages (csrc/gemm_skinny.cu), and weights ordered as TMA boxes, a CTA's whole share of K at once
+#: (csrc/gemm_stream.cu).  Measured alone on a B200 at the 0.9B shapes (us at 1 / 8 / 16 rows; library beside):
+#: qkv 4.1 / 4.4 / 4.6 ring, 5.2 / 5.8 / 6.3 boxes (4.8 / 4.8 / 4.5); gate/up with gating 7.6 / 8.3 / 9.1 ring,
+#: 10.9 / 11.9 / 13.5 boxes; down (K 4096, 512 rows of K a CTA) 7.4 / 7.8 / 8.2 ring, 6.2 / 6.5 / 6.9 boxes
+#: (7.4 / 7.4 / 7.4).  A box row is 128 bytes, one request of the TMA engine each: with many CTAs per SM the
+#: engine is the bottleneck, while a long share of K gains from having all of it in flight from the start.  So the
+#: boxes take products whose share of K per CTA is at least STREAM_MIN_KC rows, up to STREAM_MAX_ROWS rows of x.
+STREAM_GEMM = os.environ.get("TIS_STREAM_GEMM", "1") != "0"
+STREAM_MIN_KC = int(os.environ.get("TIS_STREAM_MIN_KC", "512"))
+STREAM_MAX_ROWS = int(os.environ.get("TIS_STREAM_MAX_ROWS", "16"))
+
+
+def _stream_pays(n: int, k: int, cols: int) -> bool:
+    return STREAM_GEMM and n <= STREAM_MAX_ROWS and -(-k // _ksplit(cols, k)) >= STREAM_MIN_KC
+
+
+def _stream_fits(n: int, k: int, ksplit: int) -> bool:
+    """Whether a CTA's share of the rows (all of its share of K, in shared memory for the whole loop) and
+    a round of weight boxes fit the TMA-fed kernel's shared memory."""
+    kc = -(-(-(-k // ksplit)) // 64) * 64
+    rows = 16 if n <= 16 else (32 if n <= 32 else 64)
+    return min(kc // 64, 8) * 8192 + rows * (kc + 8) * 2 + 1024 <= 200 * 1024
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                ksplit: Optional[int] = None) -> torch.Tensor:
+    """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by the TMA-fed weight-streaming kernel; with ``swiglu``
+    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    lib = library()
+    n, k = a.shape
+    cols = w.shape[1]
+    if out is None:
+        out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    calls["gemm_stream"] += 1
+    _check(lib.tis_gemm_stream(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                               ksplit or _ksplit(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()),
+                               _stream()), lib)
+    return out
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
                 ksplit: Optional[int] = None) -> torch.Tensor:
-    """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by the weight-streaming kernel; with ``swiglu``
+    """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by a weight-streaming kernel; with ``swiglu``
     the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    if (STREAM_GEMM and STREAM_MIN_KC <= -(-a.shape[1] // (ksplit or _ksplit(w.shape[1], a.shape[1])))
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and _stream_fits(a.shape[0], a.shape[1], ksplit or _ksplit(w.shape[1], a.shape[1]))):
+        return gemm_stream(a, w, out, swiglu, ksplit)
     lib = library()
     n, k = a.shape
     cols = w.shape[1]
@@ -224,7 +269,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -
     everything else to the library product."""
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
-    if _skinny_ok(a, w):
+    if _skinny_ok(a, w) or (_skinny_ok(a, w, STREAM_MAX_ROWS) and _stream_pays(a.shape[0], a.shape[1], w.shape[1])
+                            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         return gemm_skinny(a, w, out)
     if _tc_ok(a, w, TC_PLAIN_MIN_ROWS) and (out is None or (out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)):
         return gemm_tc(a, w, out)
@@ -336,6 +382,11 @@ ATTN_RESIDENT_CTAS = 148 * 2
 #: cost of starting and finishing a CTA, and of merging one more split, in units of one 64-key tile
 ATTN_CTA_OVERHEAD_TILES = 8.0
 ATTN_MERGE_PER_SPLIT_TILES = 0.1
+#: most key splits of a decode tile (one cluster).  The kernel takes clusters of 16 (a size the device
+#: allows on request), and alone it gains from them at batch 1 (12.7 -> 10.3 us at context 4096), but inside
+#: the decode step nothing is left of that (1.235 -> 1.247 ms a step) and at batch 8 they cost (17.6 -> 28.4 us):
+#: the planner stays at the portable 8.  TIS_ATTN_MAX_SPLITS overrides.
+ATTN_MAX_SPLITS_KEYS = int(os.environ.get("TIS_ATTN_MAX_SPLITS", "8"))
 
 
 def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, resident: int = ATTN_RESIDENT_CTAS,
@@ -351,7 +402,9 @@ def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, res
     than the longest CTA; plus the cost of merging."""
     total_tiles = max(1, (max_kv + 63) // 64)
     lo_tiles = total_tiles if min_kv is None else max(1, (min(min_kv, max_kv) + 63) // 64)
-    limit = min(total_tiles, 8)        # the splits are one thread-block cluster (at most 8 CTAs)
+    # the splits are one thread-block cluster: at most 8 CTAs, or 16 for decode tiles (a cluster size
+    # that the device allows on request)
+    limit = min(total_tiles, ATTN_MAX_SPLITS_KEYS if mode_keys else 8)
     if not mode_keys and lo_tiles < 0.75 * total_tiles:
         # a prompt from its start: tiles see very different numbers of keys.  The CTAs of a cluster
         # leave together, so a split without keys would hold its place until the longest one is
@@ -388,19 +441,39 @@ def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, res
     return per, max(1, (max_kv + per - 1) // per)
 
 
+#: decode steps: the attention kernel rotates queries and keys and writes the cache itself
+#: (TIS_ATTN_ROTARY=0: the rope_kv_write kernel does, in a launch of its own, as for every other step)
+ATTN_ROTARY = os.environ.get("TIS_ATTN_ROTARY", "1") != "0"
+
+
+def rotary_fusable(q: torch.Tensor, step, num_heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether ``paged_attention`` can take rows whose queries are not rotated yet and whose keys and
+    values are not in the cache yet (``rotary=``): a decode step (one row per request) in bfloat16, a head
+    size the kernel rotates in registers, at most 16 query heads per kv head."""
+    return (ATTN_ROTARY and q.dtype == torch.bfloat16 and step is not None and getattr(step, "decode_only", False)
+            and head_dim % 32 == 0 and kv_heads > 0 and num_heads % kv_heads == 0 and num_heads // kv_heads <= 16)
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor,
                     positions: torch.Tensor, row_slot: torch.Tensor, num_heads: int, kv_heads: int,
                     head_dim: int, page_size: int, window: Optional[int], fault: torch.Tensor,
-                    step=None) -> torch.Tensor:
+                    step=None, rotary=None, write_kv: bool = True) -> torch.Tensor:
     """Causal attention of the step's rows over the cache.  ``q`` is (n, >= H*hd) with the
     queries first in each row (row stride free); ``out`` is (n, H*hd).  The row at position
     p of slot s sees keys max(0, p-window+1)..p of ``plane`` through ``block_table[s]``.
 
     float32: CUDA-core kernel, everything in 32-bit.  bfloat16: tensor-core kernels over
-    tiles of rows (``kernels.attention_plan``), keys of long contexts split over CTAs."""
+    tiles of rows (``kernels.attention_plan``), keys of long contexts split over CTAs.
+
+    ``rotary=(cos, sin)`` (only where ``rotary_fusable``): the rows of ``q`` are the projection's output
+    as it is, [queries | keys | values]; the kernel rotates queries and keys itself (half-split pairs,
+    tables [positions, hd/2] float32) and, with ``write_kv``, writes the rows' keys and values into
+    their pages — what ``rope_kv_write`` does in a launch of its own everywhere else."""
     lib = library()
     n = q.shape[0]
     scale = 1.0 / math.sqrt(head_dim)
+    if rotary is not None and not rotary_fusable(q, step, num_heads, kv_heads, head_dim):
+        raise KernelError("paged_attention: rotary encoding inside the kernel is for decode steps in bfloat16")
     if q.dtype == torch.float32:
         _check(lib.tis_paged_attention_simt(
             _dt(q), _p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table), block_table.stride(0),
@@ -442,6 +515,23 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
             rows_tiles = (None, None, 0)
         else:
             rows_tiles = (tiles.rows[0][skip:], tiles.rows[1][skip:], tiles.rows[2] - skip)
+    if rotary is not None:
+        row0, rows, count = tiles.keys
+        if tiles.rows[2] or wide_count or tiles.keys_max_rows != 1:
+            raise KernelError("paged_attention: rotary encoding inside the kernel needs tiles of one row")
+        half = int(g <= 8)
+        resident = alib.resident.get((1, half))
+        if resident is None:
+            resident = alib.resident[(1, half)] = alib.tis_attn_resident_ctas(1, half)
+        per, splits = plan_splits(count, kv_heads, max_kv, True, resident, None)
+        calls["attn_keys_rotary"] += 1
+        cos, sin = rotary
+        _check(alib.tis_attn_decode_rope(_p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
+                                         block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
+                                         _p(rows), count, n, num_heads, kv_heads, page_size, int(window or 0),
+                                         _f(scale), per, splits, _p(cos), _p(sin), int(bool(write_kv)), _p(fault),
+                                         _stream()), alib)
+        return out
     for mode, (row0, rows, count) in ((1, tiles.keys), (0, rows_tiles)):
         if count == 0:
             continue

@@ -85,10 +85,17 @@ class GqaAttention(Mixer):
         table = step.block_tables[g]
         page_size = step.page_sizes[g]
         qkv = ops.gemm(x, self.w_qkv if binding.kv_write else self.w_q)
+        out = torch.empty((n, hq), dtype=qkv.dtype, device=qkv.device)
+        # a decode step: the attention kernel applies a rotary encoding and writes the cache itself
+        rotary = self.position.fused_rotary()
+        if rotary is not None and ops.rotary_fusable(qkv, step, self.num_heads, self.kv_heads, self.head_dim):
+            ops.paged_attention(qkv, out, binding.kv_plane, table, step.positions, step.row_slot, self.num_heads,
+                                self.kv_heads, self.head_dim, page_size, self.window, step.fault, step,
+                                rotary=rotary, write_kv=binding.kv_write)
+            return ops.gemm(out, self.w_o)
         self.position.encode_and_store(qkv, step, num_heads=self.num_heads, kv_heads=self.kv_heads,
                                        head_dim=self.head_dim, plane=binding.kv_plane if binding.kv_write else None,
                                        block_table=table, page_size=page_size)
-        out = torch.empty((n, hq), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, out, binding.kv_plane, table, step.positions, step.row_slot, self.num_heads,
                             self.kv_heads, self.head_dim, page_size, self.window, step.fault, step)
         return ops.gemm(out, self.w_o)

@@ -193,6 +193,12 @@ class PositionEncoding(Part):
                          plane: Optional[torch.Tensor], block_table: Optional[torch.Tensor], page_size: int) -> None:
         raise NotImplementedError
 
+    def fused_rotary(self):
+        """(cos, sin) tables ``[positions, head_dim / 2]`` float32 if this encoding is a rotation of
+        the whole head with pairs (i, i + head_dim/2) — what the decode attention kernel can apply
+        itself, together with the cache write, in place of ``encode_and_store`` — else None."""
+        return None
+
 
 class Mixer(Part):
     """Mixes information across the positions of a request.

@@ -55,6 +55,12 @@ class RotaryHalf(PositionEncoding):
                           write_kv=plane is not None)
 
 
+    def fused_rotary(self):
+        if self.interleaved or self.rotary_dim != self.head_dim:
+            return None
+        return self.cos, self.sin
+
+
 class RotaryInterleaved(RotaryHalf):
     """Pairs (2i, 2i+1) instead of (i, i + rot/2); the same angles."""
 
