@@ -28,6 +28,7 @@
 // to scratch memory and `attn_merge_kernel` merges them.
 #include "common.cuh"
 #include <cooperative_groups.h>
+#include <cstdlib>
 
 #ifndef TIS_HD
 #error "compile with -DTIS_HD=<head size>"
@@ -719,6 +720,399 @@ attn_mma_kernel(const AttnParams p) {
     }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Decode tiles with a warp of their own for the copies.
+//
+// The kernel above runs its four warps in lock step: every thread helps to order the next tile and
+// a CTA-wide barrier separates the tiles, so each tile costs the slowest warp plus the barrier, and a
+// tile's copy is only ordered when the tile before it is done.  At decode (a handful of packed rows,
+// a CTA per key split) that chain of instructions and barriers is what bounds the kernel, not the
+// bytes.  Here a fifth warp does nothing but order tiles, as far ahead as there are stages; the four
+// consumer warps (warp w: keys 16w..16w+15 of every staged tile, as above) never meet each other
+// inside the loop.  Hand-offs are mbarriers: full[stage] (the producer's 32 lanes arrive, the
+// segment leaders with the bytes they ordered) and empty[stage] (one arrival per consumer warp).
+// Same tiles, same split of the keys, same merge of the splits inside the cluster as MODE_KEYS
+// above; with FUSED the same rotary encoding and cache write.  Pages of at least 4 positions
+// (a tile then has at most 16 page segments: two lanes each).
+// ----------------------------------------------------------------------------------------------
+constexpr int DEC_THREADS = NTHREADS + 32;
+
+__device__ __forceinline__ int fetch_page_lane(const AttnParams& p, const int* bt, int kt, int hi, int lane) {
+    return fetch_page(p, bt, kt, hi, lane);
+}
+
+// load_tile for one warp: lanes 2s / 2s+1 lead the keys / values of page segment s; rows of positions
+// outside [lo, hi) are zero-filled by the lanes in turn; every lane arrives on the stage's barrier.
+__device__ __forceinline__ void load_tile_warp(bf16* stage, unsigned long long* bar, const AttnParams& p, int page,
+                                               int kvh, int kt, int lo, int hi, int lane) {
+    if (kt < lo || kt + KT > hi) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = lane; i < 2 * KT; i += 32) {
+            const int which = i & 1, row = i >> 1;
+            const int j = kt + row;
+            if (j < lo || j >= hi) {
+                bf16* dst = stage + (which * KT + row) * RS;
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = z;
+            }
+        }
+    }
+    const int which = lane & 1;
+    const int lp = kt / p.page_size + (lane >> 1);
+    const long long pfirst = (long long)lp * p.page_size;
+    int j0 = (int)(pfirst > kt ? pfirst : kt);
+    if (j0 < lo) j0 = lo;
+    long long j1 = pfirst + p.page_size;
+    if (j1 > kt + KT) j1 = kt + KT;
+    if (j1 > hi) j1 = hi;
+    const int nrows = (int)(j1 - j0);
+    if (pfirst < kt + KT && nrows > 0) {
+        if (page >= 0 && page < p.num_pages) {
+            const bf16* src = p.plane + (((size_t)page * 2 + which) * p.KVH + kvh) * (size_t)p.page_size * HD +
+                              (size_t)(j0 - pfirst) * HD;
+            const int bytes = nrows * HD * 2;
+            mbar_arrive_expect_tx(bar, bytes);
+            bulk_copy_g2s(stage + (which * KT + (j0 - kt)) * RS, src, bytes, bar);
+            return;
+        }
+        atomicExch(p.fault, 3);
+    }
+    mbar_arrive(bar);
+}
+
+template <int NR, bool FUSED>
+__global__ void __launch_bounds__(DEC_THREADS, HD <= 128 ? 2 : 1)
+attn_decode_kernel(const AttnParams p) {
+    static_assert(!FUSED || HD % 32 == 0, "the fused rotary path rotates pairs of k16 fragments");
+    constexpr int NT = 2;                                // n8 key tiles a warp scores per staged tile
+    constexpr int STAGE_ELEMS = 2 * KT * RS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int sh_first;
+    __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES];
+    const int STAGES = p.stages;
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool producer = warp == NTHREADS / 32;
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw);
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int g_lane = lane >> 2, t_lane = lane & 3;
+    const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+    const int G = p.G;
+
+    if (tid == 0) {
+        for (int st = 0; st < STAGES; ++st) { mbar_init(&full[st], 32); mbar_init(&empty[st], NTHREADS / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
+        const unsigned b0 = __ballot_sync(0xffffffffu, v0);
+        if (lane == 0) sh_first = b0 ? __ffs(b0) - 1 : -1;       // a tile of this kind has at most 16 rows
+    }
+    __syncthreads();
+    const int first = sh_first;
+
+    const int mbase = g_lane;
+    int r_idx[2], head[2], hi_row[2], lo_row[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = mbase + 8 * i;
+        const int r = m / G, g = m - r * G;
+        valid[i] = i < NR && r < rows && first >= 0 && r >= first;
+        r_idx[i] = row0 + (valid[i] ? r : 0);
+        head[i] = kvh * G + g;
+        const int pos = valid[i] ? p.positions[r_idx[i]] : 0;
+        hi_row[i] = valid[i] ? pos + 1 : 0;
+        lo_row[i] = (valid[i] && p.window > 0 && hi_row[i] > p.window) ? hi_row[i] - p.window : 0;
+    }
+    int range_lo = 0, range_hi = 0, slot = -1;
+    if (first >= 0) {
+        slot = p.row_slot[row0 + rows - 1];
+        const int pos_first = p.positions[row0 + first], pos_last = p.positions[row0 + rows - 1];
+        range_hi = pos_last + 1;
+        range_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
+        range_lo = max(range_lo, split * p.keys_per_split);
+        range_hi = min(range_hi, (split + 1) * p.keys_per_split);
+    }
+    const bool none = first < 0 || range_lo >= range_hi;
+    const int* bt = p.block_table + (size_t)(slot >= 0 ? slot : 0) * p.bt_stride;
+    const int kt0 = (range_lo / KT) * KT;
+    const int ntiles = none ? 0 : (range_hi - kt0 + KT - 1) / KT;
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (producer) {
+        // with FUSED and a plane of its own this kernel is the only one of the step that writes the plane:
+        // no tile depends on the kernel before, and the copies start at once
+        if (!(FUSED && p.plane_w != nullptr)) pdl_wait();
+        int page = ntiles == 0 ? -1 : fetch_page_lane(p, bt, kt0, range_hi, lane);
+        for (int it = 0; it < ntiles; ++it) {
+            const int stg = it % STAGES;
+            const int kt = kt0 + it * KT;
+            const int page_next = fetch_page_lane(p, bt, kt + KT, range_hi, lane);
+            if (it >= STAGES) {
+                mbar_wait(&empty[stg], (unsigned)(((it / STAGES) - 1) & 1), p.fault);   // every consumer warp is done with it
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
+            load_tile_warp(stages + stg * STAGE_ELEMS, &full[stg], p, page, kvh, kt, range_lo, range_hi, lane);
+            page = page_next;
+        }
+    } else {
+        // FUSED: does this CTA's split hold the row's own position?  Then it writes the row's key and value.
+        int own_pos = -1, own_page = -1;
+        if (FUSED && !none && p.plane_w != nullptr) {
+            const int pos = p.positions[row0 + rows - 1];
+            if (pos >= range_lo && pos < range_hi) {
+                own_pos = pos;
+                own_page = bt[pos / p.page_size];
+                if (own_page < 0 || own_page >= p.num_pages) {
+                    if (tid == 0) atomicExch(p.fault, 3);
+                    own_page = -1;
+                }
+            }
+        }
+        pdl_wait();
+        if (ntiles > 0) {
+            unsigned qa[KSTEPS][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const bf16* qrow = p.q + (size_t)r_idx[i] * p.q_stride + (size_t)head[i] * HD;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    unsigned w0 = 0u, w1 = 0u;
+                    if (valid[i]) {
+                        w0 = *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 2 * t_lane);
+                        w1 = *reinterpret_cast<const unsigned*>(qrow + kk * 16 + 8 + 2 * t_lane);
+                    }
+                    qa[kk][i] = w0;
+                    qa[kk][2 + i] = w1;
+                }
+            }
+            if (FUSED) {
+                const int pos = p.positions[row0 + rows - 1];
+                const float* cs = p.rope_cos + (size_t)pos * (HD / 2);
+                const float* sn = p.rope_sin + (size_t)pos * (HD / 2);
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const float2 c2 = *reinterpret_cast<const float2*>(cs + kk * 16 + hf * 8 + 2 * t_lane);
+                        const float2 s2 = *reinterpret_cast<const float2*>(sn + kk * 16 + hf * 8 + 2 * t_lane);
+#pragma unroll
+                        for (int i = 0; i < NR; ++i) {
+                            const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk][2 * hf + i]));
+                            const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk + KSTEPS / 2][2 * hf + i]));
+                            qa[kk][2 * hf + i] = pack_bf16(x1.x * c2.x - x2.x * s2.x, x1.y * c2.y - x2.y * s2.y);
+                            qa[kk + KSTEPS / 2][2 * hf + i] = pack_bf16(x2.x * c2.x + x1.x * s2.x, x2.y * c2.y + x1.y * s2.y);
+                        }
+                    }
+                }
+            }
+            for (int it = 0; it < ntiles; ++it) {
+                const int kt = kt0 + it * KT;
+                const int stg = it % STAGES;
+                bf16* cur = stages + stg * STAGE_ELEMS;
+                mbar_wait(&full[stg], (unsigned)((it / STAGES) & 1), p.fault);         // tile `it` has landed
+
+                if (FUSED && own_pos >= 0 && it == ntiles - 1) {
+                    const bf16* krow = p.q + (size_t)(row0 + rows - 1) * p.q_stride + (size_t)(p.H + kvh) * HD;
+                    const bf16* vrow = krow + (size_t)p.KVH * HD;
+                    const int in_tile = own_pos - kt;
+                    bf16* k_sm = cur + in_tile * RS;
+                    bf16* v_sm = cur + (KT + in_tile) * RS;
+                    bf16* k_gl = own_page < 0 ? nullptr
+                        : p.plane_w + (((size_t)own_page * 2) * p.KVH + kvh) * (size_t)p.page_size * HD +
+                          (size_t)(own_pos % p.page_size) * HD;
+                    bf16* v_gl = own_page < 0 ? nullptr : k_gl + (size_t)p.KVH * p.page_size * HD;
+                    if (warp == 0 && lane < NCH / 2) {
+                        const int c = lane;
+                        float x1[8], x2[8], o1[8], o2[8];
+                        Vec16<bf16>::load(krow + c * 8, x1);
+                        Vec16<bf16>::load(krow + HD / 2 + c * 8, x2);
+                        const float* cs = p.rope_cos + (size_t)own_pos * (HD / 2) + c * 8;
+                        const float* sn = p.rope_sin + (size_t)own_pos * (HD / 2) + c * 8;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
+                            o2[j] = x2[j] * cs[j] + x1[j] * sn[j];
+                        }
+                        const int ch1 = cache_chunk(c, own_pos, NCH) * 8, ch2 = cache_chunk(c + NCH / 2, own_pos, NCH) * 8;
+                        Vec16<bf16>::store(k_sm + ch1, o1);
+                        Vec16<bf16>::store(k_sm + ch2, o2);
+                        if (k_gl != nullptr) {
+                            Vec16<bf16>::store(k_gl + ch1, o1);
+                            Vec16<bf16>::store(k_gl + ch2, o2);
+                        }
+                    } else if (warp == 1 && lane < NCH) {
+                        const int c = lane;
+                        const uint4 raw = *reinterpret_cast<const uint4*>(vrow + c * 8);
+                        const int ch = cache_chunk(c, own_pos, NCH) * 8;
+                        *reinterpret_cast<uint4*>(v_sm + ch) = raw;
+                        if (v_gl != nullptr) *reinterpret_cast<uint4*>(v_gl + ch) = raw;
+                    }
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");       // the consumer warps only
+                }
+
+                const bf16* ks = cur;
+                const bf16* vs = cur + KT * RS;
+                const int kofs = warp * 16;
+                float s[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    unsigned b[4];
+                    const int key = kofs + ((lane >> 4) << 3) + (lane & 7);
+                    const int chunk = cache_chunk(2 * kk + ((lane >> 3) & 1), kt + key, NCH);
+                    ldmatrix_x4(b, ks + key * RS + chunk * 8);
+                    mma_bf16(s[0], qa[kk], b[0], b[1]);
+                    mma_bf16(s[1], qa[kk], b[2], b[3]);
+                }
+                float mx[2] = {-INFINITY, -INFINITY};
+                const int t_lo = kt + kofs, t_hi = kt + kofs + NT * 8;
+                const bool interior = t_lo >= range_lo && t_hi <= range_hi && t_lo >= lo_row[0] && t_hi <= hi_row[0] &&
+                                      (NR == 1 || (t_lo >= lo_row[1] && t_hi <= hi_row[1]));
+                if (interior) {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int e = 0; e < 2 * NR; ++e) {
+                            const float v = s[j][e] * p.scale_log2;
+                            s[j][e] = v;
+                            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                        }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int e = 0; e < 2 * NR; ++e) {
+                            const int i = e >> 1;
+                            const int kidx = kt + kofs + j * 8 + 2 * t_lane + (e & 1);
+                            const bool ok = kidx >= lo_row[i] && kidx < hi_row[i] && kidx >= range_lo && kidx < range_hi;
+                            const float v = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+                            s[j][e] = v;
+                            mx[i] = fmaxf(mx[i], v);
+                        }
+                }
+                float alpha[2] = {1.f, 1.f}, m_safe[2] = {0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    const float m_new = fmaxf(m_run[i], mx[i]);
+                    m_safe[i] = (m_new == -INFINITY) ? 0.f : m_new;
+                    alpha[i] = (m_run[i] == -INFINITY) ? 0.f : fast_exp2(m_run[i] - m_safe[i]);
+                    m_run[i] = m_new;
+                }
+                float psum[2] = {0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 2 * NR; ++e) {
+                        const int i = e >> 1;
+                        const float pv = fast_exp2(s[j][e] - m_safe[i]);
+                        s[j][e] = pv;
+                        psum[i] += pv;
+                    }
+                    if (NR == 1) { s[j][2] = 0.f; s[j][3] = 0.f; }
+                }
+#pragma unroll
+                for (int i = 0; i < NR; ++i) l_run[i] = l_run[i] * alpha[i] + psum[i];
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                    for (int d = 0; d < DTILES; ++d) {
+                        o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+                        if (NR == 2) { o[d][2] *= alpha[1]; o[d][3] *= alpha[1]; }
+                    }
+                }
+                unsigned pa[4];
+                pa[0] = pack_bf16(s[0][0], s[0][1]);
+                pa[1] = pack_bf16(s[0][2], s[0][3]);
+                pa[2] = pack_bf16(s[1][0], s[1][1]);
+                pa[3] = pack_bf16(s[1][2], s[1][3]);
+                const int key = kofs + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int d = 0; d < DTILES; d += 2) {
+                    unsigned b[4];
+                    ldmatrix_x4_trans(b, vs + key * RS + cache_chunk(d + (lane >> 4), kt + key, NCH) * 8);
+                    mma_bf16(o[d], pa, b[0], b[1]);
+                    mma_bf16(o[d + 1], pa, b[2], b[3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[stg]);                   // this warp is done with the stage
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+            l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+        }
+        // every consumer warp is done with the staging area, which the partial results now take
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        constexpr int HDP = HD + 4;
+        float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
+        float* mm = mo + 4 * 16 * HDP;                           // [4][16]
+        float* ml = mm + 4 * 16;                                 // [4][16]
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int m = g_lane + 8 * i;
+            if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
+            if (m_run[i] != -INFINITY) {
+#pragma unroll
+                for (int d = 0; d < DTILES; ++d)
+                    *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+            }
+        }
+        if (NR == 1 && t_lane == 0) { mm[warp * 16 + g_lane + 8] = -INFINITY; ml[warp * 16 + g_lane + 8] = 0.f; }
+    }
+
+    // one merge over the warps of all splits through distributed shared memory (as MODE_KEYS above)
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (!producer) {
+        constexpr int HDP = HD + 4;
+        float* mo = reinterpret_cast<float*>(smem_raw);
+        float* mm = mo + 4 * 16 * HDP;
+        float* ml = mm + 4 * 16;
+        const int ns = p.num_splits;
+        const int pairs = rows * G;
+        for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
+            const int m = idx / HD, d = idx - m * HD;
+            const int r = m / G, g = m - r * G;
+            float mt = -INFINITY;
+            for (int sp = 0; sp < ns; ++sp) {
+                const float* rm = cluster.map_shared_rank(mm, sp);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) mt = fmaxf(mt, rm[w * 16 + m]);
+            }
+            float acc = 0.f, lsum = 0.f;
+            if (mt != -INFINITY) {
+                for (int sp = 0; sp < ns; ++sp) {
+                    const float* rm = cluster.map_shared_rank(mm, sp);
+                    const float* rl = cluster.map_shared_rank(ml, sp);
+                    const float* ro = cluster.map_shared_rank(mo, sp);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float mw = rm[w * 16 + m];
+                        if (mw == -INFINITY) continue;
+                        const float f = fast_exp2(mw - mt);
+                        lsum += rl[w * 16 + m] * f;
+                        acc += ro[(w * 16 + m) * HDP + d] * f;
+                    }
+                }
+            }
+            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
+                __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        }
+    }
+    cluster.sync();                      // nobody leaves while its shared memory may still be read
+}
+
 // out[row, head] = sum_s w_s * part_o[row, head, s],  w_s = 2^(lse_s - max) / sum, for the rows of one tile
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   bf16* __restrict__ out, int out_stride, const int* __restrict__ tile_row0,
@@ -785,6 +1179,10 @@ TIS_API size_t tis_attn_scratch_floats(int n_rows, int H, int num_splits) {
 // max_tile_rows: the most rows any tile has (0: unknown); keys-mode tiles of at most 8 packed
 // rows take a kernel that keeps no state for the padding rows.
 // CTAs of a mode that one SM holds at a time: tis_attn_resident_ctas.
+// decode tiles: the kernel with a producer warp (1) or the lock-step kernel (0); TIS_ATTN_DECODE_WS in the
+// environment of the process, read once
+static const bool g_decode_ws = []() { const char* e = getenv("TIS_ATTN_DECODE_WS"); return !(e && e[0] == '0'); }();
+
 static int attn_launch(int mode, const void* q, int q_stride, void* out, int out_stride, const void* plane,
                        const int* block_table, int bt_stride, int num_pages, const int* positions,
                        const int* row_slot, const int* tile_row0, const int* tile_rows, int num_tiles,
@@ -833,25 +1231,36 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
     p.fault = fault;
     p.rope_cos = rope_cos; p.rope_sin = rope_sin;
     p.plane_w = (fused && write_kv) ? (bf16*)plane : nullptr;
+    // decode tiles go to the kernel with a producer warp where its layout allows (page segments: two lanes each)
+    // and while all its CTAs are resident at once, two to an SM (its 160 threads hold as many registers as allow
+    // two; the lock-step kernel fits three).  Measured on a B200 at head size 128, context 4096, us a launch,
+    // lock-step -> producer warp: batch 1 12.7 -> 11.2, batch 4 16.1 -> 13.6, batch 8 18.8 -> 15.2 (192 CTAs);
+    // batch 16 23.2 -> 30.8 (384 CTAs, a second wave), batch 64 64.8 -> 87.5.
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const bool warp_specialised = mode == MODE_KEYS && page_size >= 4 && g_decode_ws &&
+                                  (num_splits == 1 || p.cluster_merge) &&
+                                  (long long)num_tiles * KVH * num_splits <= 2LL * sm_count;
     // stages: two; for decode tiles of a grid that leaves SMs empty anyway (fewer CTAs than SMs) as many as
-    // fit one CTA per SM and a split has tiles to fill.  Measured on a B200 inside the decode step of the
-    // 0.9B model: batch 1 (24 CTAs, six stages) 1.289 -> 1.235 ms a step; at batch 8 (192 CTAs) a third
-    // stage costs residency and the step gets slower (1.465 -> 1.486 ms), so there it stays at two.
+    // fit one CTA per SM and a split has tiles to fill (measured inside the decode step of the 0.9B model:
+    // batch 1, 24 CTAs, six stages: 1.289 -> 1.235 ms a step); the kernel with a producer warp, whose copies
+    // run ahead of the consumers, takes three wherever two CTAs of three stages fit an SM.
     int stages = 2;
     if (mode == MODE_KEYS) {
-        static int sms = 0;
-        if (sms == 0) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            if (sms <= 0) sms = 148;
-        }
+        const int sms = sm_count;
         const long long ctas = (long long)num_tiles * KVH * num_splits;
         const int tiles_per_split = keys_per_split / KT;
         for (int cand = 3; cand <= MAX_STAGES; ++cand) {
             const size_t need = smem_bytes(MODE_KEYS, cand);
             if (need > 220 * 1024 || cand - 1 > tiles_per_split) break;
-            if (ctas > (long long)sms) break;
+            // the kernel with a producer warp keeps three stages wherever two CTAs of them fit an SM
+            const bool fits_twice = warp_specialised && cand == 3 && 2 * (need + 1024) <= 220 * 1024;
+            if (ctas > (long long)sms && !fits_twice) break;
             stages = cand;
         }
     }
@@ -872,6 +1281,16 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 2, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         cudaFuncSetAttribute(attn_mma_kernel<MODE_KEYS, 1, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
 #endif
+        cudaFuncSetAttribute(attn_decode_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_decode_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_decode_kernel<1, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(attn_decode_kernel<2, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+#if TIS_HD % 32 == 0
+        cudaFuncSetAttribute(attn_decode_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_decode_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaFuncSetAttribute(attn_decode_kernel<1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(attn_decode_kernel<2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+#endif
         cudaGetLastError();
         if (3 * smem_bytes(MODE_ROWS) <= 227 * 1024)
             cudaFuncSetAttribute(attn_mma_kernel<MODE_ROWS, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -885,7 +1304,7 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         cfg.blockDim = dim3(NTHREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attrs[2];
+        cudaLaunchAttribute attrs[3];
         int na = 0;
         if (p.cluster_merge) {
             attrs[na].id = cudaLaunchAttributeClusterDimension;
@@ -909,6 +1328,24 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
             cfg.dynamicSmemBytes = 3 * smem_bytes(MODE_ROWS);
             cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 3>, p);
         } else if (mode == MODE_ROWS) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_ROWS, 2, 1>, p);
+        else if (warp_specialised) {
+            cfg.blockDim = dim3(DEC_THREADS);
+            if (!p.cluster_merge) {            // one split: a cluster of one, the same merge
+                attrs[na].id = cudaLaunchAttributeClusterDimension;
+                attrs[na].val.clusterDim.x = 1;
+                attrs[na].val.clusterDim.y = 1;
+                attrs[na].val.clusterDim.z = 1;
+                cfg.numAttrs = ++na;
+            }
+            const bool nr1 = max_tile_rows > 0 && max_tile_rows * G <= 8;
+#if TIS_HD % 32 == 0
+            if (fused && nr1) cudaLaunchKernelEx(&cfg, attn_decode_kernel<1, true>, p);
+            else if (fused) cudaLaunchKernelEx(&cfg, attn_decode_kernel<2, true>, p);
+            else
+#endif
+            if (nr1) cudaLaunchKernelEx(&cfg, attn_decode_kernel<1, false>, p);
+            else cudaLaunchKernelEx(&cfg, attn_decode_kernel<2, false>, p);
+        }
 #if TIS_HD % 32 == 0
         else if (fused && G <= 8) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 1, 1, true>, p);
         else if (fused) cudaLaunchKernelEx(&cfg, attn_mma_kernel<MODE_KEYS, 2, 1, true>, p);
