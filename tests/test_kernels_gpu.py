@@ -86,15 +86,16 @@ def test_swiglu(dtype, n, F, block):
     torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
 
 
-@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("kernel", ["boxes", "ring"])
 @pytest.mark.parametrize("n", [1, 3, 8, 16, 17, 33, 64])
 @pytest.mark.parametrize("K,N", [(1536, 2304), (128, 64), (200, 120), (4096, 1536), (72, 8), (1000, 1096),
                                  (8192, 200)])
-def test_skinny_gemm(n, K, N, tma, monkeypatch):
-    """The weight-streaming products for few rows (weights as TMA boxes, a share at once — K of 8192 over
-    eight CTAs takes two rounds of boxes —; weights copied by the threads into a ring), for every split of K
-    over a cluster."""
+def test_skinny_gemm(n, K, N, kernel, monkeypatch):
+    """The weight-streaming products for few rows (a producer warp bringing a CTA's whole share of the weights
+    as boxes of the TMA engine — K of 8192 over eight CTAs takes two rounds of boxes —; or the weights copied
+    by all threads into a ring), for every split of K over a cluster."""
     ops = _ops()
+    tma = kernel != "ring"
     monkeypatch.setattr(ops, "STREAM_GEMM", tma)
     monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)           # every product that fits goes to the boxes
     before = ops.calls["gemm_stream"]
@@ -111,17 +112,17 @@ def test_skinny_gemm(n, K, N, tma, monkeypatch):
     got = ops.gemm_skinny(a.cuda(), wide[:, :N])
     torch.testing.assert_close(got.cpu().double(), a.double() @ wide[:, :N].cpu().double(), rtol=2e-2, atol=2e-2)
     fits = sum(ops._stream_fits(n, K, ks or ops._ksplit(N, K)) for ks in (None, 1, 2, 4, 8, None))
-    assert ops.calls["gemm_stream"] - before == (fits if tma else 0) and (fits >= 4 or K == 8192)
+    assert ops.calls["gemm_stream"] - before == (fits if tma else 0) and fits >= 2
     if tma and ops._tc_fault is not None:
         assert int(ops._tc_fault[0]) == 0, "a wait inside the kernel ran out"
 
 
-@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("kernel", ["boxes", "ring"])
 @pytest.mark.parametrize("n", [1, 8, 40, 64])
 @pytest.mark.parametrize("K,F", [(1536, 4096), (120, 352), (64, 32)])
-def test_skinny_gemm_with_swiglu_epilogue(n, K, F, tma, monkeypatch):
+def test_skinny_gemm_with_swiglu_epilogue(n, K, F, kernel, monkeypatch):
     ops = _ops()
-    monkeypatch.setattr(ops, "STREAM_GEMM", tma)
+    monkeypatch.setattr(ops, "STREAM_GEMM", kernel != "ring")
     monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)
     monkeypatch.setattr(ops, "SKINNY_SWIGLU_MAX_ROWS", 64)
     g = torch.Generator().manual_seed(13)
@@ -386,6 +387,87 @@ def test_paged_attention_window_edge(dtype):
             assert (got.float() - 9.0).abs().max() < 0.1
         else:
             assert got.float().abs().max() < 1.0
+
+
+@pytest.mark.parametrize("path,start,n", [("rows", 300, 160), ("groups3", 0, 700), ("tc", 300, 160), ("tc", 0, 700)])
+@pytest.mark.parametrize("H,KVH,hd,page,W", [(8, 2, 128, 16, 128), (4, 2, 64, 32, 64), (6, 2, 128, 64, 192)])
+def test_window_edge_in_prompt_portions(path, start, n, H, KVH, hd, page, W, monkeypatch):
+    """The edge of the window for rows inside tiles of many rows (the row-tile kernel, its variant with three
+    key groups, the tcgen05 kernel): for chosen rows — the first, a middle and the last row of a tile, on both
+    sides of tile borders — the key just inside the window is made to stand out for that row alone, and the key
+    just outside to stand out more still.  A row that sees one key too many, or one too few, comes out as
+    another value row altogether.  The window is a multiple of the page and of the 64-key tile, so
+    the edges of the chosen rows fall on page and tile borders as well as inside them; two padding rows of a
+    stage that runs behind lead the portion."""
+    from tiny_inference_server_b200.kernels.attention_plan import TileSet, plan_tiles
+    ops = _ops()
+    g = torch.Generator().manual_seed(51)
+    dtype = torch.bfloat16
+    L = start + n
+    plane, table = _fill_cache(dtype, [L], KVH, hd, page, g)
+    pad = 2
+    chosen = sorted({r for r in (0, 15, 16, 40, 63, 64, 100, 127, 128, 159, 200, 255, 256, 511, 512, n - 1)
+                     if r < n and start + r - W >= 0})
+    assert len(chosen) >= 5
+
+    # every chosen row looks along a direction of its own; its two keys point that way
+    marks = {}
+    for i, r in enumerate(chosen):
+        d = 3 + 2 * i
+        marks.setdefault(start + r - W, torch.zeros(hd))[d] = 120.0        # just outside the window of row r
+        marks.setdefault(start + r - W + 1, torch.zeros(hd))[d] = 80.0     # just inside
+    for pos, m in marks.items():
+        pg = int(table[0, pos // page])
+        for kvh in range(KVH):
+            plane[pg, 0, kvh, pos % page] = ref.cache_row(m.to(dtype), pos)
+    rows = [(-1, 0)] * pad + [(0, start + r) for r in range(n)]
+    row_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    positions = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    q = _rand((n + pad, (H + 2 * KVH) * hd), dtype, g, 0.3)
+    for i, r in enumerate(chosen):
+        for h in range(H):
+            q[pad + r, h * hd: (h + 1) * hd] = 0.0
+            q[pad + r, h * hd + 3 + 2 * i] = 8.0
+    fault = torch.zeros(4, dtype=torch.int32)
+    want = ref.paged_attention(q, torch.empty(n + pad, H * hd, dtype=dtype), plane, table, positions, row_slot, H, KVH,
+                               hd, page, W, fault)
+    # the tiles as the engine makes them: the padding rows belong to the segment that follows them
+    keys, rws, wide, rows_in_wide = plan_tiles([(0, n + pad)], H // KVH)
+
+    def t(v):
+        return torch.tensor(v, dtype=torch.int32, device="cuda")
+
+    tiles = TileSet((t([k[0] for k in keys]), t([k[1] for k in keys]), len(keys)),
+                    (t([k[0] for k in rws]), t([k[1] for k in rws]), len(rws)), max((k[1] for k in keys), default=0),
+                    (t([k[0] for k in wide]), t([k[1] for k in wide]), len(wide)), rows_in_wide)
+
+    class Step:
+        decode_only = False
+        max_position, min_position = L - 1, start
+
+        def plan(self, planner):
+            return tiles
+
+    monkeypatch.setattr(ops, "TC_ATTENTION", path == "tc")
+    monkeypatch.setattr(ops, "TC_ATTENTION_MIN_TILES", 1)
+    before = dict(ops.calls)
+    fault_dev = fault.cuda()
+    got = ops.paged_attention(q.cuda(), torch.full((n + pad, H * hd), 7.0, dtype=dtype, device="cuda"), plane.cuda(),
+                              table.cuda(), positions.cuda(), row_slot.cuda(), H, KVH, hd, page, W, fault_dev, Step())
+    torch.cuda.synchronize()
+    assert int(fault_dev[0]) == 0
+    assert (ops.calls["attn_tc"] - before.get("attn_tc", 0) == 1) == (path == "tc")
+    if path != "tc":
+        assert ops.calls["attn_rows"] - before.get("attn_rows", 0) == 1
+    got = got.cpu().float()
+    valid = row_slot >= 0
+    torch.testing.assert_close(got[valid], want.float()[valid], rtol=2e-2, atol=2e-2)
+    for r in chosen:                       # the key just inside wins: its value row comes out, for every head
+        pos = start + r - W + 1
+        pg = int(table[0, pos // page])
+        for h in range(H):
+            v = ref.cache_row_inverse(plane[pg, 1, h // (H // KVH), pos % page], pos).float()
+            torch.testing.assert_close(got[pad + r, h * hd:(h + 1) * hd], v, rtol=5e-2, atol=5e-2)
 
 
 def test_paged_attention_refuses_bad_head_size():

@@ -6,10 +6,10 @@
 // shared memory.  What differs is how W comes: the whole share of a CTA (up to 512 rows of K, 64 KB)
 // is ordered at once by one thread as 64 x 64 boxes of a tensor map (cp.async.bulk.tensor.2d, 128-byte
 // swizzle, zeros beyond N and K), each box counted on an mbarrier of its own — and it is ordered
-// before the kernel waits for the kernel before it (griddepcontrol.wait), because weights depend on
-// nothing.  So all bytes of the product are in flight from the start, no thread spends issue slots on
-// copies, and the loop has no CTA-wide barrier: a warp waits for a box and multiplies
-// (mma.sync m16n8k16, x from shared memory by ldmatrix, W by ldmatrix.trans through the swizzle).
+// by a warp that never waits for the kernel before this one (griddepcontrol.wait), because weights
+// depend on nothing.  So all bytes of the product are in flight from the start, the four consumer warps
+// spend no issue slots on copies, and the loop has no CTA-wide barrier: a warp waits for a box and
+// multiplies (mma.sync m16n8k16, x from shared memory by ldmatrix, W by ldmatrix.trans through the swizzle).
 // Shares of more than 512 rows of K are walked in rounds of eight boxes.
 // Every wait on an mbarrier is bounded; one that runs out sets the fault word.
 #include "tc_common.cuh"
@@ -55,21 +55,26 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// A fifth warp does nothing but order weights (one lane orders the boxes); the four consumer warps never
+// meet inside the loop.  (The same with the producer warp copying 16-byte chunks by cp.async instead was
+// measured too: 9.1 us against 6.3 us for the down projection, one warp cannot issue them fast enough.)
 template <int MT>
-__global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p) {
+__global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p) {
     namespace cg = cooperative_groups;
     extern __shared__ unsigned char smem_raw[];
     // boxes at 1024-byte boundaries: the swizzle is a function of the address
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) unsigned long long bars[MAX_BOXES];
+    __shared__ __align__(8) unsigned long long bars[MAX_BOXES], empty[MAX_BOXES];
     __shared__ int abort_flag;
     __shared__ float pair[2][BN];
+    constexpr int BOX_SM = BOX_ELEMS;                                 // elements of a box in shared memory
     const int xrow = p.kc + 8;                                        // padded rows: 16 bytes apart modulo 128
-    bf16* w_sm = reinterpret_cast<bf16*>(base);                       // boxes x [64 k][64 n], swizzled
-    bf16* xs = w_sm + (size_t)p.boxes * BOX_ELEMS;                    // [MT*16][xrow]: this CTA's share of K
+    bf16* w_sm = reinterpret_cast<bf16*>(base);                       // boxes x [64 k][WROW]
+    bf16* xs = w_sm + (size_t)p.boxes * BOX_SM;                       // [MT*16][xrow]: this CTA's share of K
     float* red = reinterpret_cast<float*>(base);                      // after the loop: [MT*16][BN] partial sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool producer = warp == NTH / 32;
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank(), ksplit = cluster.num_blocks();
     const int n0 = blockIdx.x * BN;
@@ -80,15 +85,33 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
     if (tid == 0) {
         abort_flag = 0;
-        for (int b = 0; b < MAX_BOXES; ++b) mbar_init(&bars[b], 1);
+        for (int b = 0; b < MAX_BOXES; ++b) { mbar_init(&bars[b], 1); mbar_init(&empty[b], NTH / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        // the first round of weights, before anything else: they depend on nothing
-        const int first = nkt < p.boxes ? nkt : p.boxes;
-        for (int b = 0; b < first; ++b) {
-            mbar_arrive_expect_tx(&bars[b], BOX_BYTES);
-            tma_load_2d(w_sm + (size_t)b * BOX_ELEMS, &wmap, n0, k_begin + b * BK, &bars[b]);
-        }
     }
+    __syncthreads();
+
+    float acc[MT][2][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) { acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f; }
+
+    if (producer) {
+        // weights depend on nothing: no wait for the kernel before.  Box `it` goes to slot it % boxes, once
+        // every consumer warp is done with the box that was there a round earlier.
+        bool alive = true;
+        for (int it = 0; it < nkt; ++it) {
+            const int b = it % p.boxes;
+            if (it >= p.boxes) {
+                if (alive) alive = mbar_wait(&empty[b], (unsigned)(((it / p.boxes) - 1) & 1), &abort_flag, p.fault, 7);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&bars[b], BOX_BYTES);
+                tma_load_2d(w_sm + (size_t)b * BOX_SM, &wmap, n0, k_begin + it * BK, &bars[b]);
+            }
+        }
+    } else {
     // x is the output of the kernel before this one
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     {
@@ -103,13 +126,7 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
         asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
-    __syncthreads();                               // xs, the barriers and abort_flag are visible to every warp
-
-    float acc[MT][2][4];
-#pragma unroll
-    for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) { acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f; }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");          // xs is visible to every consumer warp
 
     const unsigned w_base = smem_u32(w_sm);
     // ldmatrix.trans of the warp's 16 columns: lane -> (row inside the k16 block, 16-byte chunk of the box row)
@@ -118,21 +135,9 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
     bool alive = true;
     for (int it = 0; it < nkt; ++it) {
         const int b = it % p.boxes;
-        if (it >= p.boxes && b == 0) {
-            // a new round: everyone is done with the boxes of the round before; order the next ones
-            __syncthreads();
-            if (tid == 0) {
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                const int left = nkt - it < p.boxes ? nkt - it : p.boxes;
-                for (int j = 0; j < left; ++j) {
-                    mbar_arrive_expect_tx(&bars[j], BOX_BYTES);
-                    tma_load_2d(w_sm + (size_t)j * BOX_ELEMS, &wmap, n0, k_begin + (it + j) * BK, &bars[j]);
-                }
-            }
-        }
         if (alive) alive = mbar_wait(&bars[b], (unsigned)((it / p.boxes) & 1), &abort_flag, p.fault, 6);
         if (!alive) continue;                      // a wait ran out: no more waits, the result is not to be used
-        const unsigned box = w_base + (unsigned)b * BOX_BYTES;
+        const unsigned box = w_base + (unsigned)b * (BOX_SM * 2);
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
             unsigned bf[4];
@@ -147,11 +152,17 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
                 mma16816(acc[m][1], a, bf[2], bf[3]);
             }
         }
+        if (nkt > p.boxes) {                       // the slot is taken again a round later
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[b]);
+        }
     }
+    }   // consumers
     __syncthreads();                    // all warps are done with the staging memory
 
     // partial sums of this CTA into shared memory
     const int g = lane >> 2, t = lane & 3;
+    if (!producer)
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
@@ -166,8 +177,9 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
 
     // rank r adds up rows r, r + ksplit, ... over all CTAs of the cluster and writes them;
     // two rows at a time (threads 0-63 and 64-127), one column per thread
-    const int half = tid >> 6, col = tid & 63;
-    for (int row0 = (int)rank; row0 < p.M; row0 += 2 * (int)ksplit) {      // the same trips for every thread
+    const int half = (tid >> 6) & 1, col = tid & 63;
+    if (!producer)
+    for (int row0 = (int)rank; row0 < p.M; row0 += 2 * (int)ksplit) {      // the same trips for every consumer thread
         const int row = row0 + half * (int)ksplit;
         const bool valid = row < p.M;
         float sum = 0.f;
@@ -178,12 +190,12 @@ __global__ void __launch_bounds__(NTH) gemm_stream_kernel(const __grid_constant_
         } else {
             // the strip is [32 gate | 32 up]: out column strip*32 + j = silu(gate_j) * up_j
             pair[half][col] = sum;
-            __syncthreads();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
             if (valid && col < 32) {
                 const float gt = pair[half][col], up = pair[half][col + 32];
                 p.out[(size_t)row * p.ldo + blockIdx.x * 32 + col] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
             }
-            __syncthreads();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
         }
     }
     cluster.sync();                     // nobody leaves while its shared memory may still be read
@@ -239,7 +251,7 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((N + BN - 1) / BN, ksplit, 1);
-    cfg.blockDim = dim3(NTH, 1, 1);
+    cfg.blockDim = dim3(NTH + 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];

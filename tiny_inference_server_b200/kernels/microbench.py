@@ -195,10 +195,14 @@ def gemm(args):
         mb = K * N * 2 / 1e6
         extra = ""
         if n <= 64:
-            ops.STREAM_GEMM = not ops.STREAM_GEMM
-            c = _graph_time(mine)
-            ops.STREAM_GEMM = not ops.STREAM_GEMM
-            extra = f"   {'ring' if ops.STREAM_GEMM else 'TMA-fed'} kernel {c:7.2f} us"
+            # both weight-streaming kernels, whatever the dispatch would choose: the ring, the TMA boxes
+            saved = (ops.STREAM_GEMM, ops.STREAM_MIN_KC)
+            times = {}
+            for label, sg in (("ring", False), ("boxes", True)):
+                ops.STREAM_GEMM, ops.STREAM_MIN_KC = sg, 0
+                times[label] = _graph_time(mine)
+            ops.STREAM_GEMM, ops.STREAM_MIN_KC = saved
+            extra = "   " + "  ".join(f"{k} {v:6.2f}" for k, v in times.items())
         print(f"gemm {name:15s} rows {n:4d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s, "
               f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us{extra}")
 
