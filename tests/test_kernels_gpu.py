@@ -98,6 +98,9 @@ def test_skinny_gemm(n, K, N, kernel, monkeypatch):
     tma = kernel != "ring"
     monkeypatch.setattr(ops, "STREAM_GEMM", tma)
     monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)           # every product that fits goes to the boxes
+    monkeypatch.setattr(ops, "STREAM_MAX_KC", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_CTAS", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_ROWS", 64)
     before = ops.calls["gemm_stream"]
     g = torch.Generator().manual_seed(12)
     a = _rand((n, K), torch.bfloat16, g)
@@ -124,6 +127,9 @@ def test_skinny_gemm_with_swiglu_epilogue(n, K, F, kernel, monkeypatch):
     ops = _ops()
     monkeypatch.setattr(ops, "STREAM_GEMM", kernel != "ring")
     monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)
+    monkeypatch.setattr(ops, "STREAM_MAX_KC", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_CTAS", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_ROWS", 64)
     monkeypatch.setattr(ops, "SKINNY_SWIGLU_MAX_ROWS", 64)
     g = torch.Generator().manual_seed(13)
     a = _rand((n, K), torch.bfloat16, g)

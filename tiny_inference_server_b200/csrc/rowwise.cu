@@ -245,6 +245,52 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     const T* ksrc = row + (size_t)H * hd;
     const T* vsrc = ksrc + (size_t)KVH * hd;
 
+    if (fast && nthr % (half / N) == 0) {
+        // the threads of a row divide evenly over the chunk pairs of a head: a thread keeps one chunk pair
+        // (c, c + half/N) for every head it visits, so its cosines and sines are loaded once
+        const int cpairs = half / N;
+        const int c = tid % cpairs;
+        float cv[N], sv[N];
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+            const float4 cc = *reinterpret_cast<const float4*>(cs + c * N + j);
+            const float4 sc = *reinterpret_cast<const float4*>(sn + c * N + j);
+            cv[j] = cc.x; cv[j + 1] = cc.y; cv[j + 2] = cc.z; cv[j + 3] = cc.w;
+            sv[j] = sc.x; sv[j + 1] = sc.y; sv[j + 2] = sc.z; sv[j + 3] = sc.w;
+        }
+        const int heads = H + (page >= 0 ? KVH : 0);           // query heads, then (when written) key heads
+        for (int hh = tid / cpairs; hh < heads; hh += nthr / cpairs) {
+            const bool is_k = hh >= H;
+            const int h = is_k ? hh - H : hh;
+            const T* src = (is_k ? ksrc : row) + (size_t)h * hd;
+            float x1[N], x2[N], o1[N], o2[N];
+            Vec16<T>::load(src + c * N, x1);
+            Vec16<T>::load(src + half + c * N, x2);
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                o1[j] = x1[j] * cv[j] - x2[j] * sv[j];
+                o2[j] = x2[j] * cv[j] + x1[j] * sv[j];
+            }
+            if (!is_k) {
+                T* dst = row + (size_t)h * hd;
+                Vec16<T>::store(dst + c * N, o1);
+                Vec16<T>::store(dst + half + c * N, o2);
+            } else {
+                T* dst = kdst + (size_t)h * page_size * hd;
+                Vec16<T>::store(dst + cache_chunk(c, pos, nch) * N, o1);
+                Vec16<T>::store(dst + cache_chunk(c + cpairs, pos, nch) * N, o2);
+            }
+        }
+        if (page >= 0) {
+            for (int w = tid; w < KVH * nch; w += nthr) {
+                const int h = w / nch, cc = w - h * nch;
+                float v[N];
+                Vec16<T>::load(vsrc + (size_t)h * hd + cc * N, v);
+                Vec16<T>::store(vdst + (size_t)h * page_size * hd + cache_chunk(cc, pos, nch) * N, v);
+            }
+        }
+        return;
+    }
     if (fast) {
         // one work item = the chunk pair (c, c + half/N) of one head: both halves of N rotation pairs
         const int cpairs = half / N;

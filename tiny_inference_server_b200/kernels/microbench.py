@@ -196,12 +196,14 @@ def gemm(args):
         extra = ""
         if n <= 64:
             # both weight-streaming kernels, whatever the dispatch would choose: the ring, the TMA boxes
-            saved = (ops.STREAM_GEMM, ops.STREAM_MIN_KC)
+            saved = (ops.STREAM_GEMM, ops.STREAM_MIN_KC, ops.STREAM_MAX_KC, ops.STREAM_MAX_CTAS, ops.STREAM_MAX_ROWS)
             times = {}
             for label, sg in (("ring", False), ("boxes", True)):
-                ops.STREAM_GEMM, ops.STREAM_MIN_KC = sg, 0
-                times[label] = _graph_time(mine)
-            ops.STREAM_GEMM, ops.STREAM_MIN_KC = saved
+                ops.STREAM_GEMM, ops.STREAM_MIN_KC, ops.STREAM_MAX_KC, ops.STREAM_MAX_CTAS, ops.STREAM_MAX_ROWS = \
+                    sg, 0, 1 << 30, 1 << 30, 64
+                if not sg or ops._stream_fits(n, K, ops._ksplit(N, K)):
+                    times[label] = _graph_time(mine)
+            (ops.STREAM_GEMM, ops.STREAM_MIN_KC, ops.STREAM_MAX_KC, ops.STREAM_MAX_CTAS, ops.STREAM_MAX_ROWS) = saved
             extra = "   " + "  ".join(f"{k} {v:6.2f}" for k, v in times.items())
         print(f"gemm {name:15s} rows {n:4d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s, "
               f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us{extra}")

@@ -131,15 +131,23 @@ def _ksplit(n_cols: int, k: int) -> int:
 #: qkv 4.1 / 4.4 / 4.6 ring, 5.2 / 5.8 / 6.3 boxes (4.8 / 4.8 / 4.5); gate/up with gating 7.6 / 8.3 / 9.1 ring,
 #: 10.9 / 11.9 / 13.5 boxes; down (K 4096, 512 rows of K a CTA) 7.4 / 7.8 / 8.2 ring, 6.2 / 6.5 / 6.9 boxes
 #: (7.4 / 7.4 / 7.4).  A box row is 128 bytes, one request of the TMA engine each: with many CTAs per SM the
-#: engine is the bottleneck, while a long share of K gains from having all of it in flight from the start.  So the
-#: boxes take products whose share of K per CTA is at least STREAM_MIN_KC rows, up to STREAM_MAX_ROWS rows of x.
+#: engine is the bottleneck, while a long share of K gains from having all of it in flight from the start.  With
+#: shares of more than one round of boxes (the 3B- and 8B-sized models: 1024 rows of K a CTA and more) the kernel
+#: loses to both others (8B model at one row: 132 against 210 tok/s).  So the boxes take products whose share of
+#: K per CTA is STREAM_MIN_KC..STREAM_MAX_KC rows (one full round), of at most STREAM_MAX_CTAS CTAs, up to
+#: STREAM_MAX_ROWS rows of x.
 STREAM_GEMM = os.environ.get("TIS_STREAM_GEMM", "1") != "0"
 STREAM_MIN_KC = int(os.environ.get("TIS_STREAM_MIN_KC", "512"))
+STREAM_MAX_KC = int(os.environ.get("TIS_STREAM_MAX_KC", "512"))
+STREAM_MAX_CTAS = int(os.environ.get("TIS_STREAM_MAX_CTAS", "296"))
 STREAM_MAX_ROWS = int(os.environ.get("TIS_STREAM_MAX_ROWS", "16"))
 
 
-def _stream_pays(n: int, k: int, cols: int) -> bool:
-    return STREAM_GEMM and n <= STREAM_MAX_ROWS and -(-k // _ksplit(cols, k)) >= STREAM_MIN_KC
+def _stream_pays(n: int, k: int, cols: int, ksplit: Optional[int] = None) -> bool:
+    ks = ksplit or _ksplit(cols, k)
+    kc = -(-k // ks)
+    return (STREAM_GEMM and n <= STREAM_MAX_ROWS and STREAM_MIN_KC <= kc <= max(STREAM_MAX_KC, STREAM_MIN_KC)
+            and -(-cols // 64) * ks <= STREAM_MAX_CTAS)
 
 
 def _stream_fits(n: int, k: int, ksplit: int) -> bool:
@@ -170,8 +178,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
                 ksplit: Optional[int] = None) -> torch.Tensor:
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by a weight-streaming kernel; with ``swiglu``
     the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
-    if (STREAM_GEMM and STREAM_MIN_KC <= -(-a.shape[1] // (ksplit or _ksplit(w.shape[1], a.shape[1])))
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+    if (_stream_pays(a.shape[0], a.shape[1], w.shape[1], ksplit) and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and _stream_fits(a.shape[0], a.shape[1], ksplit or _ksplit(w.shape[1], a.shape[1]))):
         return gemm_stream(a, w, out, swiglu, ksplit)
     lib = library()
