@@ -120,6 +120,46 @@ def test_skinny_gemm(n, K, N, kernel, monkeypatch):
         assert int(ops._tc_fault[0]) == 0, "a wait inside the kernel ran out"
 
 
+@pytest.mark.parametrize("n", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("K,N", [(1536, 2304), (128, 64), (200, 120), (4096, 1536), (72, 8), (1000, 1096), (8192, 200)])
+def test_tcgen05_gemm_with_swapped_operands(n, K, N):
+    """Few rows on the tcgen05 tensor cores: 128 columns of the weights are the rows of the tile, the rows of x its
+    narrow side; every split of K over a cluster; ragged N and K (zeros from the TMA engine); a weight matrix that is
+    a column slice of a wider one; the bounded waits must not have run out."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(61)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, N), torch.bfloat16, g, 0.05)
+    want = (a.double() @ w.double())
+    for ksplit in (None, 1, 2, 4, 8):
+        got = ops.gemm_swap(a.cuda(), w.cuda(), ksplit=ksplit)
+        assert got.shape == (n, N) and got.dtype == torch.bfloat16
+        torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    wide = _rand((K, N + 64), torch.bfloat16, g, 0.05).cuda()
+    got = ops.gemm_swap(a.cuda(), wide[:, :N])
+    torch.testing.assert_close(got.cpu().double(), a.double() @ wide[:, :N].cpu().double(), rtol=2e-2, atol=2e-2)
+    assert int(ops.tc_fault()[0]) == 0, "a wait inside the kernel ran out"
+    # a row alone gives the same numbers as the row in the batch
+    r = n // 2
+    alone = ops.gemm_swap(a[r:r + 1].cuda(), w.cuda())
+    assert torch.equal(alone[0], ops.gemm_swap(a.cuda(), w.cuda())[r])
+
+
+@pytest.mark.parametrize("n", [1, 8, 40, 64])
+@pytest.mark.parametrize("K,F", [(1536, 4096), (120, 352), (64, 32)])
+def test_tcgen05_gemm_with_swapped_operands_and_swiglu_epilogue(n, K, F):
+    ops = _ops()
+    g = torch.Generator().manual_seed(62)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, 2 * F), torch.bfloat16, g, 0.05)
+    gu = (a.double() @ w.double()).reshape(n, F // 32, 2, 32)
+    want = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(n, F)
+    got = ops.gemm_swap(a.cuda(), w.cuda(), swiglu=True)
+    assert got.shape == (n, F)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    assert int(ops.tc_fault()[0]) == 0
+
+
 @pytest.mark.parametrize("kernel", ["boxes", "ring"])
 @pytest.mark.parametrize("n", [1, 8, 40, 64])
 @pytest.mark.parametrize("K,F", [(1536, 4096), (120, 352), (64, 32)])

@@ -204,6 +204,7 @@ def gemm(args):
                 if not sg or ops._stream_fits(n, K, ops._ksplit(N, K)):
                     times[label] = _graph_time(mine)
             (ops.STREAM_GEMM, ops.STREAM_MIN_KC, ops.STREAM_MAX_KC, ops.STREAM_MAX_CTAS, ops.STREAM_MAX_ROWS) = saved
+            times["tcgen05 swapped"] = _graph_time(lambda i: ops.gemm_swap(inp, ws[i % 12], swiglu=fused))
             extra = "   " + "  ".join(f"{k} {v:6.2f}" for k, v in times.items())
         print(f"gemm {name:15s} rows {n:4d} {mb:6.1f} MB: this kernel {a:7.2f} us ({mb / a * 1e3:7.1f} GB/s, "
               f"{2 * n * K * N / a / 1e6:6.1f} TFLOP/s)   library {b:7.2f} us{extra}")

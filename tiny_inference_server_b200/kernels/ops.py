@@ -105,6 +105,13 @@ SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "4"))
 #: ungated product: the kernel keeps it up to more rows (measured alone at 8 rows: 8.4 us against 9.1 us
 #: for the library product plus the gating kernel; inside the decode step at batch 8: 5123 -> 5207 tok/s)
 SKINNY_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SKINNY_SWIGLU_MAX_ROWS", "16"))
+#: above that and up to this many rows the gate/up product with the gating goes to the tcgen05 kernel with swapped
+#: operands (csrc/gemm_swap.cu).  Measured alone at the 0.9B shapes: 9.9 us at 32 rows and 11.7 us at 64, against 10.4 and
+#: 10.6 us for the library product, which still needs the gating kernel (~2.5 us) after it; the plain products of these
+#: row counts stay with the library (qkv at 64 rows: 4.6 us against 7.8).  Inside the decode step of the 0.9B model:
+#: batch 24 2.022 -> 2.012 ms, batch 32 2.135 -> 2.119, batch 64 3.052 -> 3.078, so it is used up to 32 rows.
+#: TIS_SWAP_SWIGLU_MAX_ROWS overrides (0: never).
+SWAP_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SWAP_SWIGLU_MAX_ROWS", "32"))
 EPI_STORE, EPI_SWIGLU = 0, 1
 
 
@@ -148,6 +155,32 @@ def _stream_pays(n: int, k: int, cols: int, ksplit: Optional[int] = None) -> boo
     kc = -(-k // ks)
     return (STREAM_GEMM and n <= STREAM_MAX_ROWS and STREAM_MIN_KC <= kc <= max(STREAM_MAX_KC, STREAM_MIN_KC)
             and -(-cols // 64) * ks <= STREAM_MAX_CTAS)
+
+
+def _ksplit_swap(n_cols: int, k: int) -> int:
+    """CTAs that share a strip of 128 columns in the tcgen05 product with swapped operands."""
+    strips = (n_cols + 127) // 128
+    ks = 8
+    while ks > 1 and (strips * ks > 2 * 148 or k // ks < 128):
+        ks //= 2
+    return ks
+
+
+def gemm_swap(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+              ksplit: Optional[int] = None) -> torch.Tensor:
+    """``a (n <= 64, K) @ w (K, N)`` in bfloat16 on the tcgen05 tensor cores with the operands swapped (128
+    columns of ``w`` are the rows of the tile, the rows of ``a`` its narrow side); with ``swiglu`` the columns of
+    ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    lib = library()
+    n, k = a.shape
+    cols = w.shape[1]
+    if out is None:
+        out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
+    calls["gemm_swap"] += 1
+    _check(lib.tis_gemm_swap(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                             ksplit or _ksplit_swap(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()),
+                             _stream()), lib)
+    return out
 
 
 def _stream_fits(n: int, k: int, ksplit: int) -> bool:
@@ -295,6 +328,9 @@ def gemm_swiglu(a: torch.Tensor, w_gu: torch.Tensor, hidden: int, block: int) ->
     gating in its epilogue; else the product and the gating kernel."""
     if block == 32 and _skinny_ok(a, w_gu, SKINNY_SWIGLU_MAX_ROWS):
         return gemm_skinny(a, w_gu, swiglu=True)
+    if (block == 32 and _skinny_ok(a, w_gu, SWAP_SWIGLU_MAX_ROWS) and w_gu.shape[1] % 64 == 0
+            and a.data_ptr() % 16 == 0 and w_gu.data_ptr() % 16 == 0):
+        return gemm_swap(a, w_gu, swiglu=True)
     if block == 32 and _tc_ok(a, w_gu, TC_MIN_ROWS) and w_gu.shape[1] % 64 == 0:
         return gemm_tc(a, w_gu, swiglu=True)
     gu = gemm(a, w_gu)
