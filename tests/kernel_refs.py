@@ -15,8 +15,36 @@ from typing import Optional
 import torch
 
 
-def gemm(a, w, out=None):
-    r = (a.to(torch.float32) @ w.to(torch.float32)).to(a.dtype)
+def _row_factor(scaled):
+    """sqrt(width) / (||row of the stream|| + eps) from the partial sums of squares."""
+    d = scaled.rows.shape[1]
+    return math.sqrt(d) / (scaled.parts.sum(-1, keepdim=True).sqrt() + scaled.eps)
+
+
+def scaled_rows_dense(scaled):
+    return (scaled.rows.to(torch.float32) * _row_factor(scaled)).to(scaled.rows.dtype)
+
+
+def gemm(a, w, out=None, sink=None):
+    """``a`` may be ``ops.ScaledRows`` (the product is multiplied by each row's factor afterwards); with a
+    ``sink`` of matching shape and few bfloat16 rows the product is added to the stream there and the
+    stream times the next norm's weight comes back with partial sums of squares by strip of 64 columns."""
+    from tiny_inference_server_b200.kernels import ops
+    factor = None
+    if isinstance(a, ops.ScaledRows):
+        factor, a = _row_factor(a), a.rows
+    r = a.to(torch.float32) @ w.to(torch.float32)
+    if factor is not None:
+        r = r * factor
+    if (sink is not None and out is None and a.dtype == torch.bfloat16 and a.shape[0] <= ops.SKINNY_MAX_ROWS
+            and tuple(sink.values.shape) == tuple(r.shape)):
+        sink.values += r
+        n, d = r.shape
+        strips = -(-d // 64)
+        sq = torch.zeros((n, strips * 64), dtype=torch.float32)
+        sq[:, :d] = sink.values.pow(2)
+        return ops.ScaledRows((sink.values * sink.weight).to(a.dtype), sq.reshape(n, strips, 64).sum(-1), sink.eps, sink.norm)
+    r = r.to(a.dtype)
     if out is not None:
         out.copy_(r)
         return out
@@ -294,3 +322,4 @@ def install(monkeypatch) -> None:
     g = globals()
     for name in _NAMES:
         monkeypatch.setattr(ops, name, g[name])
+    monkeypatch.setattr(ops.ScaledRows, "dense", scaled_rows_dense)

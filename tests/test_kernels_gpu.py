@@ -187,6 +187,89 @@ def test_skinny_gemm_with_swiglu_epilogue(n, K, F, kernel, monkeypatch):
         torch.testing.assert_close(ops.gemm_swiglu(a2.cuda(), w.cuda(), F, 32).cpu().double(), want2, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("kernel", ["boxes", "ring"])
+@pytest.mark.parametrize("n", [1, 5, 8, 16, 33, 64])
+@pytest.mark.parametrize("K,N", [(1536, 1536), (4096, 1536), (200, 120), (72, 8), (1000, 1096)])
+def test_skinny_gemm_adds_to_the_stream_and_defers_the_norm(n, K, N, kernel, monkeypatch):
+    """The residual epilogue (stream += product; stream * next norm's weight; partial sums of squares) and the
+    product that applies the norm's factor per row afterwards, together against add + norm + product in float64.
+    eps is large, so a factor with eps in the wrong place would show."""
+    ops = _ops()
+    monkeypatch.setattr(ops, "STREAM_GEMM", kernel != "ring")
+    monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)
+    monkeypatch.setattr(ops, "STREAM_MAX_KC", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_CTAS", 1 << 30)
+    monkeypatch.setattr(ops, "STREAM_MAX_ROWS", 64)
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 64)
+    monkeypatch.setattr(ops, "SKINNY_SWIGLU_MAX_ROWS", 64)
+    g = torch.Generator().manual_seed(21)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, N), torch.bfloat16, g, 0.05)
+    stream = _rand((n, N), torch.float32, g, 2.0)
+    stream[0] *= 30.0                                        # rows of very different length
+    weight = 1.0 + _rand((N,), torch.float32, g, 0.3)
+    eps = 0.75
+    new_stream = stream.double() + a.double() @ w.double()
+    normed = new_stream * math.sqrt(N) / (new_stream.norm(dim=-1, keepdim=True) + eps) * weight.double()
+    F = 64
+    w2 = _rand((N, 2 * F), torch.bfloat16, g, 0.05)
+    want2 = normed @ w2.double()
+    factor = math.sqrt(N) / (new_stream.norm(dim=-1, keepdim=True) + eps)
+    for ksplit in (None, 1, 2, 4, 8):
+        values = stream.cuda()
+        sink = ops.ResidualSink(values, weight.cuda(), eps, norm="the norm")
+        rows = ops.gemm_skinny(a.cuda(), w.cuda(), ksplit=ksplit, sink=sink)
+        assert isinstance(rows, ops.ScaledRows) and rows.norm == "the norm" and rows.parts.shape == (n, -(-N // 64))
+        torch.testing.assert_close(values.cpu().double(), new_stream, rtol=1e-3, atol=2e-2)
+        torch.testing.assert_close(rows.rows.cpu().double(), new_stream * weight.double(), rtol=1e-2, atol=2e-2)
+        pad = torch.zeros(n, -(-N // 64) * 64, dtype=torch.float64)
+        pad[:, :N] = values.cpu().double() ** 2
+        torch.testing.assert_close(rows.parts.cpu().double(), pad.reshape(n, -1, 64).sum(-1), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(rows.dense().cpu().double(), normed, rtol=2e-2, atol=2e-2)
+        got2 = ops.gemm(rows, w2.cuda())
+        torch.testing.assert_close(got2.cpu().double(), want2, rtol=2e-2, atol=2e-2)
+        # the gated product against the same product of the rows as they were rounded to bfloat16
+        gu = ((rows.rows.cpu().double() * factor) @ w2.double()).reshape(n, F // 32, 2, 32)
+        want_gated = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(n, F)
+        gated = ops.gemm_swiglu(rows, w2.cuda(), F, 32)
+        torch.testing.assert_close(gated.cpu().double(), want_gated, rtol=2e-2, atol=2e-2)
+    # the same through the norm kernel: both ways agree to rounding
+    values = stream.cuda()
+    delta = ops.gemm_skinny(a.cuda(), w.cuda())
+    x = ops.add_rmsnorm(values, delta, weight.cuda(), eps, torch.empty((n, N), dtype=torch.bfloat16, device="cuda"))
+    torch.testing.assert_close(ops.gemm(x, w2.cuda()).cpu().double(), got2.cpu().double(), rtol=2e-2, atol=2e-2)
+    if ops._tc_fault is not None:
+        assert int(ops._tc_fault[0]) == 0, "a wait inside the kernel ran out"
+
+
+def test_a_sink_is_ignored_by_products_that_cannot_use_it(monkeypatch):
+    """More rows than the weight-streaming kernels take, or float32: the product returns its result and leaves
+    the stream alone; rows whose factor is pending are made whole for a product that cannot apply it."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(22)
+    K, N = 256, 128
+    w = _rand((K, N), torch.bfloat16, g, 0.05).cuda()
+    weight = torch.ones(N, device="cuda")
+    a = _rand((ops.SKINNY_MAX_ROWS + 9, K), torch.bfloat16, g).cuda()
+    values = torch.zeros((a.shape[0], N), device="cuda")
+    assert not ops.sink_usable(values, torch.bfloat16)
+    got = ops.gemm(a, w, sink=ops.ResidualSink(values, weight, 1e-6))
+    assert isinstance(got, torch.Tensor) and float(values.abs().max()) == 0.0
+    torch.testing.assert_close(got.cpu().double(), a.cpu().double() @ w.cpu().double(), rtol=2e-2, atol=2e-2)
+    few = a[:3].contiguous()
+    small = torch.zeros((3, N), device="cuda")
+    assert ops.sink_usable(small, torch.bfloat16) and not ops.sink_usable(small, torch.float32)
+    rows = ops.gemm(few, w, sink=ops.ResidualSink(small, weight, 1e-6))
+    assert isinstance(rows, ops.ScaledRows)
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)           # now every product is the library's
+    monkeypatch.setattr(ops, "STREAM_GEMM", False)
+    w2 = _rand((N, 72), torch.bfloat16, g, 0.05).cuda()
+    got = ops.gemm(rows, w2)
+    want = small.cpu().double()
+    want = want * math.sqrt(N) / (want.norm(dim=-1, keepdim=True) + 1e-6)
+    torch.testing.assert_close(got.cpu().double(), want @ w2.cpu().double(), rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("M,K,N", [(128, 64, 128), (300, 72, 200), (1000, 264, 1544), (2048, 1536, 2304),
                                    (513, 4096, 1536), (129, 40, 8), (640, 128, 448)])
 def test_tcgen05_gemm(M, K, N):

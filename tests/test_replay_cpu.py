@@ -84,3 +84,42 @@ def test_pages_are_used_again(tmp_path, ref_ops):
     runner = _replay(folder, page, steps, out_dir, max_tokens)
     assert runner.cache.groups[0].pool.num_pages == max_tokens // page
     _compare(cfg, steps, out_dir, seqs, plain, tol=2e-4)
+
+
+def test_norms_folded_into_the_products_change_nothing_but_rounding(tmp_path, ref_ops, monkeypatch):
+    """bfloat16 steps of few rows: the last product of a mixer or feed-forward adds to the residual stream itself
+    and the next product applies the norm's factor (``ResidualSink`` / ``ScaledRows``), here with the references
+    of those products.  The logits equal those of the same steps with the norm as an operation of its own to
+    bfloat16 rounding, and the folded path is the one that ran."""
+    from tiny_inference_server_b200.kernels import ops
+    cfg, page, folder, seqs, plain = _setup("A", tmp_path)
+    steps = trace_tools.trace_tail(seqs, tail=32)
+    max_tokens = trace_tools.max_live_tokens(steps, round_to=64)
+    made = []
+    whole = ops.ScaledRows.dense
+    monkeypatch.setattr(ops.ScaledRows, "dense", lambda self: made.append("dense") or whole(self))
+    sink_of = ops.ResidualSink.__init__
+
+    def counted(self, *a, **k):
+        made.append("sink")
+        sink_of(self, *a, **k)
+    monkeypatch.setattr(ops.ResidualSink, "__init__", counted)
+    got = {}
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "FUSED_NORM", fused)
+        made.clear()
+        out_dir = str(tmp_path / f"out_{fused}")
+        _replay(folder, page, steps, out_dir, max_tokens, dtype="bfloat16")
+        got[fused] = trace_tools.gather(steps, out_dir, cfg["vocab_size"])
+        layers = cfg["num_layers"]
+        if fused:
+            # per single-row step: the mixer of every layer and the feed-forward of every layer but the last
+            assert made.count("sink") >= 32 * (2 * layers - 1) and "dense" not in made
+        else:
+            assert not made
+    for rid, toks in seqs.items():
+        for p in range(len(toks)):
+            a, b, ref = got[True][rid][p], got[False][rid][p], plain[rid]["main"][p].numpy()
+            scale = np.abs(ref).max()
+            assert np.abs(a - b).max() < 0.05 * scale + 0.05, f"{rid} at {p}: the two ways differ by {np.abs(a - b).max()}"
+            assert np.abs(a - ref).max() < 0.08 * scale + 0.08, f"{rid} at {p}: {np.abs(a - ref).max()} from the plain model"

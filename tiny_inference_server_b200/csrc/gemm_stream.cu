@@ -12,12 +12,17 @@
 // multiplies (mma.sync m16n8k16, x from shared memory by ldmatrix, W by ldmatrix.trans through the swizzle).
 // Shares of more than 512 rows of K are walked in rounds of eight boxes.
 // Every wait on an mbarrier is bounded; one that runs out sets the fault word.
+// The epilogues are those of gemm_skinny.cu, the residual epilogue and the norm's factor per row among them.
 #include "tc_common.cuh"
+#include "cluster_reduce.cuh"
 #include <cooperative_groups.h>
 
 namespace {
 
 using namespace tc;
+using cluster_reduce::EPI_STORE;
+using cluster_reduce::EPI_SWIGLU;
+using cluster_reduce::EPI_RESIDUAL;
 
 constexpr int BN = 64;            // columns of a strip
 constexpr int BK = 64;            // rows of K per box
@@ -26,16 +31,12 @@ constexpr int BOX_ELEMS = BK * BN;
 constexpr int BOX_BYTES = BOX_ELEMS * 2;
 constexpr int MAX_BOXES = 8;      // boxes a CTA keeps in shared memory (a round)
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
-
 struct StreamParams {
     const bf16* x; int ldx;
-    bf16* out; int ldo;
-    int M, N, K;
+    int K;
     int kc;                       // rows of K per CTA of a cluster (a multiple of BK)
     int boxes;                    // boxes in shared memory: min(kc / BK, MAX_BOXES)
-    int epi;
-    int* fault;
+    cluster_reduce::Epilogue e;   // rows, columns, where the result goes, the fault word
 };
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
@@ -67,11 +68,13 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
     __shared__ __align__(8) unsigned long long bars[MAX_BOXES], empty[MAX_BOXES];
     __shared__ int abort_flag;
     __shared__ float pair[2][BN];
+    __shared__ float row_factor[MT * 16];
+    __shared__ __align__(8) unsigned long long recv_bar;
     constexpr int BOX_SM = BOX_ELEMS;                                 // elements of a box in shared memory
     const int xrow = p.kc + 8;                                        // padded rows: 16 bytes apart modulo 128
     bf16* w_sm = reinterpret_cast<bf16*>(base);                       // boxes x [64 k][WROW]
     bf16* xs = w_sm + (size_t)p.boxes * BOX_SM;                       // [MT*16][xrow]: this CTA's share of K
-    float* red = reinterpret_cast<float*>(base);                      // after the loop: [MT*16][BN] partial sums
+    float* recv = reinterpret_cast<float*>(xs + (size_t)MT * 16 * xrow);   // partial sums pushed by the cluster
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == NTH / 32;
@@ -86,15 +89,21 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
     if (tid == 0) {
         abort_flag = 0;
         for (int b = 0; b < MAX_BOXES; ++b) { mbar_init(&bars[b], 1); mbar_init(&empty[b], NTH / 32); }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        cluster_reduce::init_barrier(&recv_bar, rank, ksplit, p.e.M);
     }
     __syncthreads();
+    cluster_reduce::cluster_arrive();        // waited for after the loop: by then every CTA's barrier is ready
 
-    float acc[MT][2][4];
+    constexpr int CHAINS = MT == 1 ? BK / 16 : 2;          // independent chains of accumulators
+    float acc[MT][2][4], accs[CHAINS - 1][MT][2][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) { acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f; }
+        for (int j = 0; j < 2; ++j) {
+            acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < CHAINS - 1; ++ch) accs[ch][m][j][0] = accs[ch][m][j][1] = accs[ch][m][j][2] = accs[ch][m][j][3] = 0.f;
+        }
 
     if (producer) {
         // weights depend on nothing: no wait for the kernel before.  Box `it` goes to slot it % boxes, once
@@ -103,7 +112,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
         for (int it = 0; it < nkt; ++it) {
             const int b = it % p.boxes;
             if (it >= p.boxes) {
-                if (alive) alive = mbar_wait(&empty[b], (unsigned)(((it / p.boxes) - 1) & 1), &abort_flag, p.fault, 7);
+                if (alive) alive = mbar_wait(&empty[b], (unsigned)(((it / p.boxes) - 1) & 1), &abort_flag, p.e.fault, 7);
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
             if (lane == 0) {
@@ -120,10 +129,12 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
         for (int i = tid; i < MT * 16 * per_row; i += NTH) {
             const int r = i / per_row, c = (i - r * per_row) * 8;
             const int k = k_begin + c;
-            const bool ok = r < p.M && k < k_end;
+            const bool ok = r < p.e.M && k < k_end;
             cp16(xs + (size_t)r * xrow + c, ok ? p.x + (size_t)r * p.ldx + k : p.x, ok ? 16 : 0);
         }
         asm volatile("cp.async.commit_group;\n" ::);
+        // the norm's factor of each row, from the partial sums the kernel before left
+        cluster_reduce::load_row_factors(p.e, row_factor, warp, lane);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     asm volatile("bar.sync 1, 128;\n" ::: "memory");          // xs is visible to every consumer warp
@@ -135,21 +146,34 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
     bool alive = true;
     for (int it = 0; it < nkt; ++it) {
         const int b = it % p.boxes;
-        if (alive) alive = mbar_wait(&bars[b], (unsigned)((it / p.boxes) & 1), &abort_flag, p.fault, 6);
+        if (alive) alive = mbar_wait(&bars[b], (unsigned)((it / p.boxes) & 1), &abort_flag, p.e.fault, 6);
         if (!alive) continue;                      // a wait ran out: no more waits, the result is not to be used
         const unsigned box = w_base + (unsigned)b * (BOX_SM * 2);
+        // all fragments of the box first, then independent chains of accumulators (one per k16 step for up to
+        // 16 rows, two otherwise): the latency of a step is not paid once per step
+        unsigned bf[BK / 16][4];
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
-            unsigned bf[4];
             const int row = kk * 16 + b_row;
-            ldsm_x4_t(bf, box + row * 128 + ((b_chunk ^ (row & 7)) << 4));
+            ldsm_x4_t(bf[kk], box + row * 128 + ((b_chunk ^ (row & 7)) << 4));
+        }
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                unsigned a[4];
-                ldsm_x4(a, xs + (size_t)(m * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * xrow + it * BK + kk * 16 +
-                               ((lane >> 4) << 3));
-                mma16816(acc[m][0], a, bf[0], bf[1]);
-                mma16816(acc[m][1], a, bf[2], bf[3]);
+        for (int m = 0; m < MT; ++m) {
+            unsigned a[BK / 16][4];
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+                ldsm_x4(a[kk], xs + (size_t)(m * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * xrow + it * BK + kk * 16 +
+                                   ((lane >> 4) << 3));
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+                const int ch = kk % CHAINS;
+                if (ch == 0) {
+                    mma16816(acc[m][0], a[kk], bf[kk][0], bf[kk][1]);
+                    mma16816(acc[m][1], a[kk], bf[kk][2], bf[kk][3]);
+                } else {
+                    mma16816(accs[ch - 1][m][0], a[kk], bf[kk][0], bf[kk][1]);
+                    mma16816(accs[ch - 1][m][1], a[kk], bf[kk][2], bf[kk][3]);
+                }
             }
         }
         if (nkt > p.boxes) {                       // the slot is taken again a round later
@@ -157,48 +181,19 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
             if (lane == 0) mbar_arrive(&empty[b]);
         }
     }
-    }   // consumers
-    __syncthreads();                    // all warps are done with the staging memory
-
-    // partial sums of this CTA into shared memory
-    const int g = lane >> 2, t = lane & 3;
-    if (!producer)
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int col = warp * 16 + j * 8 + 2 * t;
-            red[(m * 16 + g) * BN + col] = acc[m][j][0];
-            red[(m * 16 + g) * BN + col + 1] = acc[m][j][1];
-            red[(m * 16 + g + 8) * BN + col] = acc[m][j][2];
-            red[(m * 16 + g + 8) * BN + col + 1] = acc[m][j][3];
-        }
-    cluster.sync();
-
-    // rank r adds up rows r, r + ksplit, ... over all CTAs of the cluster and writes them;
-    // two rows at a time (threads 0-63 and 64-127), one column per thread
-    const int half = (tid >> 6) & 1, col = tid & 63;
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int ch = 0; ch < CHAINS - 1; ++ch) acc[m][j][i] += accs[ch][m][j][i];
+    }   // consumers
+    cluster_reduce::cluster_wait();         // every CTA of the cluster has initialised its barrier
     if (!producer)
-    for (int row0 = (int)rank; row0 < p.M; row0 += 2 * (int)ksplit) {      // the same trips for every consumer thread
-        const int row = row0 + half * (int)ksplit;
-        const bool valid = row < p.M;
-        float sum = 0.f;
-        if (valid)
-            for (unsigned r = 0; r < ksplit; ++r) sum += cluster.map_shared_rank(red, r)[row * BN + col];
-        if (p.epi == EPI_STORE) {
-            if (valid && n0 + col < p.N) p.out[(size_t)row * p.ldo + n0 + col] = __float2bfloat16_rn(sum);
-        } else {
-            // the strip is [32 gate | 32 up]: out column strip*32 + j = silu(gate_j) * up_j
-            pair[half][col] = sum;
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");
-            if (valid && col < 32) {
-                const float gt = pair[half][col], up = pair[half][col + 32];
-                p.out[(size_t)row * p.ldo + blockIdx.x * 32 + col] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
-            }
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        }
-    }
-    cluster.sync();                     // nobody leaves while its shared memory may still be read
+        cluster_reduce::push_reduce_store<MT>(acc, p.e, recv, &recv_bar, pair, row_factor, rank, ksplit, blockIdx.x,
+                                              gridDim.x, tid);
 }
 
 }  // namespace
@@ -206,9 +201,11 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
 // x (M x K, row stride ldx), w (K x N, row stride ldw), out (M x N, or M x N/2 for the SwiGLU epilogue of
 // [32 gate | 32 up] column blocks; row stride ldo): bfloat16.  ksplit: CTAs per strip (1, 2, 4 or 8).
 // Refuses what the TMA engine cannot address: K, N and the strides must be multiples of 8 elements and
-// the pointers 16-byte aligned.
-TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
-                            int ksplit, int epi, int* fault, cudaStream_t stream) {
+// the pointers 16-byte aligned.  in_ss .. out_ss: as in tis_gemm_skinny_fused.
+TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
+                                  int ksplit, int epi, const float* in_ss, int in_parts, float in_eps, int in_width,
+                                  float* res, int ldr, const float* norm_w, float* out_ss, int* fault,
+                                  cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return TIS_OK;
     if (M > 64) {
         tis_set_error("gemm_stream: %d rows; this kernel takes at most 64", M);
@@ -224,8 +221,19 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
         tis_set_error("gemm_stream: ksplit %d must be 1, 2, 4 or 8", ksplit);
         return TIS_BAD_SIZE;
     }
-    if (epi != EPI_STORE && epi != EPI_SWIGLU) {
+    if (epi < EPI_STORE || epi > EPI_RESIDUAL) {
         tis_set_error("gemm_stream: unknown epilogue %d", epi);
+        return TIS_BAD_SIZE;
+    }
+    if (epi == EPI_RESIDUAL && (res == nullptr || norm_w == nullptr || out_ss == nullptr || ldr % 2 || ldo % 2 ||
+                                (reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(norm_w)) % 8 ||
+                                reinterpret_cast<uintptr_t>(out) % 4)) {
+        tis_set_error("gemm_stream: the residual epilogue needs the stream, the norm's weight and room for the partial "
+                      "sums, even row strides (%d, %d) and aligned pointers", ldr, ldo);
+        return TIS_BAD_SIZE;
+    }
+    if (in_ss != nullptr && (in_parts <= 0 || in_width <= 0)) {
+        tis_set_error("gemm_stream: %d partial sums a row over a width of %d", in_parts, in_width);
         return TIS_BAD_SIZE;
     }
     if (epi == EPI_SWIGLU && N % 64) {
@@ -235,17 +243,18 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
     CUtensorMap wm;
     if (!tensor_map(w, N, K, ldw, BK, true, &wm)) return TIS_CUDA_ERROR;
     StreamParams p;
-    p.x = (const bf16*)x; p.ldx = ldx; p.out = (bf16*)out; p.ldo = ldo;
-    p.M = M; p.N = N; p.K = K; p.epi = epi; p.fault = fault;
+    p.x = (const bf16*)x; p.ldx = ldx; p.K = K;
+    p.e.out = (bf16*)out; p.e.ldo = ldo; p.e.M = M; p.e.N = N; p.e.epi = epi; p.e.fault = fault;
+    p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_eps = in_eps; p.e.in_sqrt_width = sqrtf((float)(in_width > 0 ? in_width : 1));
+    p.e.res = res; p.e.ldr = ldr; p.e.norm_w = norm_w; p.e.out_ss = out_ss;
     p.kc = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
     const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
     const int tiles = p.kc / BK;
     p.boxes = tiles < MAX_BOXES ? tiles : MAX_BOXES;
     const size_t stage = (size_t)p.boxes * BOX_BYTES + (size_t)mt * 16 * (p.kc + 8) * sizeof(bf16);
-    const size_t redb = (size_t)mt * 16 * BN * sizeof(float);
-    const size_t smem = (stage > redb ? stage : redb) + 1024;        // room to align the boxes
-    if (smem > 200 * 1024) {
-        tis_set_error("gemm_stream: %d rows x %d of K per CTA need %zu bytes of shared memory (limit 200 KB)", M, p.kc, smem);
+    const size_t smem = stage + cluster_reduce::recv_floats(mt * 16, ksplit) * sizeof(float) + 1024;   // + room to align the boxes
+    if (smem > 224 * 1024) {
+        tis_set_error("gemm_stream: %d rows x %d of K per CTA need %zu bytes of shared memory (limit 224 KB)", M, p.kc, smem);
         return TIS_BAD_SIZE;
     }
 
@@ -266,9 +275,9 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
     cudaError_t e;
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(gemm_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(gemm_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(gemm_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(gemm_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        cudaFuncSetAttribute(gemm_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        cudaFuncSetAttribute(gemm_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         configured = true;
     }
     if (mt == 1) e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<1>, wm, p);
@@ -279,4 +288,14 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
         return TIS_CUDA_ERROR;
     }
     return tis_check_launch("gemm_stream");
+}
+
+TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
+                            int ksplit, int epi, int* fault, cudaStream_t stream) {
+    if (epi == EPI_RESIDUAL) {
+        tis_set_error("gemm_stream: the residual epilogue goes through tis_gemm_stream_fused");
+        return TIS_BAD_SIZE;
+    }
+    return tis_gemm_stream_fused(x, ldx, w, ldw, out, ldo, M, N, K, ksplit, epi, nullptr, 0, 0.f, 0, nullptr, 0, nullptr,
+                                 nullptr, fault, stream);
 }

@@ -199,6 +199,38 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
 }
 
 // ----------------------------------------------------------------------------------
+// Rows that still lack their norm's factor (the stream times the norm's weight, and partial sums of squares
+// of the stream, as the residual epilogue of the weight-streaming products leaves them), made whole:
+// out[r] = rows[r] * sqrt(width) / (sqrt(sum of parts[r]) + eps).  For readers that cannot apply the
+// factor themselves.
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(const bf16* __restrict__ rows, int ld, const float* __restrict__ parts, int n_parts, float eps,
+                  bf16* __restrict__ out, int ldo, int d) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n_parts; i += blockDim.x) s += parts[(size_t)r * n_parts + i];
+    s = block_sum(s, red);
+    const float f = sqrtf((float)d) / (sqrtf(s) + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        out[(size_t)r * ldo + i] = __float2bfloat16_rn(__bfloat162float(rows[(size_t)r * ld + i]) * f);
+}
+
+TIS_API int tis_scale_rows(const void* rows, int ld, const float* parts, int n_parts, float eps, void* out, int ldo,
+                           int n, int d, cudaStream_t stream) {
+    if (n <= 0 || d <= 0) return TIS_OK;
+    if (n_parts <= 0) {
+        tis_set_error("scale_rows: %d partial sums a row", n_parts);
+        return TIS_BAD_SIZE;
+    }
+    tis_launch(scale_rows_kernel, dim3(n), dim3(256), 0, stream, (const bf16*)rows, ld, parts, n_parts, eps, (bf16*)out,
+               ldo, d);
+    return tis_check_launch("scale_rows");
+}
+
+// ----------------------------------------------------------------------------------
 // rotary position encoding of q and k, and the write of k, v into the row's page.
 //
 // qkv row layout: [H*hd queries | KVH*hd keys | KVH*hd values] (keys before values, as

@@ -112,7 +112,55 @@ SKINNY_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SKINNY_SWIGLU_MAX_ROWS", "16"))
 #: batch 24 2.022 -> 2.012 ms, batch 32 2.135 -> 2.119, batch 64 3.052 -> 3.078, so it is used up to 32 rows.
 #: TIS_SWAP_SWIGLU_MAX_ROWS overrides (0: never).
 SWAP_SWIGLU_MAX_ROWS = int(os.environ.get("TIS_SWAP_SWIGLU_MAX_ROWS", "32"))
-EPI_STORE, EPI_SWIGLU = 0, 1
+EPI_STORE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
+#: the norm between two weight-streaming products is folded into them (``ResidualSink`` / ``ScaledRows``);
+#: TIS_FUSED_NORM=0 keeps the norm kernel
+FUSED_NORM = os.environ.get("TIS_FUSED_NORM", "1") != "0"
+
+
+class ResidualSink:
+    """Where a product adds its result itself: the float32 residual stream ``values`` (n, d); it then also
+    leaves the stream times ``weight`` (the weight of the norm that reads the stream next) and partial sums of
+    squares, so that the norm's factor ``sqrt(d) / (||row|| + eps)`` can be applied after the next product
+    instead of before it.  ``norm`` is whoever made the sink (the reader checks it is the same norm)."""
+
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, eps: float, norm=None):
+        self.values, self.weight, self.eps, self.norm = values, weight, float(eps), norm
+
+
+class ScaledRows:
+    """Rows of a norm's output that still lack the factor of their row: ``rows`` (n, d) bfloat16 = stream *
+    norm weight, ``parts`` (n, T) float32 = partial sums of squares of the stream.  Row r of the norm's
+    output is ``rows[r] * sqrt(d) / (sqrt(parts[r].sum()) + eps)``; a weight-streaming product applies the
+    factor to its own result (``gemm`` and ``gemm_swiglu`` take these rows), ``dense()`` makes the rows whole."""
+
+    def __init__(self, rows: torch.Tensor, parts: torch.Tensor, eps: float, norm=None):
+        self.rows, self.parts, self.eps, self.norm = rows, parts, float(eps), norm
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    def dense(self) -> torch.Tensor:
+        lib = library()
+        n, d = self.rows.shape
+        out = torch.empty_like(self.rows)
+        calls["scale_rows"] += 1
+        _check(lib.tis_scale_rows(_p(self.rows), self.rows.stride(0), _p(self.parts), self.parts.shape[1], _f(self.eps),
+                                  _p(out), out.stride(0), n, d, _stream()), lib)
+        return out
+
+
+def sink_usable(values: torch.Tensor, dtype: torch.dtype) -> bool:
+    """Whether a step of these rows can fold its norms into the products around them: bfloat16 products of
+    few enough rows that they all go to the weight-streaming kernels."""
+    n, d = values.shape
+    return (FUSED_NORM and dtype == torch.bfloat16 and 0 < n <= SKINNY_MAX_ROWS and d % 8 == 0
+            and values.stride(1) == 1 and values.stride(0) % 2 == 0)
 
 
 def _skinny_ok(a: torch.Tensor, w: torch.Tensor, max_rows: Optional[int] = None) -> bool:
@@ -188,41 +236,84 @@ def _stream_fits(n: int, k: int, ksplit: int) -> bool:
     a round of weight boxes fit the TMA-fed kernel's shared memory."""
     kc = -(-(-(-k // ksplit)) // 64) * 64
     rows = 16 if n <= 16 else (32 if n <= 32 else 64)
-    return min(kc // 64, 8) * 8192 + rows * (kc + 8) * 2 + 1024 <= 200 * 1024
+    received = ksplit * -(-rows // ksplit) * 64 * 4          # partial sums pushed by the cluster
+    return min(kc // 64, 8) * 8192 + rows * (kc + 8) * 2 + received + 1024 <= 224 * 1024
 
 
-def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
-                ksplit: Optional[int] = None) -> torch.Tensor:
+def _fused_args(scaled: Optional[ScaledRows], sink: Optional[ResidualSink], n: int, cols: int, device):
+    """The arguments of the fused entry points after (ksplit, epi): the partial sums of the rows, and the
+    sink with the tensors it fills."""
+    result = None
+    if scaled is not None:
+        head = (_p(scaled.parts), scaled.parts.shape[1], _f(scaled.eps), scaled.rows.shape[1])
+    else:
+        head = (None, 0, _f(0.0), 0)
+    if sink is not None:
+        parts = torch.empty((n, -(-cols // 64)), dtype=torch.float32, device=device)
+        rows = torch.empty((n, cols), dtype=torch.bfloat16, device=device)
+        result = ScaledRows(rows, parts, sink.eps, sink.norm)
+        tail = (_p(sink.values), sink.values.stride(0), _p(sink.weight), _p(parts))
+    else:
+        tail = (None, 0, None, None)
+    return head, tail, result
+
+
+def _sink_fits(sink: Optional[ResidualSink], n: int, cols: int, out) -> bool:
+    return sink is None or (out is None and tuple(sink.values.shape) == (n, cols) and sink.weight.shape[0] == cols
+                            and sink.weight.dtype == torch.float32 and sink.values.dtype == torch.float32)
+
+
+def gemm_stream(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None):
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by the TMA-fed weight-streaming kernel; with ``swiglu``
-    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2).  ``a`` may be ``ScaledRows``;
+    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``."""
     lib = library()
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.rows
     n, k = a.shape
     cols = w.shape[1]
-    if out is None:
+    if not _sink_fits(sink, n, cols, out) or (sink is not None and swiglu):
+        raise KernelError("gemm_stream: the sink does not fit the product")
+    head, tail, result = _fused_args(scaled, sink, n, cols, a.device)
+    if sink is not None:
+        out = result.rows
+    elif out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
     calls["gemm_stream"] += 1
-    _check(lib.tis_gemm_stream(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
-                               ksplit or _ksplit(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()),
-                               _stream()), lib)
-    return out
+    epi = EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+    _check(lib.tis_gemm_stream_fused(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                                     ksplit or _ksplit(cols, k), epi, *head, *tail, _p(tc_fault()), _stream()), lib)
+    return result if sink is not None else out
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
-                ksplit: Optional[int] = None) -> torch.Tensor:
+def gemm_skinny(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                ksplit: Optional[int] = None, sink: Optional[ResidualSink] = None):
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 by a weight-streaming kernel; with ``swiglu``
-    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
-    if (_stream_pays(a.shape[0], a.shape[1], w.shape[1], ksplit) and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-            and _stream_fits(a.shape[0], a.shape[1], ksplit or _ksplit(w.shape[1], a.shape[1]))):
-        return gemm_stream(a, w, out, swiglu, ksplit)
+    the columns of ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2).  ``a`` may be ``ScaledRows``;
+    with ``sink`` the result is added to the residual stream and comes back as ``ScaledRows``."""
+    rows = a.rows if isinstance(a, ScaledRows) else a
+    if (_stream_pays(rows.shape[0], rows.shape[1], w.shape[1], ksplit) and rows.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and _stream_fits(rows.shape[0], rows.shape[1], ksplit or _ksplit(w.shape[1], rows.shape[1]))):
+        return gemm_stream(a, w, out, swiglu, ksplit, sink)
     lib = library()
+    scaled = a if isinstance(a, ScaledRows) else None
+    a = rows
     n, k = a.shape
     cols = w.shape[1]
-    if out is None:
+    if not _sink_fits(sink, n, cols, out) or (sink is not None and swiglu):
+        raise KernelError("gemm_skinny: the sink does not fit the product")
+    head, tail, result = _fused_args(scaled, sink, n, cols, a.device)
+    if sink is not None:
+        out = result.rows
+    elif out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
     calls["gemm_skinny"] += 1
-    _check(lib.tis_gemm_skinny(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
-                               ksplit or _ksplit(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _stream()), lib)
-    return out
+    epi = EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+    _check(lib.tis_gemm_skinny_fused(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                                     ksplit or _ksplit(cols, k), epi, *head, *tail, _p(tc_fault()), _stream()), lib)
+    return result if sink is not None else out
 
 
 #: The tcgen05 kernel of this library (csrc/gemm_tc.cu) against the library product, measured on a
@@ -303,15 +394,26 @@ def _library_gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
     return out
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, sink: Optional[ResidualSink] = None):
     """``a (n, K) @ w (K, N)`` in the dtype of ``a``; float32 means true float32.  Few bfloat16
     rows go to the weight-streaming kernel of this library, many to its tcgen05 kernel,
-    everything else to the library product."""
+    everything else to the library product.
+
+    ``a`` may be ``ScaledRows``.  With ``sink``, a product that goes to a weight-streaming kernel adds its
+    result to the residual stream itself and returns ``ScaledRows`` for the norm that follows; any other
+    product ignores the sink and returns its result, which the caller adds as before."""
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.rows
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
     if _skinny_ok(a, w) or (_skinny_ok(a, w, STREAM_MAX_ROWS) and _stream_pays(a.shape[0], a.shape[1], w.shape[1])
                             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
-        return gemm_skinny(a, w, out)
+        if sink is not None and not _sink_fits(sink, a.shape[0], w.shape[1], out):
+            sink = None
+        return gemm_skinny(scaled if scaled is not None else a, w, out, sink=sink)
+    if scaled is not None:
+        a = scaled.dense()
     if _tc_ok(a, w, TC_PLAIN_MIN_ROWS) and (out is None or (out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)):
         return gemm_tc(a, w, out)
     direct = _library_gemm(a, w, out, False)
@@ -322,12 +424,17 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -
     return torch.mm(a, w, out=out)
 
 
-def gemm_swiglu(a: torch.Tensor, w_gu: torch.Tensor, hidden: int, block: int) -> torch.Tensor:
+def gemm_swiglu(a, w_gu: torch.Tensor, hidden: int, block: int) -> torch.Tensor:
     """``swiglu(a @ w_gu)``: (n, hidden).  ``w_gu`` (K, 2*hidden) holds gate and up columns in
     alternating blocks of ``block``.  Few bfloat16 rows with block 32: one kernel with the
-    gating in its epilogue; else the product and the gating kernel."""
+    gating in its epilogue; else the product and the gating kernel.  ``a`` may be ``ScaledRows``."""
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.rows
     if block == 32 and _skinny_ok(a, w_gu, SKINNY_SWIGLU_MAX_ROWS):
-        return gemm_skinny(a, w_gu, swiglu=True)
+        return gemm_skinny(scaled if scaled is not None else a, w_gu, swiglu=True)
+    if scaled is not None:
+        a = scaled.dense()
     if (block == 32 and _skinny_ok(a, w_gu, SWAP_SWIGLU_MAX_ROWS) and w_gu.shape[1] % 64 == 0
             and a.data_ptr() % 16 == 0 and w_gu.data_ptr() % 16 == 0):
         return gemm_swap(a, w_gu, swiglu=True)

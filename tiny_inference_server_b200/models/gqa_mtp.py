@@ -138,8 +138,9 @@ class GqaMtpModel(Model):
         """Trunk over the step's rows, then (``aux``) the MTP heads in order, each fed by the
         stage before it (server.py:328-359 upstream); logits only at the wanted rows."""
         stream = ResidualStream(self.embedding.forward(step.tokens))
-        for e in self.entries[: self.n_trunk_entries]:
-            e.block.forward(stream, step, e.binding)
+        trunk = self.entries[: self.n_trunk_entries]
+        for i, e in enumerate(trunk):
+            e.block.forward(stream, step, e.binding, following=trunk[i + 1].block if i + 1 < len(trunk) else None)
         h = stream.normed(self.rms_out)
         out = StepOutput(main=self.lm_head.forward(h.index_select(0, want_rows)))
         if aux:

@@ -25,6 +25,8 @@ class GqaAttention(Mixer):
     """
 
     graph_safe = True
+    accepts_scaled_rows = True
+    fuses_residual = True
 
     def __init__(self, width: int, num_heads: int, kv_heads: int, head_dim: int, position,
                  window: Optional[int] = None, lag: int = 0, prefix: str = "",
@@ -78,7 +80,7 @@ class GqaAttention(Mixer):
         self.w_q = self.w_qkv[:, : self.num_heads * self.head_dim]
         self.w_o = tensors[self.prefix + self.names["o"]].to(device=ctx.device, dtype=ctx.dtype).contiguous()
 
-    def forward(self, x: torch.Tensor, step, binding: LayerBinding) -> torch.Tensor:
+    def forward(self, x, step, binding: LayerBinding, residual=None):
         n = x.shape[0]
         hq = self.num_heads * self.head_dim
         g = binding.kv_group
@@ -92,13 +94,13 @@ class GqaAttention(Mixer):
             ops.paged_attention(qkv, out, binding.kv_plane, table, step.positions, step.row_slot, self.num_heads,
                                 self.kv_heads, self.head_dim, page_size, self.window, step.fault, step,
                                 rotary=rotary, write_kv=binding.kv_write)
-            return ops.gemm(out, self.w_o)
+            return ops.gemm(out, self.w_o, sink=residual)
         self.position.encode_and_store(qkv, step, num_heads=self.num_heads, kv_heads=self.kv_heads,
                                        head_dim=self.head_dim, plane=binding.kv_plane if binding.kv_write else None,
                                        block_table=table, page_size=page_size)
         ops.paged_attention(qkv, out, binding.kv_plane, table, step.positions, step.row_slot, self.num_heads,
                             self.kv_heads, self.head_dim, page_size, self.window, step.fault, step)
-        return ops.gemm(out, self.w_o)
+        return ops.gemm(out, self.w_o, sink=residual)
 
 
 register_part("mixer", "gqa", GqaAttention)

@@ -160,11 +160,19 @@ class Part:
 
 class Norm(Part):
     """``forward(x) -> y`` on the 32-bit residual stream; ``add_norm`` first adds a
-    pending update to the stream in place, then normalises it."""
+    pending update to the stream in place, then normalises it.
+
+    ``sink(values)``: a norm whose factor per row is a function of the row's sum of squares may return
+    a ``kernels.ops.ResidualSink`` for the stream ``values``: the part before the norm then adds its
+    update to the stream inside its last product and the part after applies the factor after its first
+    product, so that the norm needs no kernel.  None (the default): the norm runs as a kernel of its own."""
 
     @classmethod
     def from_config(cls, cfg, prefix: str):
         raise NotImplementedError
+
+    def sink(self, values: torch.Tensor):
+        return None
 
     def forward(self, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
@@ -212,6 +220,11 @@ class Mixer(Part):
     """
 
     graph_safe = False
+    #: ``x`` may come as ``kernels.ops.ScaledRows`` (a norm's output that still lacks the factor of each row)
+    accepts_scaled_rows = False
+    #: ``forward`` takes ``residual=`` (a ``kernels.ops.ResidualSink`` or None); given one, it may add its update
+    #: to the stream itself and return the ``ScaledRows`` its last product made instead of the update
+    fuses_residual = False
 
     def kv_spec(self) -> Optional[KVSpec]:
         return None
@@ -235,7 +248,11 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """``forward(x, step) -> (n, width)``, row by row: no cache, no state."""
+    """``forward(x, step) -> (n, width)``, row by row: no cache, no state.
+    ``accepts_scaled_rows`` and ``fuses_residual``: as for a mixer."""
+
+    accepts_scaled_rows = False
+    fuses_residual = False
 
     @classmethod
     def from_config(cls, cfg, prefix: str, layer_index: int):

@@ -18,6 +18,9 @@ class SwiGLU(FeedForward):
     else all gates, then all ups), so that one 64-column strip of the product holds both
     factors of 32 outputs and the gating can be the product's epilogue."""
 
+    accepts_scaled_rows = True
+    fuses_residual = True
+
     def __init__(self, width: int, hidden: int, prefix: str = "", names: Optional[Dict[str, str]] = None):
         super().__init__(prefix)
         self.width = width
@@ -49,9 +52,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = both.reshape(self.width, 2 * self.hidden).to(device=ctx.device, dtype=ctx.dtype).contiguous()
         self.w_down = tensors[self.prefix + self.names["down"]].to(device=ctx.device, dtype=ctx.dtype).contiguous()
 
-    def forward(self, x: torch.Tensor, step=None) -> torch.Tensor:
+    def forward(self, x, step=None, residual=None):
         h = ops.gemm_swiglu(x, self.w_gate_up, self.hidden, self.block)
-        return ops.gemm(h, self.w_down)
+        return ops.gemm(h, self.w_down, sink=residual)
 
 
 register_part("ffn", "swiglu", SwiGLU)

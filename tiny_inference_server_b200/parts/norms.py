@@ -41,5 +41,9 @@ class RMSNormL2(Norm):
     def forward(self, residual: torch.Tensor) -> torch.Tensor:
         return self.add_norm(residual, None)
 
+    def sink(self, values: torch.Tensor):
+        # the factor of a row, sqrt(width) / (||row|| + eps), is what the products apply themselves
+        return ops.ResidualSink(values, self.scale, self.eps, norm=self)
+
 
 register_part("norm", "rmsnorm_l2", RMSNormL2)
