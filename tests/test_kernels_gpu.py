@@ -763,6 +763,9 @@ def test_attention_splits_plan():
         per, splits = plan_splits(tiles, kvh, max_kv, keys_mode)
         assert per % 64 == 0 and per >= 64 and splits >= 1
         assert per * splits >= max_kv and per * (splits - 1) < max_kv
+    # clusters of 16 only while the CTAs of the decode kernel are all resident (two to an SM)
+    assert plan_splits(1, 3, 4096, True)[1] == 16 and plan_splits(4, 3, 4096, True)[1] == 16
+    assert plan_splits(8, 3, 4096, True)[1] == 8 and plan_splits(64, 3, 4096, True)[1] <= 8
 
 
 @pytest.mark.parametrize("H,KVH,hd,page,window", [(12, 3, 128, 16, None), (4, 4, 64, 8, None), (6, 2, 32, 16, None),

@@ -27,6 +27,7 @@
 // the engine plans at most eight) a CTA writes a normalised partial output and its log2-sum
 // to scratch memory and `attn_merge_kernel` merges them.
 #include "common.cuh"
+#include "cluster_reduce.cuh"
 #include <cooperative_groups.h>
 #include <cstdlib>
 
@@ -99,6 +100,16 @@ __device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned pari
     for (int spin = 0; spin < MBAR_SPINS; ++spin) {
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (done) return;
+    }
+    atomicExch(fault, 4);
+}
+// the same for a barrier that CTAs of the cluster complete (acquire at cluster scope)
+__device__ __forceinline__ void mbar_wait_cluster(unsigned long long* bar, unsigned parity, int* fault) {
+    unsigned done = 0;
+    for (int spin = 0; spin < MBAR_SPINS; ++spin) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+                     "selp.u32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
         if (done) return;
     }
     atomicExch(fault, 4);
@@ -788,7 +799,7 @@ attn_decode_kernel(const AttnParams p) {
     constexpr int STAGE_ELEMS = 2 * KT * RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int sh_first;
-    __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES];
+    __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES], merge_bar;
     const int STAGES = p.stages;
 
     pdl_launch_dependents();
@@ -800,10 +811,22 @@ attn_decode_kernel(const AttnParams p) {
     const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
     const int G = p.G;
 
+    // The merge of the splits (see the end of the kernel): output dims are owned in blocks of eight, block d by
+    // rank d % splits.  Every CTA of the cluster pushes its partial result of a block to the block's owner; the
+    // owner expects, from each split and for each of the tile's rows * G query rows, its blocks and the row's
+    // maximum and sum.
+    const unsigned ns = (unsigned)p.num_splits, rank = (unsigned)split;
+    const int pairs = rows * G;
+    const int own_blocks = (int)rank < DTILES ? (DTILES - 1 - (int)rank) / (int)ns + 1 : 0;
+    const int OW = ((DTILES + (int)ns - 1) / (int)ns) * 8 + 4;       // floats a query row of a split takes at an owner
+    float* recv = reinterpret_cast<float*>(smem_raw + (size_t)STAGES * STAGE_ELEMS * sizeof(bf16));
     if (tid == 0) {
         for (int st = 0; st < STAGES; ++st) { mbar_init(&full[st], 32); mbar_init(&empty[st], NTHREADS / 32); }
+        mbar_init(&merge_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        mbar_arrive_expect_tx(&merge_bar, own_blocks ? (int)ns * pairs * (own_blocks * 8 + 2) * 4 : 0);
     }
+    cluster_reduce::cluster_arrive();        // waited for before the first push: by then every CTA's barrier is ready
     if (warp == 0) {
         const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
         const unsigned b0 = __ballot_sync(0xffffffffu, v0);
@@ -861,6 +884,7 @@ attn_decode_kernel(const AttnParams p) {
             load_tile_warp(stages + stg * STAGE_ELEMS, &full[stg], p, page, kvh, kt, range_lo, range_hi, lane);
             page = page_next;
         }
+        cluster_reduce::cluster_wait();
     } else {
         // FUSED: does this CTA's split hold the row's own position?  Then it writes the row's key and value.
         int own_pos = -1, own_page = -1;
@@ -1051,7 +1075,12 @@ attn_decode_kernel(const AttnParams p) {
             l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
             l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
         }
-        // every consumer warp is done with the staging area, which the partial results now take
+        // Merge.  First the four warps of this CTA, through the staging area (every tile has landed and been read):
+        // one partial result per query row.  Then over the splits by pushing (as the split-K sums of the
+        // weight-streaming products, cluster_reduce.cuh): output dims are owned in blocks of eight, block d by
+        // rank d % splits; every CTA sends its partial of a block to the owner (st.async, counted on the owner's
+        // mbarrier), the owner combines the partials of the splits from its own shared memory and writes the
+        // output.  No cluster barrier after the loop, no remote load, and a CTA leaves when it has what it owns.
         asm volatile("bar.sync 1, 128;\n" ::: "memory");
         constexpr int HDP = HD + 4;
         float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
@@ -1061,56 +1090,67 @@ attn_decode_kernel(const AttnParams p) {
         for (int i = 0; i < NR; ++i) {
             const int m = g_lane + 8 * i;
             if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
-            if (m_run[i] != -INFINITY) {
 #pragma unroll
-                for (int d = 0; d < DTILES; ++d)
-                    *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+            for (int d = 0; d < DTILES; ++d)
+                *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        cluster_reduce::cluster_wait();
+        const unsigned recv_base = cluster_reduce::shared_addr(recv), bar_base = cluster_reduce::shared_addr(&merge_bar);
+        constexpr int QUADS = HD / 4;                            // groups of four dims of a query row
+        for (int u = tid; u < pairs * QUADS; u += NTHREADS) {
+            const int m = u / QUADS, q = u - m * QUADS;
+            float mw[4], mt = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { mw[w] = mm[w * 16 + m]; mt = fmaxf(mt, mw[w]); }
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float lsum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - mt);
+                const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + m) * HDP + 4 * q);
+                lsum += ml[w * 16 + m] * f;
+                acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+            }
+            const int block = q >> 1;
+            const unsigned owner = (unsigned)block % ns;
+            const unsigned at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + (block / (int)ns) * 8 + (q & 1) * 4) * 4);
+            asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];\n"
+                         ::"r"(cluster_reduce::map_to_rank(at, owner)), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w),
+                           "r"(cluster_reduce::map_to_rank(bar_base, owner)) : "memory");
+            // the row's maximum and sum go to every rank that owns a block: quad q sends them to rank q
+            if (q < (int)ns && q < DTILES) {
+                const unsigned ml_at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + OW - 4) * 4);
+                asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];\n"
+                             ::"r"(cluster_reduce::map_to_rank(ml_at, (unsigned)q)), "f"(mt), "f"(lsum),
+                               "r"(cluster_reduce::map_to_rank(bar_base, (unsigned)q)) : "memory");
             }
         }
-        if (NR == 1 && t_lane == 0) { mm[warp * 16 + g_lane + 8] = -INFINITY; ml[warp * 16 + g_lane + 8] = 0.f; }
-    }
-
-    // one merge over the warps of all splits through distributed shared memory (as MODE_KEYS above)
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    if (!producer) {
-        constexpr int HDP = HD + 4;
-        float* mo = reinterpret_cast<float*>(smem_raw);
-        float* mm = mo + 4 * 16 * HDP;
-        float* ml = mm + 4 * 16;
-        const int ns = p.num_splits;
-        const int pairs = rows * G;
-        for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
-            const int m = idx / HD, d = idx - m * HD;
+        mbar_wait_cluster(&merge_bar, 0u, p.fault);              // bounded
+        const int own_dims = own_blocks * 8;
+        for (int idx = tid; idx < pairs * own_dims; idx += NTHREADS) {
+            const int m = idx / own_dims, c = idx - m * own_dims;
+            const int d = ((c >> 3) * (int)ns + (int)rank) * 8 + (c & 7);
             const int r = m / G, g = m - r * G;
+            const float* from = recv + m * OW;
+            const int step_sp = pairs * OW;
             float mt = -INFINITY;
-            for (int sp = 0; sp < ns; ++sp) {
-                const float* rm = cluster.map_shared_rank(mm, sp);
-#pragma unroll
-                for (int w = 0; w < 4; ++w) mt = fmaxf(mt, rm[w * 16 + m]);
-            }
+#pragma unroll 8
+            for (unsigned sp = 0; sp < ns; ++sp) mt = fmaxf(mt, from[sp * step_sp + OW - 4]);
             float acc = 0.f, lsum = 0.f;
             if (mt != -INFINITY) {
-                for (int sp = 0; sp < ns; ++sp) {
-                    const float* rm = cluster.map_shared_rank(mm, sp);
-                    const float* rl = cluster.map_shared_rank(ml, sp);
-                    const float* ro = cluster.map_shared_rank(mo, sp);
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const float mw = rm[w * 16 + m];
-                        if (mw == -INFINITY) continue;
-                        const float f = fast_exp2(mw - mt);
-                        lsum += rl[w * 16 + m] * f;
-                        acc += ro[(w * 16 + m) * HDP + d] * f;
-                    }
+#pragma unroll 8
+                for (unsigned sp = 0; sp < ns; ++sp) {
+                    const float msp = from[sp * step_sp + OW - 4];
+                    const float f = msp == -INFINITY ? 0.f : fast_exp2(msp - mt);
+                    lsum += from[sp * step_sp + OW - 3] * f;
+                    acc += from[sp * step_sp + c] * f;
                 }
             }
             p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
                 __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
         }
     }
-    cluster.sync();                      // nobody leaves while its shared memory may still be read
 }
 
 // out[row, head] = sum_s w_s * part_o[row, head, s],  w_s = 2^(lse_s - max) / sum, for the rows of one tile
@@ -1250,13 +1290,20 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
     // fit one CTA per SM and a split has tiles to fill (measured inside the decode step of the 0.9B model:
     // batch 1, 24 CTAs, six stages: 1.289 -> 1.235 ms a step); the kernel with a producer warp, whose copies
     // run ahead of the consumers, takes three wherever two CTAs of three stages fit an SM.
+    // the kernel with a producer warp also keeps, beside the stages, what the cluster pushes to it for the merge:
+    // from each split, for each query row of a tile, its output blocks, the row's maximum and sum
+    size_t recv_bytes = 0;
+    if (warp_specialised) {
+        const int pairs = max_tile_rows > 0 ? max_tile_rows * G : 16;
+        recv_bytes = (size_t)num_splits * pairs * (((HD / 8 + num_splits - 1) / num_splits) * 8 + 4) * sizeof(float);
+    }
     int stages = 2;
     if (mode == MODE_KEYS) {
         const int sms = sm_count;
         const long long ctas = (long long)num_tiles * KVH * num_splits;
         const int tiles_per_split = keys_per_split / KT;
         for (int cand = 3; cand <= MAX_STAGES; ++cand) {
-            const size_t need = smem_bytes(MODE_KEYS, cand);
+            const size_t need = warp_specialised ? (size_t)cand * STAGE_BYTES + recv_bytes : smem_bytes(MODE_KEYS, cand);
             if (need > 220 * 1024 || cand - 1 > tiles_per_split) break;
             // the kernel with a producer warp keeps three stages wherever two CTAs of them fit an SM
             const bool fits_twice = warp_specialised && cand == 3 && 2 * (need + 1024) <= 220 * 1024;
@@ -1265,7 +1312,11 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         }
     }
     p.stages = stages;
-    const size_t smem = smem_bytes(mode, stages);
+    const size_t smem = warp_specialised ? (size_t)stages * STAGE_BYTES + recv_bytes : smem_bytes(mode, stages);
+    if (smem > 220 * 1024) {
+        tis_set_error("attention: %d stages and the merge of %d splits need %zu bytes of shared memory", stages, num_splits, smem);
+        return TIS_BAD_SIZE;
+    }
     dim3 grid(num_tiles, KVH, num_splits);
     static bool configured = false;          // once per process (and before any stream capture)
     if (!configured) {

@@ -532,11 +532,13 @@ ATTN_RESIDENT_CTAS = 148 * 2
 #: cost of starting and finishing a CTA, and of merging one more split, in units of one 64-key tile
 ATTN_CTA_OVERHEAD_TILES = 8.0
 ATTN_MERGE_PER_SPLIT_TILES = 0.1
-#: most key splits of a decode tile (one cluster).  The kernel takes clusters of 16 (a size the device
-#: allows on request), and alone it gains from them at batch 1 (12.7 -> 10.3 us at context 4096), but inside
-#: the decode step nothing is left of that (1.235 -> 1.247 ms a step) and at batch 8 they cost (17.6 -> 28.4 us):
-#: the planner stays at the portable 8.  TIS_ATTN_MAX_SPLITS overrides.
-ATTN_MAX_SPLITS_KEYS = int(os.environ.get("TIS_ATTN_MAX_SPLITS", "8"))
+#: most key splits of a decode tile (one cluster): 16, a cluster size that the device allows on request, while
+#: the CTAs of the kernel with a producer warp are all resident (two to an SM); else the portable 8.  Measured
+#: inside the decode step of the 0.9B model at context 4096, 8 -> 16 splits: batch 1 1.003 -> 0.938 ms a step,
+#: batch 2 1.022 -> 0.977, batch 4 1.080 -> 1.051; at batch 8 (384 CTAs) 16 splits cost (17.6 -> 28.4 us a launch).
+#: TIS_ATTN_MAX_SPLITS overrides.
+ATTN_MAX_SPLITS_KEYS = int(os.environ.get("TIS_ATTN_MAX_SPLITS", "16"))
+ATTN_DECODE_RESIDENT_CTAS = 148 * 2
 
 
 def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, resident: int = ATTN_RESIDENT_CTAS,
@@ -565,6 +567,8 @@ def plan_splits(num_tiles: int, kv_heads: int, max_kv: int, mode_keys: bool, res
         per_tiles = (total_tiles + s - 1) // s
         if (total_tiles + per_tiles - 1) // per_tiles != s:
             continue
+        if s > 8 and (s != 16 or num_tiles * kv_heads * s > ATTN_DECODE_RESIDENT_CTAS):
+            continue                   # above the portable cluster size only 16, and only while all CTAs are resident
         # tiles with key counts spread evenly from lo_tiles to total_tiles
         work, ctas = 0.0, 0.0
         samples = min(num_tiles, 16)
