@@ -62,6 +62,7 @@ class StepContext:
         self.lag = lag
         self._stages = stages if stages is not None else {}
         self.decode_only = decode_only      # every request has exactly one row
+        self.want_identity = False          # the wanted rows are all rows of the step, in order (no gather needed)
         self.plans = plans if plans is not None else {}     # planner key -> what its ``bind`` returned
         self.scratch: Dict = {}             # buffers that kernels of this step may share
 
@@ -93,6 +94,7 @@ class StepLayout:
     max_position: int
     decode_only: bool
     min_position: int = 0
+    want_identity: bool = False      # by the shape of the step, the wanted rows are all rows in order
 
 
 def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
@@ -173,7 +175,8 @@ def layout_step(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seque
         max_pos = max(max_pos, max_position)
     flat = np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
     return StepLayout(flat, offsets, n, segments, lags, facts, len(want_rows), max_pos,
-                      all(s.rows == 1 for s in segments), int(positions[:n_real].min()) if n_real else 0)
+                      all(s.rows == 1 for s in segments), int(positions[:n_real].min()) if n_real else 0,
+                      want_identity=bool(want_all))
 
 
 def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Sequence[int], vocab_size: int,
@@ -218,7 +221,8 @@ def layout_decode(entries: Sequence[StepEntry], starts: Sequence[int], lags: Seq
     if max_position is not None:
         max_pos = max(max_pos, max_position)
     segments = [Segment(e.slot, i, 1, starts[i]) for i, e in enumerate(entries)]
-    return StepLayout(flat, offsets, n, segments, lags, facts, n, max_pos, True, min(starts) if n_real else 0)
+    return StepLayout(flat, offsets, n, segments, lags, facts, n, max_pos, True, min(starts) if n_real else 0,
+                      want_identity=True)
 
 
 def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[torch.Tensor],
@@ -240,6 +244,7 @@ def context_from_layout(lay: StepLayout, dev: torch.Tensor, block_tables: List[t
                       block_tables, page_sizes, fault, lay.max_position, stages=stages,
                       decode_only=lay.decode_only, plans=plans)
     ctx.min_position = lay.min_position
+    ctx.want_identity = lay.want_identity
     for lag in lay.lags:
         st = StepContext(lay.n, view("tokens"), view(f"pos{lag}"), view(f"slot{lag}"), view("last"), lay.segments,
                          block_tables, page_sizes, fault, max(0, lay.max_position - lag), trunk_slot=view("slots"),

@@ -142,12 +142,14 @@ class GqaMtpModel(Model):
         for i, e in enumerate(trunk):
             e.block.forward(stream, step, e.binding, following=trunk[i + 1].block if i + 1 < len(trunk) else None)
         h = stream.normed(self.rms_out)
-        out = StepOutput(main=self.lm_head.forward(h.index_select(0, want_rows)))
+        # a step whose shape says that every row is wanted (a decode step) needs no gather
+        pick = (lambda t: t) if getattr(step, "want_identity", False) else (lambda t: t.index_select(0, want_rows))
+        out = StepOutput(main=self.lm_head.forward(pick(h)))
         if aux:
             prev = h
             for i, head in enumerate(self.heads):
                 prev = head.forward(prev, self._pending[i], step, self.entries[self.n_trunk_entries + i])
-                out.aux.append(self.lm_head.forward(prev.index_select(0, want_rows)))
+                out.aux.append(self.lm_head.forward(pick(prev)))
                 out.aux_valid.append(step.stage(head.lag).row_slot.index_select(0, want_rows) >= 0)
         return out
 
