@@ -187,7 +187,7 @@ def test_skinny_gemm_with_swiglu_epilogue(n, K, F, kernel, monkeypatch):
         torch.testing.assert_close(ops.gemm_swiglu(a2.cuda(), w.cuda(), F, 32).cpu().double(), want2, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("kernel", ["boxes", "ring"])
+@pytest.mark.parametrize("kernel", ["boxes", "ring", "swapped"])
 @pytest.mark.parametrize("n", [1, 5, 8, 16, 33, 64])
 @pytest.mark.parametrize("K,N", [(1536, 1536), (4096, 1536), (200, 120), (72, 8), (1000, 1096)])
 def test_skinny_gemm_adds_to_the_stream_and_defers_the_norm(n, K, N, kernel, monkeypatch):
@@ -215,10 +215,12 @@ def test_skinny_gemm_adds_to_the_stream_and_defers_the_norm(n, K, N, kernel, mon
     w2 = _rand((N, 2 * F), torch.bfloat16, g, 0.05)
     want2 = normed @ w2.double()
     factor = math.sqrt(N) / (new_stream.norm(dim=-1, keepdim=True) + eps)
+    swapped = kernel == "swapped"               # the tcgen05 kernel with swapped operands has the same epilogues
+    product = ops.gemm_swap if swapped else ops.gemm_skinny
     for ksplit in (None, 1, 2, 4, 8):
         values = stream.cuda()
         sink = ops.ResidualSink(values, weight.cuda(), eps, norm="the norm")
-        rows = ops.gemm_skinny(a.cuda(), w.cuda(), ksplit=ksplit, sink=sink)
+        rows = product(a.cuda(), w.cuda(), ksplit=ksplit, sink=sink)
         assert isinstance(rows, ops.ScaledRows) and rows.norm == "the norm" and rows.parts.shape == (n, -(-N // 64))
         torch.testing.assert_close(values.cpu().double(), new_stream, rtol=1e-3, atol=2e-2)
         torch.testing.assert_close(rows.rows.cpu().double(), new_stream * weight.double(), rtol=1e-2, atol=2e-2)
@@ -226,12 +228,12 @@ def test_skinny_gemm_adds_to_the_stream_and_defers_the_norm(n, K, N, kernel, mon
         pad[:, :N] = values.cpu().double() ** 2
         torch.testing.assert_close(rows.parts.cpu().double(), pad.reshape(n, -1, 64).sum(-1), rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(rows.dense().cpu().double(), normed, rtol=2e-2, atol=2e-2)
-        got2 = ops.gemm(rows, w2.cuda())
+        got2 = ops.gemm_swap(rows, w2.cuda(), ksplit=ksplit) if swapped else ops.gemm(rows, w2.cuda())
         torch.testing.assert_close(got2.cpu().double(), want2, rtol=2e-2, atol=2e-2)
         # the gated product against the same product of the rows as they were rounded to bfloat16
         gu = ((rows.rows.cpu().double() * factor) @ w2.double()).reshape(n, F // 32, 2, 32)
         want_gated = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(n, F)
-        gated = ops.gemm_swiglu(rows, w2.cuda(), F, 32)
+        gated = ops.gemm_swap(rows, w2.cuda(), swiglu=True, ksplit=ksplit) if swapped else ops.gemm_swiglu(rows, w2.cuda(), F, 32)
         torch.testing.assert_close(gated.cpu().double(), want_gated, rtol=2e-2, atol=2e-2)
     # the same through the norm kernel: both ways agree to rounding
     values = stream.cuda()

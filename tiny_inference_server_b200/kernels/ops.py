@@ -170,6 +170,26 @@ def _skinny_ok(a: torch.Tensor, w: torch.Tensor, max_rows: Optional[int] = None)
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
+#: The ring kernel wins where a CTA's share of K is short: up to RING_MAX_TILES tiles of 64 rows.  With longer
+#: shares (the products of larger models) the loop is what counts, and the TMA-fed tcgen05 kernel with swapped
+#: operands streams better.  Measured alone on a B200 at 1..8 rows, us ring / library / swapped: 3B-sized model
+#: (width 3072, ffn 8192) qkv (12 tiles a CTA) 11.2 / 7.3 / 9.8, o (6) 6.1 / 8.5 / 7.3, gate/up with gating (24)
+#: 21.8 / 22.8 + gating / 19.0, down (16) 14.2 / 17.9 / 12.6; 8B-sized (4096, 14336) qkv (16) 14.4 / 10.0 / 12.3,
+#: o (8) 8.9 / 13.5 / 9.6, gate/up (64) 57 / 40 + gating / 38, down (28) 24.4 / 22.9 / 20.9.  So: short shares to the
+#: ring; long ones to the swapped kernel when the matrix is tall (K >= 2 N) or carries the gating, else to the library.
+RING_MAX_TILES = int(os.environ.get("TIS_RING_MAX_TILES", "8"))
+
+
+def _ring_tiles(n_cols: int, k: int) -> int:
+    """Tiles of 64 rows of K that a CTA of the ring kernel walks."""
+    return -(-(-(-k // _ksplit(n_cols, k))) // 64)
+
+
+def _swap_ok(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False) -> bool:
+    return (a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (not swiglu or w.shape[1] % 64 == 0)
+            and (out is None or out.stride(1) == 1))
+
+
 def _ksplit(n_cols: int, k: int) -> int:
     """CTAs that share a 64-column strip of the weights (a cluster adding up over K): as many as
     keep the grid near two CTAs per SM, each with at least 128 rows of K."""
@@ -214,21 +234,30 @@ def _ksplit_swap(n_cols: int, k: int) -> int:
     return ks
 
 
-def gemm_swap(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
-              ksplit: Optional[int] = None) -> torch.Tensor:
+def gemm_swap(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+              ksplit: Optional[int] = None, sink: Optional["ResidualSink"] = None):
     """``a (n <= 64, K) @ w (K, N)`` in bfloat16 on the tcgen05 tensor cores with the operands swapped (128
     columns of ``w`` are the rows of the tile, the rows of ``a`` its narrow side); with ``swiglu`` the columns of
-    ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2)."""
+    ``w`` are [32 gate | 32 up] blocks and the result is (n, N/2).  ``a`` may be ``ScaledRows``; with ``sink`` the
+    result is added to the residual stream and comes back as ``ScaledRows``."""
     lib = library()
+    scaled = a if isinstance(a, ScaledRows) else None
+    if scaled is not None:
+        a = scaled.rows
     n, k = a.shape
     cols = w.shape[1]
-    if out is None:
+    if not _sink_fits(sink, n, cols, out) or (sink is not None and swiglu):
+        raise KernelError("gemm_swap: the sink does not fit the product")
+    head, tail, result = _fused_args(scaled, sink, n, cols, a.device)
+    if sink is not None:
+        out = result.rows
+    elif out is None:
         out = torch.empty((n, cols // 2 if swiglu else cols), dtype=a.dtype, device=a.device)
     calls["gemm_swap"] += 1
-    _check(lib.tis_gemm_swap(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
-                             ksplit or _ksplit_swap(cols, k), EPI_SWIGLU if swiglu else EPI_STORE, _p(tc_fault()),
-                             _stream()), lib)
-    return out
+    epi = EPI_RESIDUAL if sink is not None else (EPI_SWIGLU if swiglu else EPI_STORE)
+    _check(lib.tis_gemm_swap_fused(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), n, cols, k,
+                                   ksplit or _ksplit_swap(cols, k), epi, *head, *tail, _p(tc_fault()), _stream()), lib)
+    return result if sink is not None else out
 
 
 def _stream_fits(n: int, k: int, ksplit: int) -> bool:
@@ -407,11 +436,18 @@ def gemm(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, sink: Optional[
         a = scaled.rows
     if a.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("float32 products must not run in TF32: torch.backends.cuda.matmul.allow_tf32 is set")
-    if _skinny_ok(a, w) or (_skinny_ok(a, w, STREAM_MAX_ROWS) and _stream_pays(a.shape[0], a.shape[1], w.shape[1])
-                            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+    streams = _stream_pays(a.shape[0], a.shape[1], w.shape[1]) and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+    if (_skinny_ok(a, w) and (streams or _ring_tiles(w.shape[1], a.shape[1]) <= RING_MAX_TILES)) or \
+            (_skinny_ok(a, w, STREAM_MAX_ROWS) and streams):
         if sink is not None and not _sink_fits(sink, a.shape[0], w.shape[1], out):
             sink = None
         return gemm_skinny(scaled if scaled is not None else a, w, out, sink=sink)
+    if _skinny_ok(a, w) and a.shape[1] >= 2 * w.shape[1] and _swap_ok(a, w, out):
+        # a long share of K per CTA and a tall matrix: the tcgen05 kernel with swapped operands
+        if sink is not None and not (_sink_fits(sink, a.shape[0], w.shape[1], out) and sink.values.stride(0) % 4 == 0
+                                     and sink.values.data_ptr() % 16 == 0 and sink.weight.data_ptr() % 16 == 0):
+            sink = None
+        return gemm_swap(scaled if scaled is not None else a, w, out, sink=sink)
     if scaled is not None:
         a = scaled.dense()
     if _tc_ok(a, w, TC_PLAIN_MIN_ROWS) and (out is None or (out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0)):
@@ -431,13 +467,14 @@ def gemm_swiglu(a, w_gu: torch.Tensor, hidden: int, block: int) -> torch.Tensor:
     scaled = a if isinstance(a, ScaledRows) else None
     if scaled is not None:
         a = scaled.rows
-    if block == 32 and _skinny_ok(a, w_gu, SKINNY_SWIGLU_MAX_ROWS):
+    if block == 32 and _skinny_ok(a, w_gu, SKINNY_SWIGLU_MAX_ROWS) and (
+            _ring_tiles(w_gu.shape[1], a.shape[1]) <= RING_MAX_TILES or not _swap_ok(a, w_gu, swiglu=True)):
         return gemm_skinny(scaled if scaled is not None else a, w_gu, swiglu=True)
-    if scaled is not None:
-        a = scaled.dense()
     if (block == 32 and _skinny_ok(a, w_gu, SWAP_SWIGLU_MAX_ROWS) and w_gu.shape[1] % 64 == 0
             and a.data_ptr() % 16 == 0 and w_gu.data_ptr() % 16 == 0):
-        return gemm_swap(a, w_gu, swiglu=True)
+        return gemm_swap(scaled if scaled is not None else a, w_gu, swiglu=True)
+    if scaled is not None:
+        a = scaled.dense()
     if block == 32 and _tc_ok(a, w_gu, TC_MIN_ROWS) and w_gu.shape[1] % 64 == 0:
         return gemm_tc(a, w_gu, swiglu=True)
     gu = gemm(a, w_gu)
