@@ -144,13 +144,21 @@ class GqaMtpModel(Model):
         h = stream.normed(self.rms_out)
         # a step whose shape says that every row is wanted (a decode step) needs no gather
         pick = (lambda t: t) if getattr(step, "want_identity", False) else (lambda t: t.index_select(0, want_rows))
-        out = StepOutput(main=self.lm_head.forward(pick(h)))
-        if aux:
-            prev = h
-            for i, head in enumerate(self.heads):
-                prev = head.forward(prev, self._pending[i], step, self.entries[self.n_trunk_entries + i])
-                out.aux.append(self.lm_head.forward(pick(prev)))
-                out.aux_valid.append(step.stage(head.lag).row_slot.index_select(0, want_rows) >= 0)
+        if not (aux and self.heads):
+            return StepOutput(main=self.lm_head.forward(pick(h)))
+        # the heads' rows first (each is fed by the stage before it), then one product with the output matrix for
+        # the trunk and all heads: the matrix, by far the largest, is read once a step
+        rows, valid = [pick(h)], []
+        prev = h
+        for i, head in enumerate(self.heads):
+            prev = head.forward(prev, self._pending[i], step, self.entries[self.n_trunk_entries + i])
+            rows.append(pick(prev))
+            valid.append(step.stage(head.lag).row_slot.index_select(0, want_rows) >= 0)
+        n = rows[0].shape[0]
+        logits = self.lm_head.forward(torch.cat(rows, dim=0))
+        out = StepOutput(main=logits[:n])
+        out.aux = [logits[(i + 1) * n:(i + 2) * n] for i in range(len(self.heads))]
+        out.aux_valid = valid
         return out
 
 
