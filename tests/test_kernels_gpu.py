@@ -653,6 +653,46 @@ def test_gemm(dtype, n, K, N):
     torch.testing.assert_close(got32.cpu().double(), want, **tol)
 
 
+@pytest.mark.parametrize("n,K,N,kernel", [(5, 1536, 2304, "gemm_skinny"), (3, 4096, 4096, "gemm_skinny"),
+                                          (8, 4096, 1536, "gemm_stream"), (5, 8192, 200, "gemm_swap"),
+                                          (6, 14336, 4096, "gemm_swap"), (6, 3072, 5120, "gemm_library"),
+                                          (9, 1536, 2304, "gemm_library")])
+def test_few_rows_go_to_the_kernel_their_shape_calls_for(n, K, N, kernel):
+    """Few bfloat16 rows: a short share of K per CTA goes to the ring (or, one round of boxes, to the TMA-fed kernel),
+    a long share to the tcgen05 kernel with swapped operands when the matrix is tall, else to the library; with a
+    sink and rows whose norm factor is pending, every one of them gives the same result as add + norm + product."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(19)
+    a = _rand((n, K), torch.bfloat16, g)
+    w = _rand((K, N), torch.bfloat16, g, 0.03).cuda()
+    before = dict(ops.calls)
+    got = ops.gemm(a.cuda(), w)
+    ran = {k for k, v in ops.calls.items() if v != before.get(k, 0)}
+    assert ran == {kernel}, ran
+    torch.testing.assert_close(got.cpu().double(), a.double() @ w.cpu().double(), rtol=2e-2, atol=2e-2)
+    # the same product fed with rows whose factor is pending and told to add to a stream
+    stream = _rand((n, K), torch.float32, g, 2.0)
+    rows = ops.ScaledRows((stream * 1.5).to(torch.bfloat16).cuda(),
+                          torch.nn.functional.pad(stream.pow(2), (0, -K % 64)).reshape(n, -1, 64).sum(-1).cuda(), 0.5)
+    x = (stream * 1.5).to(torch.bfloat16).double() * math.sqrt(K) / (stream.double().norm(dim=-1, keepdim=True) + 0.5)
+    target = _rand((n, N), torch.float32, g, 2.0)
+    values = target.cuda()
+    weight = (1.0 + _rand((N,), torch.float32, g, 0.3)).cuda()
+    out = ops.gemm(rows, w, sink=ops.ResidualSink(values, weight, 0.25) if ops.sink_usable(values, torch.bfloat16) else None)
+    want = x @ w.cpu().double()
+    if isinstance(out, ops.ScaledRows):
+        assert kernel != "gemm_library"
+        torch.testing.assert_close(values.cpu().double(), target.double() + want, rtol=2e-2, atol=3e-2)
+        torch.testing.assert_close(out.dense().cpu().double(),
+                                   (values.cpu().double() * math.sqrt(N) / (values.cpu().double().norm(dim=-1, keepdim=True) + 0.25)
+                                    * weight.cpu().double()), rtol=2e-2, atol=2e-2)
+    else:
+        assert kernel == "gemm_library"
+        torch.testing.assert_close(out.cpu().double(), want, rtol=2e-2, atol=3e-2)
+        assert torch.equal(values.cpu(), target)
+    assert int(ops.tc_fault()[0]) == 0
+
+
 def test_float32_products_are_not_tf32():
     """A product whose exact value needs more than TF32's 10 mantissa bits."""
     ops = _ops()
