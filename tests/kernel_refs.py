@@ -16,9 +16,13 @@ import torch
 
 
 def _row_factor(scaled):
-    """sqrt(width) / (||row of the stream|| + eps) from the partial sums of squares."""
+    """The norm's factor of each row from the partial sums of squares: "l2_eps": sqrt(width) / (||row|| + eps);
+    "mean_eps": 1 / sqrt(mean of squares + eps)."""
     d = scaled.rows.shape[1]
-    return math.sqrt(d) / (scaled.parts.sum(-1, keepdim=True).sqrt() + scaled.eps)
+    s = scaled.parts.sum(-1, keepdim=True)
+    if scaled.kind == "mean_eps":
+        return 1.0 / torch.sqrt(s / d + scaled.eps)
+    return math.sqrt(d) / (s.sqrt() + scaled.eps)
 
 
 def scaled_rows_dense(scaled):
@@ -43,7 +47,8 @@ def gemm(a, w, out=None, sink=None):
         strips = -(-d // 64)
         sq = torch.zeros((n, strips * 64), dtype=torch.float32)
         sq[:, :d] = sink.values.pow(2)
-        return ops.ScaledRows((sink.values * sink.weight).to(a.dtype), sq.reshape(n, strips, 64).sum(-1), sink.eps, sink.norm)
+        return ops.ScaledRows((sink.values * sink.weight).to(a.dtype), sq.reshape(n, strips, 64).sum(-1), sink.eps, sink.norm,
+                              sink.kind)
     r = r.to(a.dtype)
     if out is not None:
         out.copy_(r)

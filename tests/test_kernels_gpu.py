@@ -244,6 +244,34 @@ def test_skinny_gemm_adds_to_the_stream_and_defers_the_norm(n, K, N, kernel, mon
         assert int(ops._tc_fault[0]) == 0, "a wait inside the kernel ran out"
 
 
+@pytest.mark.parametrize("kernel", ["ring", "boxes", "swapped"])
+def test_the_other_norm_factor(kernel, monkeypatch):
+    """Rows whose norm is rsqrt(mean of squares + eps) (the "mean_eps" factor) instead of this architecture's
+    sqrt(d) / (norm + eps): the products apply that factor from the same partial sums, and so does ``dense()``."""
+    ops = _ops()
+    monkeypatch.setattr(ops, "STREAM_GEMM", kernel == "boxes")
+    monkeypatch.setattr(ops, "STREAM_MIN_KC", 0)
+    monkeypatch.setattr(ops, "STREAM_MAX_KC", 1 << 30)
+    g = torch.Generator().manual_seed(23)
+    n, K, N, eps = 6, 328, 136, 0.3
+    stream = _rand((n, K), torch.float32, g, 1.5)
+    stream[1] *= 0.01                                            # a row for which eps decides
+    weight = 1.0 + _rand((K,), torch.float32, g, 0.3)
+    operand = (stream * weight).to(torch.bfloat16)
+    parts = torch.nn.functional.pad(stream.pow(2), (0, -K % 64)).reshape(n, -1, 64).sum(-1)
+    rows = ops.ScaledRows(operand.cuda(), parts.cuda(), eps, kind="mean_eps")
+    factor = 1.0 / torch.sqrt(stream.double().pow(2).mean(-1, keepdim=True) + eps)
+    other = math.sqrt(K) / (stream.double().norm(dim=-1, keepdim=True) + eps)
+    assert ((factor - other).abs() / factor).max() > 0.2        # the two factors differ where eps matters
+    w = _rand((K, N), torch.bfloat16, g, 0.05)
+    want = (operand.double() * factor) @ w.double()
+    got = (ops.gemm_swap if kernel == "swapped" else ops.gemm_skinny)(rows, w.cuda())
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(rows.dense().cpu().double(), operand.double() * factor, rtol=1e-2, atol=1e-2)
+    with pytest.raises(ops.KernelError):
+        ops.ResidualSink(torch.zeros(1, 8), torch.ones(8), 0.0, kind="layer_norm")
+
+
 def test_a_sink_is_ignored_by_products_that_cannot_use_it(monkeypatch):
     """More rows than the weight-streaming kernels take, or float32: the product returns its result and leaves
     the stream alone; rows whose factor is pending are made whole for a product that cannot apply it."""

@@ -3,6 +3,8 @@ given random weights by the engine's random-weights mode, loaded by tensor name 
 whole, token by token and in portions — with no change to a file of the package:
 
 * a position encoding of another kind ("none": no rotation, the cache write only);
+* a norm of another form (rsqrt(mean of squares + eps)), which the decode products fold into themselves as they do
+  the architecture's own;
 * a feed-forward with routing (two experts, the better one per token);
 * a mixer whose cached keys and values have different widths (a key of 8, a value of 24 elements);
 * a whole architecture with tensor names of its own (``register_architecture``).
@@ -95,6 +97,78 @@ def test_toy_position_encoding_without_rotation(device, tmp_path, request, monke
     for cuts in CUTS:
         got = _step_through(_runner(folder, device, request), toks, cuts)
         assert float((got - want).abs().max()) < 2e-4, cuts
+
+
+# ---------------------------------------------------------------------------------------------------
+# a norm of another form
+# ---------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_toy_norm_of_another_form(device, tmp_path, request, monkeypatch):
+    """y = x * rsqrt(mean(x^2) + eps) * scale, with a large eps so that its place matters.  Whole, the norm runs as
+    the part's own operations; token by token in bfloat16 the last product of every mixer and feed-forward adds to
+    the stream itself and the next product applies this norm's factor (the sink the norm hands out names it)."""
+    from tiny_inference_server_b200 import register_part
+    from tiny_inference_server_b200.kernels import ops
+    from tiny_inference_server_b200.parts import Norm, WeightSpec
+
+    class MeanSquareNorm(Norm):
+        def __init__(self, width, eps, prefix=""):
+            super().__init__(prefix)
+            self.width, self.eps = width, float(eps)
+            self.scale, self.out_dtype = None, torch.float32
+
+        @classmethod
+        def from_config(cls, cfg, prefix):
+            return cls(cfg.hidden_size, cfg.rms_norm_eps, prefix=prefix)
+
+        def weight_specs(self):
+            return {"scale": WeightSpec((self.width,), init="ones_normal")}
+
+        def load(self, tensors, ctx):
+            self.scale = tensors[self.prefix + "scale"].to(device=ctx.device, dtype=torch.float32).contiguous()
+            self.out_dtype = ctx.dtype
+
+        def add_norm(self, residual, delta):
+            if delta is not None:
+                residual += delta.float()
+            return (residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + self.eps) * self.scale).to(self.out_dtype)
+
+        def forward(self, residual):
+            return self.add_norm(residual, None)
+
+        def sink(self, values):
+            return ops.ResidualSink(values, self.scale, self.eps, norm=self, kind="mean_eps")
+
+    register_part("norm", "toy_mean_square", MeanSquareNorm)
+    cfg = dict(tiny_configs.TINY_A, norm_type="toy_mean_square", rms_norm_eps=0.5, num_mtp_heads=0)
+    folder = tiny_configs.make_model_folder(cfg, 8, str(tmp_path / "m"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    toks = tiny_configs.random_prompts(cfg["vocab_size"], [19], seed=9)[0]
+    own_form = plain_model.plain_forward(c, W, toks, mtp=False)["main"]
+    monkeypatch.setattr(plain_model, "plain_rms_norm",
+                        lambda x, scale, eps: x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * scale)
+    want = plain_model.plain_forward(c, W, toks, mtp=False)["main"]
+    assert float((want - own_form).abs().max()) > 0.05           # the form of the norm matters for this model
+    for cuts in CUTS:
+        got = _step_through(_runner(folder, device, request), toks, cuts)
+        assert float((got - want).abs().max()) < 2e-4, cuts
+    # bfloat16, token by token: the norms are folded into the products (a sink per mixer and feed-forward but the last)
+    sinks = []
+    made = ops.ResidualSink.__init__
+
+    def counted(self, *a, **k):
+        sinks.append(k.get("kind"))
+        made(self, *a, **k)
+    monkeypatch.setattr(ops.ResidualSink, "__init__", counted)
+    got = _step_through(_runner(folder, device, request, dtype="bfloat16"), toks, [1] * 19)
+    # (on the device the step is captured into a graph once and replayed: the sinks are made at the capture)
+    steps_in_python = 19 if device == "cpu" else 1
+    assert len(sinks) >= steps_in_python * (2 * cfg["num_layers"] - 1) and set(sinks) == {"mean_eps"}
+    assert float((got - want).abs().max()) < 3e-2
+    monkeypatch.setattr(ops, "FUSED_NORM", False)
+    unfused = _step_through(_runner(folder, device, request, dtype="bfloat16"), toks, [1] * 19)
+    assert float((unfused - want).abs().max()) < 3e-2 and float((unfused - got).abs().max()) < 3e-2
 
 
 # ---------------------------------------------------------------------------------------------------

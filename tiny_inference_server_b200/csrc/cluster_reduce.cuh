@@ -25,7 +25,7 @@ struct Epilogue {
     int M, N;
     int epi;
     // rows that still lack their norm's factor: partial sums of squares [M][in_parts] (null: none)
-    const float* in_ss; int in_parts; float in_eps, in_sqrt_width;
+    const float* in_ss; int in_parts; NormFactor in_factor;
     // EPI_RESIDUAL: the stream [M][ldr] (read and written), the next norm's weight [N], partial sums out [M][strips]
     float* res; int ldr; const float* norm_w; float* out_ss;
     int* fault;
@@ -63,7 +63,7 @@ __device__ __forceinline__ void load_row_factors(const Epilogue& e, float* row_f
         float s = 0.f;
         for (int i = lane; i < e.in_parts; i += 32) s += e.in_ss[(size_t)r * e.in_parts + i];
         s = warp_sum(s);
-        if (lane == 0) row_factor[r] = e.in_sqrt_width / (sqrtf(s) + e.in_eps);
+        if (lane == 0) row_factor[r] = e.in_factor.of(s);
     }
 }
 

@@ -81,6 +81,21 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// The factor a norm of the RMS family multiplies a row with, from the row's sum of squares s over a width d:
+// kind 0: sqrt(d) / (sqrt(s) + eps) (eps added to the L2 norm); kind 1: rsqrt(s / d + eps).  Both are
+// num / (sqrt(s * mul + add) + plus) with constants the host works out, so that a kernel has no case to tell apart.
+enum { TIS_NORM_L2_EPS = 0, TIS_NORM_MEAN_EPS = 1 };
+struct NormFactor {
+    float num, mul, add, plus;
+    __device__ __forceinline__ float of(float sum_sq) const { return num / (sqrtf(fmaf(sum_sq, mul, add)) + plus); }
+};
+inline NormFactor norm_factor(int kind, int width, float eps) {
+    NormFactor f;
+    const float d = (float)(width > 0 ? width : 1);
+    if (kind == TIS_NORM_MEAN_EPS) { f.num = 1.f; f.mul = 1.f / d; f.add = eps; f.plus = 0.f; }
+    else { f.num = sqrtf(d); f.mul = 1.f; f.add = 0.f; f.plus = eps; }
+    return f;
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

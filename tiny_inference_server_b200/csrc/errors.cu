@@ -34,4 +34,4 @@ bool tis_pdl_enabled() {
 
 // Version of the launcher interface; the Python side refuses a library built from
 // other sources than its own.
-TIS_API int tis_abi_version() { return 2; }
+TIS_API int tis_abi_version() { return 3; }

@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
 // Refuses what the TMA engine cannot address: K, N and the strides must be multiples of 8 elements and
 // the pointers 16-byte aligned.  in_ss .. out_ss: as in tis_gemm_skinny_fused.
 TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
-                                  int ksplit, int epi, const float* in_ss, int in_parts, float in_eps, int in_width,
+                                  int ksplit, int epi, const float* in_ss, int in_parts, float in_eps, int in_width, int in_kind,
                                   float* res, int ldr, const float* norm_w, float* out_ss, int* fault,
                                   cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return TIS_OK;
@@ -232,8 +232,8 @@ TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw
                       "sums, even row strides (%d, %d) and aligned pointers", ldr, ldo);
         return TIS_BAD_SIZE;
     }
-    if (in_ss != nullptr && (in_parts <= 0 || in_width <= 0)) {
-        tis_set_error("gemm_stream: %d partial sums a row over a width of %d", in_parts, in_width);
+    if (in_ss != nullptr && (in_parts <= 0 || in_width <= 0 || in_kind < TIS_NORM_L2_EPS || in_kind > TIS_NORM_MEAN_EPS)) {
+        tis_set_error("gemm_stream: %d partial sums a row over a width of %d, norm kind %d", in_parts, in_width, in_kind);
         return TIS_BAD_SIZE;
     }
     if (epi == EPI_SWIGLU && N % 64) {
@@ -245,7 +245,7 @@ TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw
     StreamParams p;
     p.x = (const bf16*)x; p.ldx = ldx; p.K = K;
     p.e.out = (bf16*)out; p.e.ldo = ldo; p.e.M = M; p.e.N = N; p.e.epi = epi; p.e.fault = fault;
-    p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_eps = in_eps; p.e.in_sqrt_width = sqrtf((float)(in_width > 0 ? in_width : 1));
+    p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_factor = norm_factor(in_kind, in_width, in_eps);
     p.e.res = res; p.e.ldr = ldr; p.e.norm_w = norm_w; p.e.out_ss = out_ss;
     p.kc = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
     const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
@@ -296,6 +296,6 @@ TIS_API int tis_gemm_stream(const void* x, int ldx, const void* w, int ldw, void
         tis_set_error("gemm_stream: the residual epilogue goes through tis_gemm_stream_fused");
         return TIS_BAD_SIZE;
     }
-    return tis_gemm_stream_fused(x, ldx, w, ldw, out, ldo, M, N, K, ksplit, epi, nullptr, 0, 0.f, 0, nullptr, 0, nullptr,
+    return tis_gemm_stream_fused(x, ldx, w, ldw, out, ldo, M, N, K, ksplit, epi, nullptr, 0, 0.f, 0, 0, nullptr, 0, nullptr,
                                  nullptr, fault, stream);
 }

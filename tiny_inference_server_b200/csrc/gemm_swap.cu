@@ -164,7 +164,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 float sq = 0.f;
                 for (int i = lane; i < p.e.in_parts; i += 32) sq += p.e.in_ss[(size_t)r * p.e.in_parts + i];
                 sq = warp_sum(sq);
-                if (lane == 0) row_factor[r] = p.e.in_sqrt_width / (sqrtf(sq) + p.e.in_eps);
+                if (lane == 0) row_factor[r] = p.e.in_factor.of(sq);
             }
         }
         cluster_reduce::cluster_wait();
@@ -330,7 +330,7 @@ int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, SwapParams p, int 
 // Refuses what the TMA engine cannot address: K, N and the strides must be multiples of 8 elements and the pointers
 // 16-byte aligned.  in_ss .. out_ss: as in tis_gemm_skinny_fused (epi 2 = the residual epilogue).
 TIS_API int tis_gemm_swap_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
-                                int ksplit, int epi, const float* in_ss, int in_parts, float in_eps, int in_width,
+                                int ksplit, int epi, const float* in_ss, int in_parts, float in_eps, int in_width, int in_kind,
                                 float* res, int ldr, const float* norm_w, float* out_ss, int* fault, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return TIS_OK;
     if (M > 64) {
@@ -361,8 +361,8 @@ TIS_API int tis_gemm_swap_fused(const void* x, int ldx, const void* w, int ldw, 
                       "sums, a row stride (%d) that is a multiple of 4 and 16-byte aligned pointers", ldr);
         return TIS_BAD_SIZE;
     }
-    if (in_ss != nullptr && (in_parts <= 0 || in_width <= 0)) {
-        tis_set_error("gemm_swap: %d partial sums a row over a width of %d", in_parts, in_width);
+    if (in_ss != nullptr && (in_parts <= 0 || in_width <= 0 || in_kind < TIS_NORM_L2_EPS || in_kind > TIS_NORM_MEAN_EPS)) {
+        tis_set_error("gemm_swap: %d partial sums a row over a width of %d, norm kind %d", in_parts, in_width, in_kind);
         return TIS_BAD_SIZE;
     }
     const int nb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -371,7 +371,7 @@ TIS_API int tis_gemm_swap_fused(const void* x, int ldx, const void* w, int ldw, 
     SwapParams p;
     p.K = K; p.stages = 0;
     p.e.out = (bf16*)out; p.e.ldo = ldo; p.e.M = M; p.e.N = N; p.e.epi = epi; p.e.fault = fault;
-    p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_eps = in_eps; p.e.in_sqrt_width = sqrtf((float)(in_width > 0 ? in_width : 1));
+    p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_factor = norm_factor(in_kind, in_width, in_eps);
     p.e.res = res; p.e.ldr = ldr; p.e.norm_w = norm_w; p.e.out_ss = out_ss;
     p.kc = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
     if (nb == 16) return launch_swap<16>(mw, mx, p, ksplit, stream);
@@ -385,6 +385,6 @@ TIS_API int tis_gemm_swap(const void* x, int ldx, const void* w, int ldw, void* 
         tis_set_error("gemm_swap: the residual epilogue goes through tis_gemm_swap_fused");
         return TIS_BAD_SIZE;
     }
-    return tis_gemm_swap_fused(x, ldx, w, ldw, out, ldo, M, N, K, ksplit, epi, nullptr, 0, 0.f, 0, nullptr, 0, nullptr,
+    return tis_gemm_swap_fused(x, ldx, w, ldw, out, ldo, M, N, K, ksplit, epi, nullptr, 0, 0.f, 0, 0, nullptr, 0, nullptr,
                                nullptr, fault, stream);
 }

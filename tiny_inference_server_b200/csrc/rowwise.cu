@@ -201,10 +201,10 @@ TIS_API int tis_add_rmsnorm(int dtype, float* residual, const void* delta, const
 // ----------------------------------------------------------------------------------
 // Rows that still lack their norm's factor (the stream times the norm's weight, and partial sums of squares
 // of the stream, as the residual epilogue of the weight-streaming products leaves them), made whole:
-// out[r] = rows[r] * sqrt(width) / (sqrt(sum of parts[r]) + eps).  For readers that cannot apply the
+// out[r] = rows[r] * norm_factor(kind, width, eps).of(sum of parts[r]).  For readers that cannot apply the
 // factor themselves.
 __global__ void __launch_bounds__(256)
-scale_rows_kernel(const bf16* __restrict__ rows, int ld, const float* __restrict__ parts, int n_parts, float eps,
+scale_rows_kernel(const bf16* __restrict__ rows, int ld, const float* __restrict__ parts, int n_parts, NormFactor factor,
                   bf16* __restrict__ out, int ldo, int d) {
     __shared__ float red[33];
     pdl_launch_dependents();
@@ -213,20 +213,20 @@ scale_rows_kernel(const bf16* __restrict__ rows, int ld, const float* __restrict
     float s = 0.f;
     for (int i = threadIdx.x; i < n_parts; i += blockDim.x) s += parts[(size_t)r * n_parts + i];
     s = block_sum(s, red);
-    const float f = sqrtf((float)d) / (sqrtf(s) + eps);
+    const float f = factor.of(s);
     for (int i = threadIdx.x; i < d; i += blockDim.x)
         out[(size_t)r * ldo + i] = __float2bfloat16_rn(__bfloat162float(rows[(size_t)r * ld + i]) * f);
 }
 
-TIS_API int tis_scale_rows(const void* rows, int ld, const float* parts, int n_parts, float eps, void* out, int ldo,
-                           int n, int d, cudaStream_t stream) {
+TIS_API int tis_scale_rows(const void* rows, int ld, const float* parts, int n_parts, float eps, int kind, void* out,
+                           int ldo, int n, int d, cudaStream_t stream) {
     if (n <= 0 || d <= 0) return TIS_OK;
-    if (n_parts <= 0) {
-        tis_set_error("scale_rows: %d partial sums a row", n_parts);
+    if (n_parts <= 0 || kind < TIS_NORM_L2_EPS || kind > TIS_NORM_MEAN_EPS) {
+        tis_set_error("scale_rows: %d partial sums a row, norm kind %d", n_parts, kind);
         return TIS_BAD_SIZE;
     }
-    tis_launch(scale_rows_kernel, dim3(n), dim3(256), 0, stream, (const bf16*)rows, ld, parts, n_parts, eps, (bf16*)out,
-               ldo, d);
+    tis_launch(scale_rows_kernel, dim3(n), dim3(256), 0, stream, (const bf16*)rows, ld, parts, n_parts,
+               norm_factor(kind, d, eps), (bf16*)out, ldo, d);
     return tis_check_launch("scale_rows");
 }
 

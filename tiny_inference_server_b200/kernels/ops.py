@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 2
+ABI_VERSION = 3
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -118,24 +118,32 @@ EPI_STORE, EPI_SWIGLU, EPI_RESIDUAL = 0, 1, 2
 FUSED_NORM = os.environ.get("TIS_FUSED_NORM", "1") != "0"
 
 
+#: the factor a norm multiplies a row with, as a function of the row's sum of squares s over a width d:
+#: "l2_eps": sqrt(d) / (sqrt(s) + eps) (eps added to the L2 norm); "mean_eps": rsqrt(s / d + eps)
+NORM_KINDS = {"l2_eps": 0, "mean_eps": 1}
+
+
 class ResidualSink:
     """Where a product adds its result itself: the float32 residual stream ``values`` (n, d); it then also
     leaves the stream times ``weight`` (the weight of the norm that reads the stream next) and partial sums of
-    squares, so that the norm's factor ``sqrt(d) / (||row|| + eps)`` can be applied after the next product
-    instead of before it.  ``norm`` is whoever made the sink (the reader checks it is the same norm)."""
+    squares, so that the norm's factor per row (``kind``, one of ``NORM_KINDS``) can be applied after the next
+    product instead of before it.  ``norm`` is whoever made the sink (the reader checks it is the same norm)."""
 
-    def __init__(self, values: torch.Tensor, weight: torch.Tensor, eps: float, norm=None):
-        self.values, self.weight, self.eps, self.norm = values, weight, float(eps), norm
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, eps: float, norm=None, kind: str = "l2_eps"):
+        if kind not in NORM_KINDS:
+            raise KernelError(f"norm factor {kind!r}: the products know {sorted(NORM_KINDS)}")
+        self.values, self.weight, self.eps, self.norm, self.kind = values, weight, float(eps), norm, kind
 
 
 class ScaledRows:
     """Rows of a norm's output that still lack the factor of their row: ``rows`` (n, d) bfloat16 = stream *
     norm weight, ``parts`` (n, T) float32 = partial sums of squares of the stream.  Row r of the norm's
-    output is ``rows[r] * sqrt(d) / (sqrt(parts[r].sum()) + eps)``; a weight-streaming product applies the
-    factor to its own result (``gemm`` and ``gemm_swiglu`` take these rows), ``dense()`` makes the rows whole."""
+    output is ``rows[r]`` times the factor of ``kind`` (``NORM_KINDS``) at ``parts[r].sum()``; a weight-streaming
+    product applies the factor to its own result (``gemm`` and ``gemm_swiglu`` take these rows), ``dense()`` makes
+    the rows whole."""
 
-    def __init__(self, rows: torch.Tensor, parts: torch.Tensor, eps: float, norm=None):
-        self.rows, self.parts, self.eps, self.norm = rows, parts, float(eps), norm
+    def __init__(self, rows: torch.Tensor, parts: torch.Tensor, eps: float, norm=None, kind: str = "l2_eps"):
+        self.rows, self.parts, self.eps, self.norm, self.kind = rows, parts, float(eps), norm, kind
 
     @property
     def shape(self):
@@ -151,7 +159,7 @@ class ScaledRows:
         out = torch.empty_like(self.rows)
         calls["scale_rows"] += 1
         _check(lib.tis_scale_rows(_p(self.rows), self.rows.stride(0), _p(self.parts), self.parts.shape[1], _f(self.eps),
-                                  _p(out), out.stride(0), n, d, _stream()), lib)
+                                  NORM_KINDS[self.kind], _p(out), out.stride(0), n, d, _stream()), lib)
         return out
 
 
@@ -274,13 +282,13 @@ def _fused_args(scaled: Optional[ScaledRows], sink: Optional[ResidualSink], n: i
     sink with the tensors it fills."""
     result = None
     if scaled is not None:
-        head = (_p(scaled.parts), scaled.parts.shape[1], _f(scaled.eps), scaled.rows.shape[1])
+        head = (_p(scaled.parts), scaled.parts.shape[1], _f(scaled.eps), scaled.rows.shape[1], NORM_KINDS[scaled.kind])
     else:
-        head = (None, 0, _f(0.0), 0)
+        head = (None, 0, _f(0.0), 0, 0)
     if sink is not None:
         parts = torch.empty((n, -(-cols // 64)), dtype=torch.float32, device=device)
         rows = torch.empty((n, cols), dtype=torch.bfloat16, device=device)
-        result = ScaledRows(rows, parts, sink.eps, sink.norm)
+        result = ScaledRows(rows, parts, sink.eps, sink.norm, sink.kind)
         tail = (_p(sink.values), sink.values.stride(0), _p(sink.weight), _p(parts))
     else:
         tail = (None, 0, None, None)
