@@ -28,6 +28,7 @@
 // to scratch memory and `attn_merge_kernel` merges them.
 #include "common.cuh"
 #include "cluster_reduce.cuh"
+#include "timeline.cuh"
 #include <cooperative_groups.h>
 #include <cstdlib>
 
@@ -71,6 +72,9 @@ struct AttnParams {
     // rotary encoding and cache write done by this kernel (decode rows; see FUSED below)
     const float* rope_cos; const float* rope_sin;   // [positions][HD/2]
     bf16* plane_w;          // the plane, writable: where the row's key and value go (null: another entry fills it)
+    TIS_TIMELINE_MEMBER     // (instrumented builds only; the decode kernel's stamps: 0 entry, 1 before and 2 after the
+                            //  dependency wait, 3 first tile landed, 4 last tile landed, 5 loop done, 6 partial results
+                            //  pushed, 7 partials of the cluster arrived, 8 stored)
 };
 
 // ---- mbarrier and bulk-copy (TMA) helpers --------------------------------------------
@@ -232,7 +236,8 @@ attn_mma_kernel(const AttnParams p) {
     const int kvh = blockIdx.y, split = blockIdx.z;
     const int warp = tid >> 5, lane = tid & 31;
     const int g_lane = lane >> 2, t_lane = lane & 3;
-    const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+    // (no tile arrays: tile i is row i alone — a decode step — and two dependent loads fewer before the first copy)
+    const int row0 = p.tile_row0 != nullptr ? p.tile_row0[tile] : tile, rows = p.tile_rows != nullptr ? p.tile_rows[tile] : 1;
     const int G = p.G;
 
     // first valid row of the tile (rows of a stage that lags the trunk start with padding)
@@ -802,13 +807,15 @@ attn_decode_kernel(const AttnParams p) {
     __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES], merge_bar;
     const int STAGES = p.stages;
 
+    TIS_STAMP(p, 0);
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool producer = warp == NTHREADS / 32;
     bf16* stages = reinterpret_cast<bf16*>(smem_raw);
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int g_lane = lane >> 2, t_lane = lane & 3;
-    const int row0 = p.tile_row0[tile], rows = p.tile_rows[tile];
+    // (no tile arrays: tile i is row i alone — a decode step — and two dependent loads fewer before the first copy)
+    const int row0 = p.tile_row0 != nullptr ? p.tile_row0[tile] : tile, rows = p.tile_rows != nullptr ? p.tile_rows[tile] : 1;
     const int G = p.G;
 
     // The merge of the splits (see the end of the kernel): output dims are owned in blocks of eight, block d by
@@ -899,7 +906,9 @@ attn_decode_kernel(const AttnParams p) {
                 }
             }
         }
+        TIS_STAMP(p, 1);
         pdl_wait();
+        TIS_STAMP(p, 2);
         if (ntiles > 0) {
             unsigned qa[KSTEPS][4];
 #pragma unroll
@@ -941,6 +950,8 @@ attn_decode_kernel(const AttnParams p) {
                 const int stg = it % STAGES;
                 bf16* cur = stages + stg * STAGE_ELEMS;
                 mbar_wait(&full[stg], (unsigned)((it / STAGES) & 1), p.fault);         // tile `it` has landed
+                if (it == 0) TIS_STAMP(p, 3);
+                if (it == ntiles - 1) TIS_STAMP(p, 4);
 
                 if (FUSED && own_pos >= 0 && it == ntiles - 1) {
                     const bf16* krow = p.q + (size_t)(row0 + rows - 1) * p.q_stride + (size_t)(p.H + kvh) * HD;
@@ -1081,6 +1092,7 @@ attn_decode_kernel(const AttnParams p) {
         // rank d % splits; every CTA sends its partial of a block to the owner (st.async, counted on the owner's
         // mbarrier), the owner combines the partials of the splits from its own shared memory and writes the
         // output.  No cluster barrier after the loop, no remote load, and a CTA leaves when it has what it owns.
+        TIS_STAMP(p, 5);
         asm volatile("bar.sync 1, 128;\n" ::: "memory");
         constexpr int HDP = HD + 4;
         float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
@@ -1126,7 +1138,9 @@ attn_decode_kernel(const AttnParams p) {
                                "r"(cluster_reduce::map_to_rank(bar_base, (unsigned)q)) : "memory");
             }
         }
+        TIS_STAMP(p, 6);
         mbar_wait_cluster(&merge_bar, 0u, p.fault);              // bounded
+        TIS_STAMP(p, 7);
         const int own_dims = own_blocks * 8;
         for (int idx = tid; idx < pairs * own_dims; idx += NTHREADS) {
             const int m = idx / own_dims, c = idx - m * own_dims;
@@ -1150,6 +1164,7 @@ attn_decode_kernel(const AttnParams p) {
             p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
                 __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
         }
+        TIS_STAMP(p, 8);
     }
 }
 
@@ -1158,7 +1173,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
                                   bf16* __restrict__ out, int out_stride, const int* __restrict__ tile_row0,
                                   const int* __restrict__ tile_rows, int H, int num_splits) {
     const int tile = blockIdx.y, hq = blockIdx.x;
-    const int row0 = tile_row0[tile], rows = tile_rows[tile];
+    const int row0 = tile_row0 != nullptr ? tile_row0[tile] : tile, rows = tile_rows != nullptr ? tile_rows[tile] : 1;
     for (int r = 0; r < rows; ++r) {
         const int row = row0 + r;
         const size_t pr = ((size_t)row * H + hq) * num_splits;
@@ -1271,6 +1286,7 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
     p.fault = fault;
     p.rope_cos = rope_cos; p.rope_sin = rope_sin;
     p.plane_w = (fused && write_kv) ? (bf16*)plane : nullptr;
+    TIS_TIMELINE_TAKE(p);
     // decode tiles go to the kernel with a producer warp where its layout allows (page segments: two lanes each)
     // and while all its CTAs are resident at once, two to an SM (its 160 threads hold as many registers as allow
     // two; the lock-step kernel fits three).  Measured on a B200 at head size 128, context 4096, us a launch,
@@ -1305,6 +1321,9 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         for (int cand = 3; cand <= MAX_STAGES; ++cand) {
             const size_t need = warp_specialised ? (size_t)cand * STAGE_BYTES + recv_bytes : smem_bytes(MODE_KEYS, cand);
             if (need > 220 * 1024 || cand - 1 > tiles_per_split) break;
+            // the kernel with a producer warp: no more stages than a split has tiles (shared memory that it leaves
+            // free lets its CTAs start beside those of the product before it, and order their tiles, earlier)
+            if (warp_specialised && cand > tiles_per_split) break;
             // the kernel with a producer warp keeps three stages wherever two CTAs of them fit an SM
             const bool fits_twice = warp_specialised && cand == 3 && 2 * (need + 1024) <= 220 * 1024;
             if (ctas > (long long)sms && !fits_twice) break;

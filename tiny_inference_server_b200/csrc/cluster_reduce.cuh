@@ -56,16 +56,47 @@ __device__ __forceinline__ void init_barrier(unsigned long long* bar, unsigned r
                  "r"((unsigned)(owned * STRIP * 4) * ksplit) : "memory");
 }
 
-// the norm's factor of each row into shared memory (consumer threads; visible after their next barrier)
-__device__ __forceinline__ void load_row_factors(const Epilogue& e, float* row_factor, int warp, int lane) {
-    if (e.in_ss == nullptr) return;
-    for (int r = warp; r < e.M; r += CONSUMERS / 32) {
-        float s = 0.f;
-        for (int i = lane; i < e.in_parts; i += 32) s += e.in_ss[(size_t)r * e.in_parts + i];
-        s = warp_sum(s);
-        if (lane == 0) row_factor[r] = e.in_factor.of(s);
+// The norm's factor of each row, from the partial sums of squares the kernel before left, in two halves so that the
+// loads are not waited for before the loop: `RowFactorLoads::order` (consumer threads, after the dependency wait)
+// only issues the loads — eight lanes a row, sixteen rows at once, up to eight partial sums a lane — and
+// `finish` (after the loop, before the barrier that precedes the epilogue) adds them up and writes the factors
+// to shared memory.  Rows or partial sums beyond that (more than 16 rows, more than 64 sums a row) are done at once
+// in `order`, a warp per row.
+struct RowFactorLoads {
+    float part[8];
+    bool deferred;
+    __device__ __forceinline__ void order(const Epilogue& e, float* row_factor, int tid) {
+        deferred = false;
+        if (e.in_ss == nullptr) return;
+        const int warp = tid >> 5, lane = tid & 31;
+        if (e.M <= 16 && e.in_parts <= 64) {
+            deferred = true;
+            const int row = tid >> 3, l8 = tid & 7;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = l8 + 8 * j;
+                part[j] = (row < e.M && i < e.in_parts) ? e.in_ss[(size_t)row * e.in_parts + i] : 0.f;
+            }
+            return;
+        }
+        for (int r = warp; r < e.M; r += CONSUMERS / 32) {
+            float s = 0.f;
+            for (int i = lane; i < e.in_parts; i += 32) s += e.in_ss[(size_t)r * e.in_parts + i];
+            s = warp_sum(s);
+            if (lane == 0) row_factor[r] = e.in_factor.of(s);
+        }
     }
-}
+    __device__ __forceinline__ void finish(const Epilogue& e, float* row_factor, int tid) const {
+        if (!deferred) return;                        // (the same for every consumer thread)
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += part[j];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if ((tid & 7) == 0 && (tid >> 3) < e.M) row_factor[tid >> 3] = e.in_factor.of(s);
+    }
+};
 
 // Called by the 128 consumer threads (tid 0..127; warp w holds columns 16w..16w+15 of the strip as two n8
 // fragments of mma.m16n8k16 per 16 rows), after every thread of the cluster has passed cluster_wait().

@@ -1,5 +1,6 @@
 // Last-error text of the library (per host thread) and the launch check.
 #include "common.cuh"
+#include "timeline.cuh"
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -35,3 +36,18 @@ bool tis_pdl_enabled() {
 // Version of the launcher interface; the Python side refuses a library built from
 // other sources than its own.
 TIS_API int tis_abi_version() { return 3; }
+
+#ifdef TIS_TIMELINE
+static thread_local unsigned long long* g_timeline = nullptr;
+
+// The next launch of an instrumented kernel of this library writes its stamps to `buffer`
+// ([CTAs][TIS_TIMELINE_SLOTS] 64-bit words, zeroed by the caller); the launches after it write nothing.
+TIS_API void tis_timeline_next(void* buffer) { g_timeline = static_cast<unsigned long long*>(buffer); }
+TIS_API int tis_timeline_slots() { return TIS_TIMELINE_SLOTS; }
+
+Timeline tis_timeline_take() {
+    Timeline t{g_timeline};
+    g_timeline = nullptr;
+    return t;
+}
+#endif

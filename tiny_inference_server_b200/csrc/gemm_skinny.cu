@@ -24,6 +24,7 @@
 // anything — and only then waits (griddepcontrol.wait) for the kernel before it, whose output
 // is x.  So the weight stream of one projection overlaps the tail of the kernel before.
 #include "cluster_reduce.cuh"
+#include "timeline.cuh"
 #include <cooperative_groups.h>
 
 namespace {
@@ -46,6 +47,8 @@ struct GemmParams {
     int kc;                       // rows of K per CTA of a cluster (a multiple of BK)
     int stages;                   // ring length: min(tiles per CTA, MAX_STAGES)
     cluster_reduce::Epilogue e;   // rows, columns, where the result goes
+    TIS_TIMELINE_MEMBER           // (instrumented builds only; stamps: 0 entry, 1 weights ordered, 2 dependency wait over,
+                                  //  3 first tile ready, 4 loop done, 5 cluster barrier passed, 6 stored)
 };
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
@@ -115,6 +118,7 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
     const int nkt = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
 
     // let the kernel after this one start its own prologue as soon as it can
+    TIS_STAMP(p, 0);
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
     if (tid == 0) cluster_reduce::init_barrier(&recv_bar, rank, ksplit, p.e.M);
     cluster_reduce::cluster_arrive();        // waited for after the loop: by then every CTA's barrier is ready
@@ -125,13 +129,16 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
     for (int s = 0; s < pre; ++s) load_w(w_st + s * W_ELEMS, p, k_begin + s * BK, k_end, n0, tid);
     cp_commit();
     // x is the output of the kernel before this one
+    TIS_STAMP(p, 1);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    TIS_STAMP(p, 2);
     for (int s = 0; s < pre; ++s) {
         load_x<MT>(x_st + s * X_ELEMS, p, k_begin + s * BK, k_end, tid);
         cp_commit();                     // one group per tile: tile s is ready when all but pre-1-s groups are done
     }
-    // the norm's factor of each row, from the partial sums the kernel before left
-    cluster_reduce::load_row_factors(p.e, row_factor, warp, lane);
+    // the norm's factor of each row, from the partial sums the kernel before left: the loads now, the rest after the loop
+    cluster_reduce::RowFactorLoads factors;
+    factors.order(p.e, row_factor, tid);
 
     float acc[MT][2][4];
 #pragma unroll
@@ -180,6 +187,7 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
         // the whole share is in flight already: one wait, one barrier, no barrier between tiles
         cp_wait<0>();
         __syncthreads();
+        TIS_STAMP(p, 3);
         for (int it = 0; it < nkt; ++it) tile_products(w_st + it * W_ELEMS, x_st + it * X_ELEMS);
     } else {
         for (int it = 0; it < nkt; ++it) {
@@ -195,6 +203,7 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
             else if (later == 6) cp_wait<6>();
             else cp_wait<7>();
             __syncthreads();
+            if (it == 0) TIS_STAMP(p, 3);
             const int nx = it + STAGES - 1;        // the stage of tile it-1 is free now
             if (nx < nkt) {
                 load_w(w_st + (nx % STAGES) * W_ELEMS, p, k_begin + nx * BK, k_end, n0, tid);
@@ -212,11 +221,15 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int ch = 0; ch < CHAINS - 1; ++ch) acc[m][j][i] += accs[ch][m][j][i];
+    TIS_STAMP(p, 4);
     cp_wait<0>();
+    factors.finish(p.e, row_factor, tid);
     __syncthreads();                    // row_factor is written (also when this CTA had no tile)
     cluster_reduce::cluster_wait();     // every CTA of the cluster has initialised its barrier
+    TIS_STAMP(p, 5);
     cluster_reduce::push_reduce_store<MT>(acc, p.e, recv, &recv_bar, pair, row_factor, rank, ksplit, blockIdx.x,
                                           gridDim.x, tid);
+    TIS_STAMP(p, 6);
 }
 
 }  // namespace
@@ -271,6 +284,7 @@ TIS_API int tis_gemm_skinny_fused(const void* x, int ldx, const void* w, int ldw
     p.e.out = (bf16*)out; p.e.ldo = ldo; p.e.M = M; p.e.N = N; p.e.epi = epi;
     p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_factor = norm_factor(in_kind, in_width, in_eps);
     p.e.res = res; p.e.ldr = ldr; p.e.norm_w = norm_w; p.e.out_ss = out_ss; p.e.fault = fault;
+    TIS_TIMELINE_TAKE(p);
     p.kc = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
     const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
     const int tiles = p.kc / BK;

@@ -15,6 +15,7 @@
 // The epilogues are those of gemm_skinny.cu, the residual epilogue and the norm's factor per row among them.
 #include "tc_common.cuh"
 #include "cluster_reduce.cuh"
+#include "timeline.cuh"
 #include <cooperative_groups.h>
 
 namespace {
@@ -37,6 +38,7 @@ struct StreamParams {
     int kc;                       // rows of K per CTA of a cluster (a multiple of BK)
     int boxes;                    // boxes in shared memory: min(kc / BK, MAX_BOXES)
     cluster_reduce::Epilogue e;   // rows, columns, where the result goes, the fault word
+    TIS_TIMELINE_MEMBER           // (instrumented builds only; stamps as in gemm_skinny.cu: 3 = first box landed)
 };
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
     const int k_end = min(p.K, k_begin + p.kc);
     const int nkt = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
 
+    TIS_STAMP(p, 0);
     asm volatile("griddepcontrol.launch_dependents;\n" ::);
     if (tid == 0) {
         abort_flag = 0;
@@ -105,6 +108,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
             for (int ch = 0; ch < CHAINS - 1; ++ch) accs[ch][m][j][0] = accs[ch][m][j][1] = accs[ch][m][j][2] = accs[ch][m][j][3] = 0.f;
         }
 
+    cluster_reduce::RowFactorLoads factors;
     if (producer) {
         // weights depend on nothing: no wait for the kernel before.  Box `it` goes to slot it % boxes, once
         // every consumer warp is done with the box that was there a round earlier.
@@ -122,7 +126,9 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
         }
     } else {
     // x is the output of the kernel before this one
+    TIS_STAMP(p, 1);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    TIS_STAMP(p, 2);
     {
         const int kw = nkt * BK;                   // columns of xs that the loop reads
         const int per_row = kw / 8;
@@ -133,8 +139,8 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
             cp16(xs + (size_t)r * xrow + c, ok ? p.x + (size_t)r * p.ldx + k : p.x, ok ? 16 : 0);
         }
         asm volatile("cp.async.commit_group;\n" ::);
-        // the norm's factor of each row, from the partial sums the kernel before left
-        cluster_reduce::load_row_factors(p.e, row_factor, warp, lane);
+        // the norm's factor of each row, from the partial sums the kernel before left: the loads now, the rest after the loop
+        factors.order(p.e, row_factor, tid);
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     asm volatile("bar.sync 1, 128;\n" ::: "memory");          // xs is visible to every consumer warp
@@ -148,6 +154,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
         const int b = it % p.boxes;
         if (alive) alive = mbar_wait(&bars[b], (unsigned)((it / p.boxes) & 1), &abort_flag, p.e.fault, 6);
         if (!alive) continue;                      // a wait ran out: no more waits, the result is not to be used
+        if (it == 0) TIS_STAMP(p, 3);
         const unsigned box = w_base + (unsigned)b * (BOX_SM * 2);
         // all fragments of the box first, then independent chains of accumulators (one per k16 step for up to
         // 16 rows, two otherwise): the latency of a step is not paid once per step
@@ -189,11 +196,16 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int ch = 0; ch < CHAINS - 1; ++ch) acc[m][j][i] += accs[ch][m][j][i];
+    TIS_STAMP(p, 4);
+    factors.finish(p.e, row_factor, tid);
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");          // row_factor is written
     }   // consumers
     cluster_reduce::cluster_wait();         // every CTA of the cluster has initialised its barrier
+    TIS_STAMP(p, 5);
     if (!producer)
         cluster_reduce::push_reduce_store<MT>(acc, p.e, recv, &recv_bar, pair, row_factor, rank, ksplit, blockIdx.x,
                                               gridDim.x, tid);
+    TIS_STAMP(p, 6);
 }
 
 }  // namespace
@@ -247,6 +259,7 @@ TIS_API int tis_gemm_stream_fused(const void* x, int ldx, const void* w, int ldw
     p.e.out = (bf16*)out; p.e.ldo = ldo; p.e.M = M; p.e.N = N; p.e.epi = epi; p.e.fault = fault;
     p.e.in_ss = in_ss; p.e.in_parts = in_parts; p.e.in_factor = norm_factor(in_kind, in_width, in_eps);
     p.e.res = res; p.e.ldr = ldr; p.e.norm_w = norm_w; p.e.out_ss = out_ss;
+    TIS_TIMELINE_TAKE(p);
     p.kc = ((K + ksplit - 1) / ksplit + BK - 1) / BK * BK;
     const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
     const int tiles = p.kc / BK;

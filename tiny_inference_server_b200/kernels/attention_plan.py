@@ -31,10 +31,11 @@ class TileSet:
     tiles are the first ``rows_in_wide`` of ``rows``, so a caller runs either ``wide`` and the
     rest of ``rows``, or all of ``rows``."""
 
-    def __init__(self, keys, rows, keys_max_rows: int = 0, wide=None, rows_in_wide: int = 0):
+    def __init__(self, keys, rows, keys_max_rows: int = 0, wide=None, rows_in_wide: int = 0, keys_identity: bool = False):
         self.keys = keys
         self.rows = rows
         self.keys_max_rows = keys_max_rows      # the most rows of any ``keys`` tile (0: not known)
+        self.keys_identity = keys_identity      # ``keys`` tile i is row i alone (a decode step): a kernel need not read the arrays
         self.wide = wide if wide is not None else (None, None, 0)
         self.rows_in_wide = rows_in_wide
 
@@ -77,19 +78,21 @@ class AttentionTilePlanner(StepPlanner):
         arrays = {"k0": [t[0] for t in keys], "kn": [t[1] for t in keys],
                   "r0": [t[0] for t in rows], "rn": [t[1] for t in rows],
                   "w0": [t[0] for t in wide], "wn": [t[1] for t in wide]}
-        facts = (len(keys), len(rows), max((t[1] for t in keys), default=0), len(wide), rows_in_wide)
+        # (the last fact: the keys tiles are the step's rows, one each and in order, and there are no others)
+        identity = bool(keys) and not rows and not wide and all(t == (i, 1) for i, t in enumerate(keys))
+        facts = (len(keys), len(rows), max((t[1] for t in keys), default=0), len(wide), rows_in_wide, identity)
         return arrays, facts
 
     def plan_decode(self, rows: int):
         idx, ones = list(range(rows)), [1] * rows
         if self.group_size <= 16:
-            return {"k0": idx, "kn": ones, "r0": [], "rn": [], "w0": [], "wn": []}, (rows, 0, 1, 0, 0)
-        return {"k0": [], "kn": [], "r0": idx, "rn": ones, "w0": [], "wn": []}, (0, rows, 0, 0, 0)
+            return {"k0": idx, "kn": ones, "r0": [], "rn": [], "w0": [], "wn": []}, (rows, 0, 1, 0, 0, True)
+        return {"k0": [], "kn": [], "r0": idx, "rn": ones, "w0": [], "wn": []}, (0, rows, 0, 0, 0, False)
 
     def bind(self, arrays: Dict[str, torch.Tensor], facts) -> TileSet:
-        nk, nr, kmax, nw, nrw = facts
+        nk, nr, kmax, nw, nrw = facts[:5]
         return TileSet((arrays["k0"], arrays["kn"], nk), (arrays["r0"], arrays["rn"], nr), kmax,
-                       (arrays["w0"], arrays["wn"], nw), nrw)
+                       (arrays["w0"], arrays["wn"], nw), nrw, keys_identity=len(facts) > 5 and bool(facts[5]))
 
 
 _planners: Dict[int, AttentionTilePlanner] = {}

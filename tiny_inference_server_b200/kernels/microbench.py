@@ -238,9 +238,98 @@ def prefill(args):
         r.release(s)
 
 
+def timeline(args):
+    """Where the time of a decode layer goes, from inside its kernels: the five launches of a layer (qkv, attention,
+    o, gate/up, down — as the engine chains them, norms folded into the products) replayed from a graph of
+    ``--layers`` layers, in a build of the kernels that stamps the global timer at named places (csrc/timeline.cuh;
+    compiled for this command only).  Printed for a layer in the middle: per kernel and place the first, median
+    and last CTA, in ns after the last CTA of the kernel before stored its result."""
+    from . import build
+    from .attention_plan import infer_tiles
+    if "-DTIS_TIMELINE" not in build.NVCC_FLAGS:
+        build.NVCC_FLAGS.append("-DTIS_TIMELINE")            # before the libraries are first asked for
+    dev = "cuda"
+    d, F, H, KVH, hd, page, ctx, B, L = (args.width, args.ffn, args.heads, args.kv_heads, args.head_dim, args.page_size,
+                                         args.context, args.batch, args.layers)
+    lib, alib = ops.library(), ops.attention_library(hd)
+    slots = lib.tis_timeline_slots()
+    pages_per = (ctx + page - 1) // page
+    planes = [torch.randn(B * pages_per, 2, KVH, page, hd, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).reshape(B, pages_per).contiguous()
+    positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    rows_slot = torch.arange(B, dtype=torch.int32, device=dev)
+    step = _Step(infer_tiles(positions, rows_slot, H // KVH), ctx - 1)
+    rotary = (torch.ones(ctx, hd // 2, device=dev), torch.zeros(ctx, hd // 2, device=dev))
+    fault = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def w(k, n):
+        return [torch.randn(k, n, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(L)]
+    w_qkv, w_o, w_gu, w_down = w(d, (H + 2 * KVH) * hd), w(H * hd, d), w(d, 2 * F), w(F, d)
+    norm_w = torch.ones(d, device=dev)
+    stream = torch.randn(B, d, device=dev)
+    names = ("qkv", "attention", "o", "gate/up", "down")
+    max_ctas = 1024
+    stamps = torch.zeros(L * 5, max_ctas * slots, dtype=torch.int64, device=dev)
+    attn_out = torch.empty(B, H * hd, device=dev, dtype=torch.bfloat16)
+
+    def layer(l, x):
+        lib.tis_timeline_next(ops._p(stamps[l * 5 + 0]))
+        qkv = ops.gemm(x, w_qkv[l])
+        alib.tis_timeline_next(ops._p(stamps[l * 5 + 1]))
+        ops.paged_attention(qkv, attn_out, planes[l], table, positions, rows_slot, H, KVH, hd, page, None, fault, step,
+                            rotary=rotary)
+        lib.tis_timeline_next(ops._p(stamps[l * 5 + 2]))
+        a = ops.gemm(attn_out, w_o[l], sink=ops.ResidualSink(stream, norm_w, 1e-6))
+        lib.tis_timeline_next(ops._p(stamps[l * 5 + 3]))
+        h = ops.gemm_swiglu(a, w_gu[l], F, 32)
+        lib.tis_timeline_next(ops._p(stamps[l * 5 + 4]))
+        return ops.gemm(h, w_down[l], sink=ops.ResidualSink(stream, norm_w, 1e-6))
+
+    def run():
+        x = ops.ScaledRows(torch.randn(B, d, device=dev, dtype=torch.bfloat16),
+                           torch.ones(B, (d + 63) // 64, device=dev), 1e-6)
+        for l in range(L):
+            x = layer(l, x)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        stamps.zero_()
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    print(f"decode layer, {B} rows, context {ctx}: {e0.elapsed_time(e1) / L * 1e3:.2f} us a layer with the stamps "
+          f"(fault words {fault.tolist()})")
+    t = stamps.cpu().reshape(L * 5, max_ctas, slots)
+    places = {
+        "gemm": ("entry", "weights ordered", "dependency wait over", "first tile ready", "loop done", "cluster barrier passed",
+                 "stored"),
+        "attention": ("entry", "before the dependency wait", "dependency wait over", "first tile landed", "last tile landed",
+                      "loop done", "partial results pushed", "partials of the cluster arrived", "stored"),
+    }
+    mid = L // 2
+    prev = t[mid * 5 - 1]
+    prev_end = int(prev[prev[:, 0] > 0].max())
+    for k in range(5):
+        rec = t[mid * 5 + k]
+        rec = rec[rec[:, 0] > 0]
+        kind = places["attention" if k == 1 else "gemm"]
+        print(f"{names[k]} ({rec.shape[0]} CTAs): ns after the last CTA of the kernel before stored (first / median / last CTA)")
+        for i, place in enumerate(kind):
+            v = rec[:, i]
+            v = v[v > 0] - prev_end
+            if v.numel():
+                print(f"  {place:32s} {int(v.min()):8d} {int(v.median()):8d} {int(v.max()):8d}")
+        prev_end = int(rec[:, len(kind) - 1].max())
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "all"])
+    ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "timeline", "all"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
@@ -258,6 +347,10 @@ def main(argv=None):
     ap.add_argument("--no-timing", action="store_true")
     ap.add_argument("--rotary", action="store_true", help="attention: rotary encoding and cache write inside the kernel")
     args = ap.parse_args(argv)
+    if args.what == "timeline":
+        if args.layers < 2:
+            ap.error("timeline: at least two layers (the printed one has a layer before it)")
+        return timeline(args) or 0
     ops.library()
     if args.what in ("attention", "all"):
         for b in ([args.batch] if args.what == "attention" else [1, 8, 64]):

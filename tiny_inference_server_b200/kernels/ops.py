@@ -725,6 +725,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, plane: torch.Tensor, blo
         per, splits = plan_splits(count, kv_heads, max_kv, True, resident, None)
         calls["attn_keys_rotary"] += 1
         cos, sin = rotary
+        if getattr(tiles, "keys_identity", False) and count == n:
+            row0 = rows = None          # tile i is row i: the kernel reads no tile arrays
         _check(alib.tis_attn_decode_rope(_p(q), q.stride(0), _p(out), out.stride(0), _p(plane), _p(block_table),
                                          block_table.stride(0), plane.shape[0], _p(positions), _p(row_slot), _p(row0),
                                          _p(rows), count, n, num_heads, kv_heads, page_size, int(window or 0),
