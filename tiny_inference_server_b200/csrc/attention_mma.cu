@@ -834,6 +834,10 @@ attn_decode_kernel(const AttnParams p) {
         mbar_arrive_expect_tx(&merge_bar, own_blocks ? (int)ns * pairs * (own_blocks * 8 + 2) * 4 : 0);
     }
     cluster_reduce::cluster_arrive();        // waited for before the first push: by then every CTA's barrier is ready
+    // what a thread needs of the last row of the tile does not depend on which rows are valid: its loads go out
+    // together with the one that finds the first valid row, not after it (a CTA that starts late has its first copy
+    // a trip to the L2 cache earlier)
+    const int slot_last = p.row_slot[row0 + rows - 1], pos_last_early = p.positions[row0 + rows - 1];
     if (warp == 0) {
         const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
         const unsigned b0 = __ballot_sync(0xffffffffu, v0);
@@ -858,8 +862,9 @@ attn_decode_kernel(const AttnParams p) {
     }
     int range_lo = 0, range_hi = 0, slot = -1;
     if (first >= 0) {
-        slot = p.row_slot[row0 + rows - 1];
-        const int pos_first = p.positions[row0 + first], pos_last = p.positions[row0 + rows - 1];
+        slot = slot_last;
+        const int pos_last = pos_last_early;
+        const int pos_first = first == rows - 1 ? pos_last : p.positions[row0 + first];
         range_hi = pos_last + 1;
         range_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
         range_lo = max(range_lo, split * p.keys_per_split);
