@@ -69,6 +69,7 @@ struct AttnParams {
                             // distributed shared memory: no scratch (2..8 splits); else scratch + merge kernel
     int* fault;
     int stages;             // stages of the copy pipeline (2..MAX_STAGES)
+    int recv_offset;        // bytes from the start of shared memory to where the cluster's partial results land
     // rotary encoding and cache write done by this kernel (decode rows; see FUSED below)
     const float* rope_cos; const float* rope_sin;   // [positions][HD/2]
     bf16* plane_w;          // the plane, writable: where the row's key and value go (null: another entry fills it)
@@ -212,6 +213,119 @@ __device__ __forceinline__ void load_tile(bf16* stage, unsigned long long* bar, 
 // row's page for later steps, and puts them into its staged tile in place of what the copy brought.
 // This kernel is then the only one of the step that writes the plane, so with `plane_w` set it may
 // order its first key tiles before it waits for the kernel before it.
+// The merge of the key splits of a (tile, kv head), for the 128 threads of a CTA that hold partial results
+// (warp w: a quarter of the keys of every tile).  First the four warps, through the staging area (every tile has
+// landed and been read): one partial result per query row.  Then over the splits by pushing (as the split-K sums of
+// the weight-streaming products, cluster_reduce.cuh): output dims are owned in blocks of eight, block d by rank
+// d % splits; every CTA sends its partial of a block to the owner (st.async, counted on the owner's mbarrier), the
+// owner combines the partials of the splits from its own shared memory and writes the output.  No cluster barrier
+// after the loop, no remote load, and a CTA leaves when it has what it owns.  Before the kernel's loop:
+// merge_barrier_init by one thread, then cluster_arrive by all.
+struct MergeShape {
+    unsigned ns, rank;          // splits (CTAs of the cluster), this CTA's
+    int pairs;                  // query rows of the tile: rows * G
+    int own_blocks;             // blocks of eight dims this rank owns
+    int OW;                     // floats a query row of a split takes at an owner
+};
+__device__ __forceinline__ MergeShape merge_shape(int num_splits, int split, int rows, int G) {
+    MergeShape ms;
+    ms.ns = (unsigned)num_splits; ms.rank = (unsigned)split;
+    ms.pairs = rows * G;
+    ms.own_blocks = split < DTILES ? (DTILES - 1 - split) / num_splits + 1 : 0;
+    ms.OW = ((DTILES + num_splits - 1) / num_splits) * 8 + 4;
+    return ms;
+}
+__device__ __forceinline__ void merge_barrier_init(unsigned long long* merge_bar, const MergeShape& ms) {
+    mbar_init(merge_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // from each split and for each query row: its blocks, the row's maximum and sum
+    mbar_arrive_expect_tx(merge_bar, ms.own_blocks ? (int)ms.ns * ms.pairs * (ms.own_blocks * 8 + 2) * 4 : 0);
+}
+
+template <int NR>
+__device__ __forceinline__ void merge_splits_by_pushing(const AttnParams& p, unsigned char* smem_raw, float* recv,
+                                                        unsigned long long* merge_bar, const MergeShape& ms,
+                                                        const float (&o)[DTILES][4], const float (&m_run)[2],
+                                                        const float (&l_run)[2], int G, int row0, int kvh) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g_lane = lane >> 2, t_lane = lane & 3;
+    const unsigned ns = ms.ns, rank = ms.rank;
+    const int pairs = ms.pairs, own_blocks = ms.own_blocks, OW = ms.OW;
+    TIS_STAMP(p, 5);
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    constexpr int HDP = HD + 4;
+    float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
+    float* mm = mo + 4 * 16 * HDP;                           // [4][16]
+    float* ml = mm + 4 * 16;                                 // [4][16]
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int m = g_lane + 8 * i;
+        if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d)
+            *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    cluster_reduce::cluster_wait();
+    const unsigned recv_base = cluster_reduce::shared_addr(recv), bar_base = cluster_reduce::shared_addr(merge_bar);
+    constexpr int QUADS = HD / 4;                            // groups of four dims of a query row
+    for (int u = tid; u < pairs * QUADS; u += NTHREADS) {
+        const int m = u / QUADS, q = u - m * QUADS;
+        float mw[4], mt = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { mw[w] = mm[w * 16 + m]; mt = fmaxf(mt, mw[w]); }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - mt);
+            const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + m) * HDP + 4 * q);
+            lsum += ml[w * 16 + m] * f;
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+        const int block = q >> 1;
+        const unsigned owner = (unsigned)block % ns;
+        const unsigned at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + (block / (int)ns) * 8 + (q & 1) * 4) * 4);
+        asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];\n"
+                     ::"r"(cluster_reduce::map_to_rank(at, owner)), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w),
+                       "r"(cluster_reduce::map_to_rank(bar_base, owner)) : "memory");
+        // the row's maximum and sum go to every rank that owns a block: quad q sends them to rank q
+        if (q < (int)ns && q < DTILES) {
+            const unsigned ml_at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + OW - 4) * 4);
+            asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];\n"
+                         ::"r"(cluster_reduce::map_to_rank(ml_at, (unsigned)q)), "f"(mt), "f"(lsum),
+                           "r"(cluster_reduce::map_to_rank(bar_base, (unsigned)q)) : "memory");
+        }
+    }
+    TIS_STAMP(p, 6);
+    mbar_wait_cluster(merge_bar, 0u, p.fault);              // bounded
+    TIS_STAMP(p, 7);
+    const int own_dims = own_blocks * 8;
+    for (int idx = tid; idx < pairs * own_dims; idx += NTHREADS) {
+        const int m = idx / own_dims, c = idx - m * own_dims;
+        const int d = ((c >> 3) * (int)ns + (int)rank) * 8 + (c & 7);
+        const int r = m / G, g = m - r * G;
+        const float* from = recv + m * OW;
+        const int step_sp = pairs * OW;
+        float mt = -INFINITY;
+#pragma unroll 8
+        for (unsigned sp = 0; sp < ns; ++sp) mt = fmaxf(mt, from[sp * step_sp + OW - 4]);
+        float acc = 0.f, lsum = 0.f;
+        if (mt != -INFINITY) {
+#pragma unroll 8
+            for (unsigned sp = 0; sp < ns; ++sp) {
+                const float msp = from[sp * step_sp + OW - 4];
+                const float f = msp == -INFINITY ? 0.f : fast_exp2(msp - mt);
+                lsum += from[sp * step_sp + OW - 3] * f;
+                acc += from[sp * step_sp + c] * f;
+            }
+        }
+        p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
+            __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    }
+    TIS_STAMP(p, 8);
+}
+
 template <int MODE, int NR, int NG, bool FUSED = false>
 __global__ void __launch_bounds__(NTHREADS * NG)
 attn_mma_kernel(const AttnParams p) {
@@ -223,6 +337,7 @@ attn_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int sh_first;
     __shared__ __align__(8) unsigned long long bars_all[NG * MAX_STAGES];
+    __shared__ __align__(8) unsigned long long merge_bar;
     const int STAGES = p.stages;
 
     pdl_launch_dependents();         // tiles, slots, positions and block tables below are step metadata,
@@ -244,6 +359,15 @@ attn_mma_kernel(const AttnParams p) {
     if (threadIdx.x == 0) {
         for (int st = 0; st < NG * STAGES; ++st) mbar_init(&bars_all[st], NTHREADS);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // key splits that are one cluster merge by pushing (merge_splits_by_pushing): what the cluster sends this CTA
+    // lands behind the stages
+    const bool pushed_merge = MODE == MODE_KEYS && p.num_splits > 1 && p.cluster_merge;
+    const MergeShape ms = merge_shape(p.num_splits, split, rows, G);
+    float* recv = reinterpret_cast<float*>(smem_raw + p.recv_offset);
+    if (pushed_merge) {
+        if (threadIdx.x == 0) merge_barrier_init(&merge_bar, ms);
+        cluster_reduce::cluster_arrive();        // waited for before the first push
     }
     if (warp == 0 && grp == 0) {
         const bool v0 = lane < rows && p.row_slot[row0 + lane] >= 0;
@@ -572,60 +696,8 @@ attn_mma_kernel(const AttnParams p) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
 
-    if (MODE == MODE_KEYS && p.num_splits > 1 && p.cluster_merge) {
-        // The splits of this (tile, kv head) are the CTAs of one cluster.  Every warp of every split
-        // leaves its unnormalised partial result (maximum, sum, outputs) in its CTA's shared memory; after
-        // one cluster barrier every CTA merges its share of the output elements over all of them, reading
-        // the other CTAs' shared memory: one merge instead of one per CTA and one per cluster.
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        constexpr int HDP = HD + 4;                              // padded rows: fewer bank conflicts on the way in
-        __syncthreads();                                         // the staging area is free
-        float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
-        float* mm = mo + 4 * 16 * HDP;                           // [4][16]
-        float* ml = mm + 4 * 16;                                 // [4][16]
-#pragma unroll
-        for (int i = 0; i < NR; ++i) {
-            const int m = g_lane + 8 * i;
-            if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
-            if (m_run[i] != -INFINITY) {
-#pragma unroll
-                for (int d = 0; d < DTILES; ++d)
-                    *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
-            }
-        }
-        cluster.sync();
-        const int ns = p.num_splits;
-        const int pairs = rows * G;
-        for (int idx = (int)cluster.block_rank() * NTHREADS + tid; idx < pairs * HD; idx += ns * NTHREADS) {
-            const int m = idx / HD, d = idx - m * HD;
-            const int r = m / G, g = m - r * G;
-            float mt = -INFINITY;
-            for (int sp = 0; sp < ns; ++sp) {
-                const float* rm = cluster.map_shared_rank(mm, sp);
-#pragma unroll
-                for (int w = 0; w < 4; ++w) mt = fmaxf(mt, rm[w * 16 + m]);
-            }
-            float acc = 0.f, lsum = 0.f;
-            if (mt != -INFINITY) {
-                for (int sp = 0; sp < ns; ++sp) {
-                    const float* rm = cluster.map_shared_rank(mm, sp);
-                    const float* rl = cluster.map_shared_rank(ml, sp);
-                    const float* ro = cluster.map_shared_rank(mo, sp);
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const float mw = rm[w * 16 + m];
-                        if (mw == -INFINITY) continue;
-                        const float f = fast_exp2(mw - mt);
-                        lsum += rl[w * 16 + m] * f;
-                        acc += ro[(w * 16 + m) * HDP + d] * f;
-                    }
-                }
-            }
-            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
-                __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
-        }
-        cluster.sync();                  // nobody leaves while its shared memory may still be read
+    if (pushed_merge) {
+        merge_splits_by_pushing<NR>(p, smem_raw, recv, &merge_bar, ms, o, m_run, l_run, G, row0, kvh);
     } else if (MODE == MODE_KEYS) {
         // merge the four warps (each saw a quarter of the keys) through shared memory
         __syncthreads();
@@ -818,20 +890,12 @@ attn_decode_kernel(const AttnParams p) {
     const int row0 = p.tile_row0 != nullptr ? p.tile_row0[tile] : tile, rows = p.tile_rows != nullptr ? p.tile_rows[tile] : 1;
     const int G = p.G;
 
-    // The merge of the splits (see the end of the kernel): output dims are owned in blocks of eight, block d by
-    // rank d % splits.  Every CTA of the cluster pushes its partial result of a block to the block's owner; the
-    // owner expects, from each split and for each of the tile's rows * G query rows, its blocks and the row's
-    // maximum and sum.
-    const unsigned ns = (unsigned)p.num_splits, rank = (unsigned)split;
-    const int pairs = rows * G;
-    const int own_blocks = (int)rank < DTILES ? (DTILES - 1 - (int)rank) / (int)ns + 1 : 0;
-    const int OW = ((DTILES + (int)ns - 1) / (int)ns) * 8 + 4;       // floats a query row of a split takes at an owner
-    float* recv = reinterpret_cast<float*>(smem_raw + (size_t)STAGES * STAGE_ELEMS * sizeof(bf16));
+    // the merge of the splits (merge_splits_by_pushing): the barrier that counts what the cluster sends this CTA
+    const MergeShape ms = merge_shape(p.num_splits, split, rows, G);
+    float* recv = reinterpret_cast<float*>(smem_raw + p.recv_offset);
     if (tid == 0) {
         for (int st = 0; st < STAGES; ++st) { mbar_init(&full[st], 32); mbar_init(&empty[st], NTHREADS / 32); }
-        mbar_init(&merge_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        mbar_arrive_expect_tx(&merge_bar, own_blocks ? (int)ns * pairs * (own_blocks * 8 + 2) * 4 : 0);
+        merge_barrier_init(&merge_bar, ms);
     }
     cluster_reduce::cluster_arrive();        // waited for before the first push: by then every CTA's barrier is ready
     // what a thread needs of the last row of the tile does not depend on which rows are valid: its loads go out
@@ -1091,85 +1155,7 @@ attn_decode_kernel(const AttnParams p) {
             l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
             l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
         }
-        // Merge.  First the four warps of this CTA, through the staging area (every tile has landed and been read):
-        // one partial result per query row.  Then over the splits by pushing (as the split-K sums of the
-        // weight-streaming products, cluster_reduce.cuh): output dims are owned in blocks of eight, block d by
-        // rank d % splits; every CTA sends its partial of a block to the owner (st.async, counted on the owner's
-        // mbarrier), the owner combines the partials of the splits from its own shared memory and writes the
-        // output.  No cluster barrier after the loop, no remote load, and a CTA leaves when it has what it owns.
-        TIS_STAMP(p, 5);
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        constexpr int HDP = HD + 4;
-        float* mo = reinterpret_cast<float*>(smem_raw);          // [4][16][HDP]
-        float* mm = mo + 4 * 16 * HDP;                           // [4][16]
-        float* ml = mm + 4 * 16;                                 // [4][16]
-#pragma unroll
-        for (int i = 0; i < NR; ++i) {
-            const int m = g_lane + 8 * i;
-            if (t_lane == 0) { mm[warp * 16 + m] = m_run[i]; ml[warp * 16 + m] = l_run[i]; }
-#pragma unroll
-            for (int d = 0; d < DTILES; ++d)
-                *reinterpret_cast<float2*>(mo + (warp * 16 + m) * HDP + d * 8 + 2 * t_lane) = make_float2(o[d][2 * i], o[d][2 * i + 1]);
-        }
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        cluster_reduce::cluster_wait();
-        const unsigned recv_base = cluster_reduce::shared_addr(recv), bar_base = cluster_reduce::shared_addr(&merge_bar);
-        constexpr int QUADS = HD / 4;                            // groups of four dims of a query row
-        for (int u = tid; u < pairs * QUADS; u += NTHREADS) {
-            const int m = u / QUADS, q = u - m * QUADS;
-            float mw[4], mt = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) { mw[w] = mm[w * 16 + m]; mt = fmaxf(mt, mw[w]); }
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float lsum = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float f = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - mt);
-                const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + m) * HDP + 4 * q);
-                lsum += ml[w * 16 + m] * f;
-                acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
-            }
-            const int block = q >> 1;
-            const unsigned owner = (unsigned)block % ns;
-            const unsigned at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + (block / (int)ns) * 8 + (q & 1) * 4) * 4);
-            asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];\n"
-                         ::"r"(cluster_reduce::map_to_rank(at, owner)), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w),
-                           "r"(cluster_reduce::map_to_rank(bar_base, owner)) : "memory");
-            // the row's maximum and sum go to every rank that owns a block: quad q sends them to rank q
-            if (q < (int)ns && q < DTILES) {
-                const unsigned ml_at = recv_base + (unsigned)((((int)rank * pairs + m) * OW + OW - 4) * 4);
-                asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];\n"
-                             ::"r"(cluster_reduce::map_to_rank(ml_at, (unsigned)q)), "f"(mt), "f"(lsum),
-                               "r"(cluster_reduce::map_to_rank(bar_base, (unsigned)q)) : "memory");
-            }
-        }
-        TIS_STAMP(p, 6);
-        mbar_wait_cluster(&merge_bar, 0u, p.fault);              // bounded
-        TIS_STAMP(p, 7);
-        const int own_dims = own_blocks * 8;
-        for (int idx = tid; idx < pairs * own_dims; idx += NTHREADS) {
-            const int m = idx / own_dims, c = idx - m * own_dims;
-            const int d = ((c >> 3) * (int)ns + (int)rank) * 8 + (c & 7);
-            const int r = m / G, g = m - r * G;
-            const float* from = recv + m * OW;
-            const int step_sp = pairs * OW;
-            float mt = -INFINITY;
-#pragma unroll 8
-            for (unsigned sp = 0; sp < ns; ++sp) mt = fmaxf(mt, from[sp * step_sp + OW - 4]);
-            float acc = 0.f, lsum = 0.f;
-            if (mt != -INFINITY) {
-#pragma unroll 8
-                for (unsigned sp = 0; sp < ns; ++sp) {
-                    const float msp = from[sp * step_sp + OW - 4];
-                    const float f = msp == -INFINITY ? 0.f : fast_exp2(msp - mt);
-                    lsum += from[sp * step_sp + OW - 3] * f;
-                    acc += from[sp * step_sp + c] * f;
-                }
-            }
-            p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(kvh * G + g) * HD + d] =
-                __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
-        }
-        TIS_STAMP(p, 8);
+        merge_splits_by_pushing<NR>(p, smem_raw, recv, &merge_bar, ms, o, m_run, l_run, G, row0, kvh);
     }
 }
 
@@ -1314,7 +1300,7 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
     // the kernel with a producer warp also keeps, beside the stages, what the cluster pushes to it for the merge:
     // from each split, for each query row of a tile, its output blocks, the row's maximum and sum
     size_t recv_bytes = 0;
-    if (warp_specialised) {
+    if (warp_specialised || (mode == MODE_KEYS && p.cluster_merge)) {
         const int pairs = max_tile_rows > 0 ? max_tile_rows * G : 16;
         recv_bytes = (size_t)num_splits * pairs * (((HD / 8 + num_splits - 1) / num_splits) * 8 + 4) * sizeof(float);
     }
@@ -1324,7 +1310,7 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         const long long ctas = (long long)num_tiles * KVH * num_splits;
         const int tiles_per_split = keys_per_split / KT;
         for (int cand = 3; cand <= MAX_STAGES; ++cand) {
-            const size_t need = warp_specialised ? (size_t)cand * STAGE_BYTES + recv_bytes : smem_bytes(MODE_KEYS, cand);
+            const size_t need = (warp_specialised ? (size_t)cand * STAGE_BYTES : smem_bytes(MODE_KEYS, cand)) + recv_bytes;
             if (need > 220 * 1024 || cand - 1 > tiles_per_split) break;
             // the kernel with a producer warp: no more stages than a split has tiles (shared memory that it leaves
             // free lets its CTAs start beside those of the product before it, and order their tiles, earlier)
@@ -1336,7 +1322,10 @@ static int attn_launch(int mode, const void* q, int q_stride, void* out, int out
         }
     }
     p.stages = stages;
-    const size_t smem = warp_specialised ? (size_t)stages * STAGE_BYTES + recv_bytes : smem_bytes(mode, stages);
+    // the partial results of the cluster land behind the stages (and behind what the four warps of a CTA merge in)
+    const size_t front = warp_specialised ? (size_t)stages * STAGE_BYTES : smem_bytes(mode, stages);
+    p.recv_offset = (int)front;
+    const size_t smem = front + recv_bytes;
     if (smem > 220 * 1024) {
         tis_set_error("attention: %d stages and the merge of %d splits need %zu bytes of shared memory", stages, num_splits, smem);
         return TIS_BAD_SIZE;
