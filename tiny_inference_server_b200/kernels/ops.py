@@ -96,11 +96,12 @@ def _f(x: float):
 # ---------------------------------------------------------------------------------------
 
 #: rows up to which bfloat16 products go to the weight-streaming kernels of this library instead of the library
-#: product.  Measured inside the decode step of the 0.9B model on a B200 (ms a step, limit 4 / 8 / 16): batch 5
-#: 1.365 / 1.341, batch 8 1.384 / 1.361, batch 10 - / 1.548 / 1.568, batch 16 - / 1.639 / 1.657: up to eight rows the
-#: kernels of this library win, above the library's.  TIS_SKINNY_MAX_ROWS in the environment overrides it (0 sends
-#: everything to the library; the kernels themselves take up to 64 rows).
-SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "8"))
+#: product (and up to which a step's norms are folded into them).  Measured inside the decode step of the 0.9B model
+#: on a B200, ms a step with the limit at 8 / 16: batch 10 1.467 / 1.387, batch 12 1.491 / 1.397, batch 16
+#: 1.544 / 1.437; at 24 rows (tiles of 32 rows) 2.045 / 2.047: nothing.  (Before the reductions of these kernels were
+#: pushed and the norms folded in, the library won from 9 rows, and before that from 5.)  TIS_SKINNY_MAX_ROWS in the
+#: environment overrides it (0 sends everything to the library; the kernels themselves take up to 64 rows).
+SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "16"))
 #: the gate/up product with the gating in its epilogue saves a launch and the round trip of the
 #: ungated product: the kernel keeps it up to more rows (measured alone at 8 rows: 8.4 us against 9.1 us
 #: for the library product plus the gating kernel; inside the decode step at batch 8: 5123 -> 5207 tok/s)
