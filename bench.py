@@ -10,7 +10,7 @@ layer sizes of the upstream 0.9B model (30 layers, width 1536, 12 query and 3 kv
 one JSON line: decode tokens a second timed on the device with CUDA events (``value``),
 the same through the Python entry point with host tokens in and out (``e2e``), a prefill
 of 2048 tokens (replayed from the graph of its shape, and launched for the first time), the decode
-step's HBM roofline, decode at batch 1 and 64, at contexts 1024 and 8192 and with the two MTP heads
+step's HBM roofline, decode at batch 1, 16 and 64, at contexts 1024 and 8192 and with the two MTP heads
 running beside the trunk, and the same points for the 3B- and 8B-sized members of the family
 (``gqa_mtp_3b``, ``gqa_mtp_8b``: all their layers, context 8192, weights made on the device).
 The step reads ~1.6 GB of weights and ~1.5 GB of cache, far more than the 126 MB L2, so
@@ -437,7 +437,7 @@ def main(argv=None):
     if not args.no_points:
         points = {}
         half = max(8, args.steps // 2)
-        for b in (1, 64):
+        for b in (1, 16, 64):
             pms, _ = decode_run(runner, b, start_len, half, args.warmup, Sampler, count_ops)
             nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, b, CONTEXT)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
