@@ -684,7 +684,7 @@ def test_gemm(dtype, n, K, N):
 @pytest.mark.parametrize("n,K,N,kernel", [(5, 1536, 2304, "gemm_skinny"), (3, 4096, 4096, "gemm_skinny"),
                                           (8, 4096, 1536, "gemm_stream"), (5, 8192, 200, "gemm_swap"),
                                           (6, 14336, 4096, "gemm_swap"), (6, 3072, 5120, "gemm_library"),
-                                          (9, 1536, 2304, "gemm_skinny"), (17, 1536, 2304, "gemm_library")])
+                                          (9, 1536, 2304, "gemm_skinny"), (33, 1536, 2304, "gemm_library")])
 def test_few_rows_go_to_the_kernel_their_shape_calls_for(n, K, N, kernel):
     """Few bfloat16 rows: a short share of K per CTA goes to the ring (or, one round of boxes, to the TMA-fed kernel),
     a long share to the tcgen05 kernel with swapped operands when the matrix is tall, else to the library; with a

@@ -58,23 +58,34 @@ __device__ __forceinline__ void init_barrier(unsigned long long* bar, unsigned r
 
 // The norm's factor of each row, from the partial sums of squares the kernel before left, in two halves so that the
 // loads are not waited for before the loop: `RowFactorLoads::order` (consumer threads, after the dependency wait)
-// only issues the loads — eight lanes a row, sixteen rows at once, up to eight partial sums a lane — and
+// only issues the loads — all rows at once, eight, four or two lanes a row, up to eight partial sums a lane — and
 // `finish` (after the loop, before the barrier that precedes the epilogue) adds them up and writes the factors
-// to shared memory.  Rows or partial sums beyond that (more than 16 rows, more than 64 sums a row) are done at once
-// in `order`, a warp per row.
+// to shared memory.  More partial sums a row than that are added up at once in `order`, a warp per row.
+template <int MT>              // 16 * MT rows at most: the kernel for up to 16 rows has only its own case
 struct RowFactorLoads {
     float part[8];
-    bool deferred;
+    int shift;                  // a row is shared by 1 << shift lanes (3: up to 16 rows, 2: up to 32, 1: up to 64); 0: nothing deferred
     __device__ __forceinline__ void order(const Epilogue& e, float* row_factor, int tid) {
-        deferred = false;
+        shift = 0;
         if (e.in_ss == nullptr) return;
         const int warp = tid >> 5, lane = tid & 31;
-        if (e.M <= 16 && e.in_parts <= 64) {
-            deferred = true;
-            const int row = tid >> 3, l8 = tid & 7;
+        if (e.M <= 16 && e.in_parts <= 64) {          // the decode step's case, with constants
+            shift = 3;
+            const int row = tid >> 3, l = tid & 7;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int i = l8 + 8 * j;
+                const int i = l + 8 * j;
+                part[j] = (row < e.M && i < e.in_parts) ? e.in_ss[(size_t)row * e.in_parts + i] : 0.f;
+            }
+            return;
+        }
+        const int sh = e.M <= 32 ? 2 : 1;
+        if (MT > 1 && e.in_parts <= (8 << sh)) {
+            shift = sh;
+            const int row = tid >> sh, l = tid & ((1 << sh) - 1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = l + (j << sh);
                 part[j] = (row < e.M && i < e.in_parts) ? e.in_ss[(size_t)row * e.in_parts + i] : 0.f;
             }
             return;
@@ -87,14 +98,16 @@ struct RowFactorLoads {
         }
     }
     __device__ __forceinline__ void finish(const Epilogue& e, float* row_factor, int tid) const {
-        if (!deferred) return;                        // (the same for every consumer thread)
+        if (shift == 0) return;                       // (the same for every consumer thread)
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) s += part[j];
         s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if ((tid & 7) == 0 && (tid >> 3) < e.M) row_factor[tid >> 3] = e.in_factor.of(s);
+        if (MT == 1 || shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if (MT == 1 || shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
+        const int sh = MT == 1 ? 3 : shift;
+        const int row = tid >> sh;
+        if ((tid & ((1 << sh) - 1)) == 0 && row < e.M) row_factor[row] = e.in_factor.of(s);
     }
 };
 

@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
         cp_commit();                     // one group per tile: tile s is ready when all but pre-1-s groups are done
     }
     // the norm's factor of each row, from the partial sums the kernel before left: the loads now, the rest after the loop
-    cluster_reduce::RowFactorLoads factors;
+    cluster_reduce::RowFactorLoads<MT> factors;
     factors.order(p.e, row_factor, tid);
 
     float acc[MT][2][4];

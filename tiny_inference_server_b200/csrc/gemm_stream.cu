@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
             for (int ch = 0; ch < CHAINS - 1; ++ch) accs[ch][m][j][0] = accs[ch][m][j][1] = accs[ch][m][j][2] = accs[ch][m][j][3] = 0.f;
         }
 
-    cluster_reduce::RowFactorLoads factors;
+    cluster_reduce::RowFactorLoads<MT> factors;
     if (producer) {
         // weights depend on nothing: no wait for the kernel before.  Box `it` goes to slot it % boxes, once
         // every consumer warp is done with the box that was there a round earlier.

@@ -98,10 +98,11 @@ def _f(x: float):
 #: rows up to which bfloat16 products go to the weight-streaming kernels of this library instead of the library
 #: product (and up to which a step's norms are folded into them).  Measured inside the decode step of the 0.9B model
 #: on a B200, ms a step with the limit at 8 / 16: batch 10 1.467 / 1.387, batch 12 1.491 / 1.397, batch 16
-#: 1.544 / 1.437; at 24 rows (tiles of 32 rows) 2.045 / 2.047: nothing.  (Before the reductions of these kernels were
-#: pushed and the norms folded in, the library won from 9 rows, and before that from 5.)  TIS_SKINNY_MAX_ROWS in the
-#: environment overrides it (0 sends everything to the library; the kernels themselves take up to 64 rows).
-SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "16"))
+#: 1.544 / 1.437; at 16 / 32: batch 24 2.045 / 1.986, batch 32 2.132 / 2.068; at 64 rows the library wins by far
+#: (batch 64: 3.02 against 4.22 ms).  (Before the reductions of these kernels were pushed and the norms folded in,
+#: the library won from 9 rows, and before that from 5.)  TIS_SKINNY_MAX_ROWS in the environment overrides it
+#: (0 sends everything to the library; the kernels themselves take up to 64 rows).
+SKINNY_MAX_ROWS = int(os.environ.get("TIS_SKINNY_MAX_ROWS", "32"))
 #: the gate/up product with the gating in its epilogue saves a launch and the round trip of the
 #: ungated product: the kernel keeps it up to more rows (measured alone at 8 rows: 8.4 us against 9.1 us
 #: for the library product plus the gating kernel; inside the decode step at batch 8: 5123 -> 5207 tok/s)
@@ -224,7 +225,7 @@ STREAM_GEMM = os.environ.get("TIS_STREAM_GEMM", "1") != "0"
 STREAM_MIN_KC = int(os.environ.get("TIS_STREAM_MIN_KC", "512"))
 STREAM_MAX_KC = int(os.environ.get("TIS_STREAM_MAX_KC", "512"))
 STREAM_MAX_CTAS = int(os.environ.get("TIS_STREAM_MAX_CTAS", "296"))
-STREAM_MAX_ROWS = int(os.environ.get("TIS_STREAM_MAX_ROWS", "16"))
+STREAM_MAX_ROWS = int(os.environ.get("TIS_STREAM_MAX_ROWS", "32"))
 
 
 def _stream_pays(n: int, k: int, cols: int, ksplit: Optional[int] = None) -> bool:
