@@ -876,6 +876,7 @@ attn_decode_kernel(const AttnParams p) {
     constexpr int STAGE_ELEMS = 2 * KT * RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int sh_first;
+    __shared__ __align__(16) float rope_sh[FUSED ? HD : 4];           // the row's cosines, then its sines
     __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES], merge_bar;
     const int STAGES = p.stages;
 
@@ -975,6 +976,17 @@ attn_decode_kernel(const AttnParams p) {
                 }
             }
         }
+        // the angles of the row's position do not depend on the kernel before: the consumer warps bring them into
+        // shared memory while they would only wait (in registers they would not fit beside the queries)
+        if (FUSED && ntiles > 0) {
+            const int pos = p.positions[row0 + rows - 1];
+            for (int i = tid; i < HD / 4; i += NTHREADS) {              // HD / 2 cosines and as many sines, four a thread
+                const float* src = i < HD / 8 ? p.rope_cos + (size_t)pos * (HD / 2) + 4 * i
+                                              : p.rope_sin + (size_t)pos * (HD / 2) + 4 * (i - HD / 8);
+                *reinterpret_cast<float4*>(rope_sh + 4 * i) = *reinterpret_cast<const float4*>(src);
+            }
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
         TIS_STAMP(p, 1);
         pdl_wait();
         TIS_STAMP(p, 2);
@@ -995,9 +1007,8 @@ attn_decode_kernel(const AttnParams p) {
                 }
             }
             if (FUSED) {
-                const int pos = p.positions[row0 + rows - 1];
-                const float* cs = p.rope_cos + (size_t)pos * (HD / 2);
-                const float* sn = p.rope_sin + (size_t)pos * (HD / 2);
+                const float* cs = rope_sh;
+                const float* sn = rope_sh + HD / 2;
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS / 2; ++kk) {
 #pragma unroll
@@ -1037,8 +1048,8 @@ attn_decode_kernel(const AttnParams p) {
                         float x1[8], x2[8], o1[8], o2[8];
                         Vec16<bf16>::load(krow + c * 8, x1);
                         Vec16<bf16>::load(krow + HD / 2 + c * 8, x2);
-                        const float* cs = p.rope_cos + (size_t)own_pos * (HD / 2) + c * 8;
-                        const float* sn = p.rope_sin + (size_t)own_pos * (HD / 2) + c * 8;
+                        const float* cs = rope_sh + c * 8;                  // (the row's own position: the angles above)
+                        const float* sn = rope_sh + HD / 2 + c * 8;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
