@@ -876,7 +876,7 @@ attn_decode_kernel(const AttnParams p) {
     constexpr int STAGE_ELEMS = 2 * KT * RS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int sh_first;
-    __shared__ __align__(16) float rope_sh[FUSED ? HD : 4];           // the row's cosines, then its sines
+    __shared__ __align__(16) float rope_sh[HD];                       // FUSED: the row's cosines, then its sines
     __shared__ __align__(8) unsigned long long full[MAX_STAGES], empty[MAX_STAGES], merge_bar;
     const int STAGES = p.stages;
 
