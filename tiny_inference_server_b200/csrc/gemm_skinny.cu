@@ -147,8 +147,8 @@ __global__ void __launch_bounds__(NTH) gemm_skinny_kernel(const GemmParams p) {
         for (int j = 0; j < 2; ++j) { acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f; }
 
     // a tile's products: all fragments of the tile first, then independent chains of accumulators (one per
-    // k16 step for up to 16 rows, two otherwise), so that the latency of a step is not paid once per step
-    constexpr int CHAINS = MT == 1 ? BK / 16 : 2;
+    // k16 step for up to 32 rows, two otherwise), so that the latency of a step is not paid once per step
+    constexpr int CHAINS = MT <= 2 ? BK / 16 : 2;
     float accs[CHAINS - 1][MT][2][4];
 #pragma unroll
     for (int ch = 0; ch < CHAINS - 1; ++ch)

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
     __syncthreads();
     cluster_reduce::cluster_arrive();        // waited for after the loop: by then every CTA's barrier is ready
 
-    constexpr int CHAINS = MT == 1 ? BK / 16 : 2;          // independent chains of accumulators
+    constexpr int CHAINS = MT <= 2 ? BK / 16 : 2;          // independent chains of accumulators
     float acc[MT][2][4], accs[CHAINS - 1][MT][2][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(NTH + 32) gemm_stream_kernel(const __grid_cons
         if (it == 0) TIS_STAMP(p, 3);
         const unsigned box = w_base + (unsigned)b * (BOX_SM * 2);
         // all fragments of the box first, then independent chains of accumulators (one per k16 step for up to
-        // 16 rows, two otherwise): the latency of a step is not paid once per step
+        // 32 rows, two otherwise): the latency of a step is not paid once per step
         unsigned bf[BK / 16][4];
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
