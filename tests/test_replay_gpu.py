@@ -162,6 +162,45 @@ def test_decode_steps_of_up_to_64_rows(dtype, tmp_path, tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,live", [("A", 12), ("C", 24), ("E", 30), ("WIDE", 20)])
+def test_decode_steps_of_9_to_32_rows(name, live, dtype, tmp_path, tmp_path_factory, monkeypatch):
+    """Ten to thirty requests live at once: decode steps in the graph buckets of 16 and 32 rows.  In bfloat16 these
+    are the rows for which the norms are folded into the products of this library (tiles of 16 and of 32 rows, the
+    gating of 17..32 rows in the tcgen05 kernel with swapped operands) and the key splits of the lock-step attention
+    kernel merge by pushing; main and MTP logits at every position against the plain implementation."""
+    cfg, page, seed = tiny_configs.ALL[name]
+    folder = tiny_configs.make_model_folder(cfg, seed, str(tmp_path / "m"))
+    c, W = plain_model.read_config(folder), plain_model.read_weights(folder)
+    lengths = [3 + (5 * i) % 17 + 14 for i in range(live)]
+    prompts = tiny_configs.random_prompts(cfg["vocab_size"], lengths, seed=78)
+    seqs = {f"r{i}": p for i, p in enumerate(prompts)}
+    plain = {rid: plain_model.plain_forward(c, W, toks) for rid, toks in seqs.items()}
+    steps = trace_tools.trace_mixed(seqs, max_live=live, decode_from=0.3, skip_every=7)
+    rows = max(len(s["entries"]) for s in steps)
+    assert 8 < rows <= 32
+    runner = make_runner(folder, dtype, trace_tools.max_live_tokens(steps, round_to=64), page_size=page, mtp=True,
+                         max_live=32)
+    from tiny_inference_server_b200.kernels import ops
+    sinks = []
+    made = ops.ResidualSink.__init__
+    monkeypatch.setattr(ops.ResidualSink, "__init__", lambda self, *a, **k: (sinks.append(a[0].shape[0]), made(self, *a, **k))[1])
+    out_dir = str(tmp_path / "out")
+    TraceReplayer(runner, out_dir, write_aux=True).run(json.dumps(s) for s in steps)
+    runner.cache.check()
+    assert runner.cache.drained()
+    # bfloat16: steps of more than 8 rows had their norms folded into the products; float32: none
+    assert (max(sinks, default=0) > 8) == (dtype == "bfloat16"), sinks[:8]
+    bucket = 16 if rows <= 16 else 32
+    assert any(key[0] == bucket and g.graph is not None for key, g in runner.graphs.graphs.items()), \
+        f"no decode step ran from the graph of {bucket} rows"
+    tol = TOL[dtype]
+    if name == "WIDE" and dtype == "bfloat16":
+        # the 0.9B widths: the bound relative to the largest logit, as in the replay at these sizes below
+        tol = 1.5e-2 * float(max(plain[r]["main"].abs().max() for r in plain))
+    _compare(cfg, steps, out_dir, seqs, plain, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_across_the_context_bounds_of_the_graphs(dtype, tmp_path, tmp_path_factory):
     """Decode graphs are kept per bound on the context (512, 1024, 2048 keys, ...), each with its own plan
     of key splits.  One request decodes across three bounds — a new graph, another split plan, the same
