@@ -69,6 +69,30 @@ def test_greedy_takes_lowest_index_of_the_maximum_and_applies_penalty():
     assert out.tolist() == [5, 7, 40]
 
 
+@pytest.mark.parametrize("k,V", [(1, 49152), (8, 8193), (3, 1025), (40, 5000), (200, 3000), (5, 1024)])
+def test_arg_max_over_the_ctas_of_a_row(k, V):
+    """The first pass runs over several CTAs a row (fewer the more rows there are), in runs of 1024 entries:
+    the maximum in every run in turn, and equal maxima in runs of different CTAs (lowest index wins); the
+    probabilities of a sampled row need the maximum of the whole row too."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(k * 7 + V)
+    logits = torch.randn(k, V, generator=g)
+    want = []
+    for r in range(k):
+        a = (r * 1024 + 17 * r + 5) % V             # a run further on for every row
+        b = (a + 3 * 1024 + 1) % V                  # the same value in another run
+        logits[r, a] = 9.0
+        if r % 2:
+            logits[r, b] = 9.0
+            want.append(min(a, b))
+        else:
+            want.append(a)
+    out, _, _ = _run(ops, logits, [0.0] * k, [0] * k, [0.0] * k, [1.0] * k, [[]] * k, [0] * k, [0] * k, want_probs=False)
+    assert out.tolist() == want
+    out, probs, _ = _run(ops, logits, [1.0] * k, [0] * k, [0.0] * k, [1.0] * k, [[]] * k, [3] * k, list(range(k)))
+    torch.testing.assert_close(probs, torch.softmax(logits, -1), rtol=1e-4, atol=1e-7)
+
+
 def test_same_seed_same_token_and_seen_bitmap_grows():
     ops = _ops()
     g = torch.Generator().manual_seed(1)

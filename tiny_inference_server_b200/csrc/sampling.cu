@@ -1,7 +1,13 @@
-// Sampling from rows of 32-bit logits, one CTA per row, in the order of the upstream
-// sampler (server.py:22-50): repetition penalty over the tokens seen so far, division
+// Sampling from rows of 32-bit logits, in the order of the upstream sampler
+// (server.py:22-50): repetition penalty over the tokens seen so far, division
 // by the temperature, top-k, top-p, softmax, one draw.  Greedy rows (temperature 0 or
 // top_k 1) take the arg-max of the penalised logits, lowest index on ties.
+//
+// A row belongs to a cluster of up to eight CTAs (fewer when there are many rows).  The
+// first pass, the maximum and its lowest index, is shared out over the cluster in
+// interleaved runs of 1024 entries; every CTA writes its (maximum, index) into the first
+// CTA's shared memory, and after one cluster barrier the first CTA holds the row's.  A
+// greedy row is done then; for the others the first CTA goes on alone.
 //
 // No sort is made.  The k-th largest value, and the value at which the descending
 // cumulative probability first passes p, are found by radix selection over the ordered
@@ -11,9 +17,10 @@
 //
 // The draw is by inverse CDF in index order with one Philox4x32-10 number per row,
 // keyed by (seed, counter): the same seed, counter and logits give the same token.
-#include "common.cuh"
+#include "cluster_reduce.cuh"
 
 #define SAMPLE_THREADS 1024
+#define SAMPLE_MAX_CLUSTER 8
 
 struct Philox {
     static __device__ __forceinline__ void round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
@@ -72,8 +79,14 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     __shared__ unsigned int sh_u[2];
     __shared__ float sh_f[2];
     __shared__ int sh_tok;
+    __shared__ float part_max[SAMPLE_MAX_CLUSTER];
+    __shared__ int part_tok[SAMPLE_MAX_CLUSTER];
 
-    const int r = blockIdx.x, tid = threadIdx.x;
+    unsigned ranks, rank;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(ranks));
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+    const int r = blockIdx.x / ranks, tid = threadIdx.x;
+    if (ranks > 1) cluster_reduce::cluster_arrive();      // waited for before the first write to another CTA
     const float temp = temps[r];
     const int top_k = top_ks[r];
     const float top_p = top_ps[r];
@@ -88,14 +101,14 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     row.penalty = pen;
     row.inv_temp = greedy ? 1.f : 1.f / temp;
 
-    // ---- maximum and its lowest index
+    // ---- maximum and its lowest index: this CTA's runs of the row, then over the cluster
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    for (int i = (int)rank * SAMPLE_THREADS + tid; i < V; i += SAMPLE_THREADS * (int)ranks) {
         const float x = row.at(i);
         if (x > best || (x == best && i < best_i)) { best = x; best_i = i; }
     }
-    const float M = block_max(best, red);
+    float M = block_max(best, red);
     {
         int cand = (best == M) ? best_i : 0x7fffffff;
 #pragma unroll
@@ -103,6 +116,26 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
         if (tid == 0) sh_tok = 0x7fffffff;
         __syncthreads();
         if ((tid & 31) == 0) atomicMin(&sh_tok, cand);
+        __syncthreads();
+    }
+    if (ranks > 1) {
+        cluster_reduce::cluster_wait();           // every CTA of the cluster has started
+        if (tid == 0) {
+            const unsigned at_max = cluster_reduce::map_to_rank(cluster_reduce::shared_addr(&part_max[rank]), 0u);
+            const unsigned at_tok = cluster_reduce::map_to_rank(cluster_reduce::shared_addr(&part_tok[rank]), 0u);
+            asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at_max), "f"(M) : "memory");
+            asm volatile("st.shared::cluster.s32 [%0], %1;\n" ::"r"(at_tok), "r"(sh_tok) : "memory");
+        }
+        cluster_reduce::cluster_arrive();         // release: the two stores above
+        cluster_reduce::cluster_wait();
+        if (rank != 0) return;                    // nothing reads the memory of these CTAs
+        float m_all = part_max[0];
+        for (unsigned c = 1; c < ranks; ++c) m_all = fmaxf(m_all, part_max[c]);
+        int tok_all = 0x7fffffff;
+        for (unsigned c = 0; c < ranks; ++c)
+            if (part_max[c] == m_all) tok_all = min(tok_all, part_tok[c]);
+        M = m_all;
+        if (tid == 0) sh_tok = tok_all;
         __syncthreads();
     }
     if (greedy) {
@@ -269,9 +302,26 @@ TIS_API int tis_sample_rows(const float* logits, int k, int V, const float* temp
         tis_set_error("sample_rows: vocabulary size %d", V);
         return TIS_BAD_SIZE;
     }
-    sample_rows_kernel<<<k, SAMPLE_THREADS, 0, stream>>>(logits, V, temps, top_ks, top_ps, penalties, slots,
-                                                         seen_bitmap, bitmap_words, seeds, counters, out_tokens,
-                                                         probs_out);
+    // CTAs a row: as many as leave every CTA a run of its own and all clusters resident at once
+    int ranks = SAMPLE_MAX_CLUSTER;
+    while (ranks > 1 && ((long long)k * ranks > 148 || (long long)(ranks - 1) * SAMPLE_THREADS >= V)) ranks >>= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(k * ranks), 1, 1);
+    cfg.blockDim = dim3(SAMPLE_THREADS, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)ranks;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_rows_kernel, logits, V, temps, top_ks, top_ps, penalties, slots,
+                                             seen_bitmap, bitmap_words, seeds, counters, out_tokens, probs_out);
+    if (e != cudaSuccess) {
+        tis_set_error("sample_rows: %s", cudaGetErrorString(e));
+        return TIS_CUDA_ERROR;
+    }
     return tis_check_launch("sample_rows");
 }
 
