@@ -141,15 +141,16 @@ def fill_cache(runner, slots, length):
         grp.pages.normal_(0.0, 0.5, generator=g)
 
 
-def decode_run(runner, batch, start_len, steps, warmup, sampler_cls, count_ops):
-    """Device time of ``steps`` decode steps at ``batch`` requests; returns (ms per step, launches per step)."""
+def decode_run(runner, batch, start_len, steps, warmup, sampler_cls, count_ops, sampling=None):
+    """Device time of ``steps`` decode steps at ``batch`` requests; returns (ms per step, launches per step).
+    ``sampling``: keyword arguments of SamplingParams (default: greedy)."""
     import torch
     from tiny_inference_server_b200.engine import StepEntry
     from tiny_inference_server_b200.sampling import SampleSpec, SamplingParams
 
     slots = [runner.add_request() for _ in range(batch)]
     fill_cache(runner, slots, start_len)
-    greedy = SamplingParams(temperature=0.0)
+    greedy = SamplingParams(**(sampling or {"temperature": 0.0}))
     gen = torch.Generator().manual_seed(2)
     feed = torch.randint(0, runner.vocab_size, (warmup + steps, batch), generator=gen).tolist()
 
@@ -447,6 +448,10 @@ def main(argv=None):
         nbytes, _ = model_bytes_and_flops(cfg_dict, args.layers, args.batch, 1024)
         points[f"decode_b{args.batch}_ctx1024"] = round(args.batch / (pms * 1e-3), 1)
         points[f"decode_b{args.batch}_ctx1024_hbm_frac"] = round(nbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        # the same step with a token drawn instead of the arg-max (the sampler runs inside the step's graph)
+        drawn = {"temperature": 0.8, "top_k": 50, "top_p": 0.95, "rep_penalty": 1.1}
+        pms, _ = decode_run(runner, args.batch, start_len, half, args.warmup, Sampler, count_ops, sampling=drawn)
+        points[f"decode_b{args.batch}_top_k50_top_p95"] = round(args.batch / (pms * 1e-3), 1)
         out["points"] = points
         pf_ms, pf_first = prefill_run(runner, PREFILL_TOKENS)
         out["prefill"] = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,

@@ -37,9 +37,21 @@ def _run(ops, logits, temps, top_ks, top_ps, pens, seen_lists, seeds, counters, 
     return out.cpu(), (probs.cpu() if want_probs else None), bm.cpu()
 
 
-@pytest.mark.parametrize("V", [6, 100, 301, 49152])
-def test_probabilities_match_upstream_formulas(V):
+@pytest.fixture
+def stage_limit():
+    """Sets how much of a row a CTA keeps in shared memory; the device's own limit again afterwards."""
     ops = _ops()
+    yield ops.sample_stage_limit
+    ops.sample_stage_limit(-1)
+
+
+# (vocabulary, entries of a row a CTA may keep): one CTA a row; eight with a share each; shares of 76 entries
+# in four CTAs; no share kept at all (every pass reads the logits), in one CTA and in eight
+@pytest.mark.parametrize("V,limit", [(6, -1), (100, -1), (301, -1), (49152, -1), (301, 80), (100, 0), (8193, 0),
+                                     (128256, -1)])
+def test_probabilities_match_upstream_formulas(V, limit, stage_limit):
+    ops = _ops()
+    stage_limit(limit)
     g = torch.Generator().manual_seed(0)
     settings = [(1.0, 0, 0.0, 1.0), (0.7, 0, 0.0, 1.0), (1.0, 3, 0.0, 1.0), (1.0, 0, 0.9, 1.0),
                 (0.9, 50, 0.95, 1.1), (1.3, 5, 0.5, 1.3), (1.0, 0, 0.0, 2.0), (0.5, 2, 0.3, 1.0)]
@@ -91,6 +103,36 @@ def test_arg_max_over_the_ctas_of_a_row(k, V):
     assert out.tolist() == want
     out, probs, _ = _run(ops, logits, [1.0] * k, [0] * k, [0.0] * k, [1.0] * k, [[]] * k, [3] * k, list(range(k)))
     torch.testing.assert_close(probs, torch.softmax(logits, -1), rtol=1e-4, atol=1e-7)
+
+
+@pytest.mark.parametrize("V,limit", [(49152, -1), (8193, -1), (301, 80), (5000, 0), (5000, 700)])
+def test_draws_lie_in_their_interval_of_the_cdf_with_several_ctas_a_row(V, limit, stage_limit):
+    """Rows of every kind of setting, several draws each: the uniform number of (seed, counter) lies inside the
+    drawn token's own interval of the reference CDF (widened by float32 rounding of the sums, which the kernel
+    adds up in another order), whichever CTA of the row holds the token."""
+    ops = _ops()
+    stage_limit(limit)
+    g = torch.Generator().manual_seed(V + limit)
+    settings = [(1.0, 0, 0.0, 1.0), (1.0, 40, 0.0, 1.0), (1.0, 0, 0.9, 1.0), (0.8, 50, 0.95, 1.1)]
+    draws = 6
+    k = len(settings) * draws
+    logits = (torch.randn(len(settings), V, generator=g) * 2).repeat_interleave(draws, 0)
+    rows = [s for s in settings for _ in range(draws)]
+    seen = [[1, V - 1]] * k
+    seeds, counters = [5] * k, list(range(k))
+    out, _, _ = _run(ops, logits, [s[0] for s in rows], [s[1] for s in rows], [s[2] for s in rows],
+                     [s[3] for s in rows], seen, seeds, counters, want_probs=False)
+    owners = set()
+    for r, (t, tk, tp, pen) in enumerate(rows):
+        p = ref.row_probs(logits[r], t, tk, tp, pen, seen[r])
+        u = (ref._philox_u32(seeds[r], counters[r]) >> 8) / 16777216.0
+        cum = torch.cumsum(p, -1)
+        tok = int(out[r])
+        lo = float(cum[tok - 1]) if tok > 0 else 0.0
+        assert float(p[tok]) > 0 and lo - 2e-5 <= u * float(cum[-1]) <= float(cum[tok]) + 2e-5, \
+            f"row {r} {rows[r]}: token {tok} drawn for u={u}, its interval is [{lo}, {float(cum[tok])}]"
+        owners.add(tok * 8 // V)
+    assert len(owners) > 2 or V < 1000          # the tokens came from several parts of the row
 
 
 def test_same_seed_same_token_and_seen_bitmap_grows():

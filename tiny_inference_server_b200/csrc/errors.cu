@@ -35,7 +35,7 @@ bool tis_pdl_enabled() {
 
 // Version of the launcher interface; the Python side refuses a library built from
 // other sources than its own.
-TIS_API int tis_abi_version() { return 3; }
+TIS_API int tis_abi_version() { return 4; }
 
 #ifdef TIS_TIMELINE
 static thread_local unsigned long long* g_timeline = nullptr;

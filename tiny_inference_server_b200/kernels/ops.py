@@ -19,7 +19,7 @@ import torch
 from . import build as _build
 
 _lib = None
-ABI_VERSION = 3
+ABI_VERSION = 4
 #: launches of this library's kernels so far (library matrix products are not counted)
 launches = 0
 #: calls by kind, for tests that must know which kernel a product or an attention went to
@@ -791,6 +791,12 @@ def sample_rows(logits: torch.Tensor, temps: torch.Tensor, top_ks: torch.Tensor,
                                _p(seen_bitmap), words, _p(seeds), _p(counters), _p(out_tokens), _p(probs_out),
                                _stream()), lib)
     return out_tokens
+
+
+def sample_stage_limit(entries: int) -> None:
+    """For tests: the most entries of a row that a CTA of the sampling kernel keeps in shared memory (fewer
+    means more CTAs a row; 0: none, every pass reads the logits; -1: what the device allows)."""
+    _check(library().tis_sample_stage_limit(int(entries)), library())
 
 
 def bitmap_set(bitmap_row: torch.Tensor, tokens: torch.Tensor) -> None:
