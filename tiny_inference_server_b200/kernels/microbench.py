@@ -6,6 +6,7 @@
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 8        (weight-streaming kernel)
     python -m tiny_inference_server_b200.kernels.microbench gemm --rows 4096     (tcgen05 kernel, above 64 rows)
     python -m tiny_inference_server_b200.kernels.microbench prefill --tokens 2048 --layers 4
+    python -m tiny_inference_server_b200.kernels.microbench sampling --rows 8 --vocab 49152
     python -m tiny_inference_server_b200.kernels.microbench all
 
 ``--reps N --no-timing`` launches the kernel N times and exits (a profiler attaches to that);
@@ -156,6 +157,37 @@ def rowwise(args):
                                                 fault), 12)
     mb = n * ((H + 2 * KVH) * hd * 2 + (H + 2 * KVH) * hd * 2) / 1e6
     print(f"rope_kv_write  {n} rows: {t:7.2f} us  {mb / t * 1e3:7.1f} GB/s")
+
+
+def sampling(args):
+    """The sampling kernel at ``--rows`` rows of ``--vocab`` logits, for the kinds of setting a row can have."""
+    dev = "cuda"
+    k, v = args.rows, args.vocab
+    bufs = max(2, min(16, (300 << 20) // (k * v * 4)))
+    logits = [torch.randn(k, v, device=dev) * 3 for _ in range(bufs)]
+    slots = torch.arange(k, dtype=torch.int32, device=dev)
+    seen = torch.zeros(k, (v + 31) // 32, dtype=torch.int32, device=dev)
+    seeds = torch.arange(k, dtype=torch.int64, device=dev)
+    counters = torch.zeros(k, dtype=torch.int64, device=dev)
+    out = torch.empty(k, dtype=torch.int32, device=dev)
+    for name, temp, top_k, top_p, pen in [("greedy", 0.0, 0, 0.0, 1.0), ("temperature", 1.0, 0, 0.0, 1.0),
+                                          ("top-k 50", 1.0, 50, 0.0, 1.0), ("top-p 0.9", 1.0, 0, 0.9, 1.0),
+                                          ("top-k 50, top-p 0.95, penalty 1.1", 0.8, 50, 0.95, 1.1)]:
+        temps = torch.full((k,), temp, device=dev)
+        top_ks = torch.full((k,), top_k, dtype=torch.int32, device=dev)
+        top_ps = torch.full((k,), top_p, device=dev)
+        pens = torch.full((k,), pen, device=dev)
+        if args.no_timing:
+            if pen == 1.0:
+                continue                      # a profiler looks at the setting with everything in it
+            for i in range(args.reps):
+                ops.sample_rows(logits[i % bufs], temps, top_ks, top_ps, pens, slots, seen, seeds, counters, out, None)
+            torch.cuda.synchronize()
+            print(f"sampling {k} x {v} {name}: {args.reps} launches")
+            return
+        t = _graph_time(lambda i: ops.sample_rows(logits[i % bufs], temps, top_ks, top_ps, pens, slots, seen, seeds,
+                                                  counters, out, None), 20)
+        print(f"sampling {k} x {v}  {name:36s}: {t:7.2f} us")
 
 
 def gemm(args):
@@ -329,7 +361,8 @@ def timeline(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "timeline", "all"])
+    ap.add_argument("what", choices=["attention", "attention-prefill", "rowwise", "gemm", "prefill", "sampling", "timeline",
+                                     "all"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--rows", type=int, default=8)
@@ -342,6 +375,7 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=3)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--ffn", type=int, default=4096)
+    ap.add_argument("--vocab", type=int, default=49152)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--reps", type=int, default=4)
     ap.add_argument("--no-timing", action="store_true")
@@ -366,6 +400,8 @@ def main(argv=None):
             gemm(args)
     if args.what in ("prefill", "all"):
         prefill(args)
+    if args.what in ("sampling", "all"):
+        sampling(args)
     return 0
 
 
