@@ -86,6 +86,7 @@ namespace {
 struct Shared {
     float red[33];
     unsigned int slots[2][SAMPLE_MAX_CLUSTER][256];          // every rank's histogram: counts, or masses as float bits
+    unsigned int merged[256];                                // the histogram of the row
     unsigned int parts[2][SAMPLE_MAX_CLUSTER][2];            // every rank's part of a small exchange
     float warp_part[32];
     unsigned int picked[2];                                  // bin, and the rank left to descend
@@ -185,17 +186,25 @@ __device__ __forceinline__ uint32_t radix_threshold(Shared& sh, unsigned* lane_h
         }
         hbuf ^= 1;
         cluster_sync();
+        if (tid < 256) {                      // the ranks' parts of a bin, added up in rank order
+            unsigned mu = 0u;
+            float mf = 0.f;
+            for (unsigned c = 0; c < ranks; ++c) {
+                const unsigned v = sh.slots[hbuf][c][tid];
+                if (MASS) mf += __uint_as_float(v); else mu += v;
+            }
+            sh.merged[tid] = MASS ? __float_as_uint(mf) : mu;
+        }
+        __syncthreads();
         if (tid < 32) {
             // lane l: bins 8l .. 8l+7; from the top bin down, the first bin at which the sum reaches the goal
             unsigned hu[8], tu = 0u;
             float hf[8], tf = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                hu[j] = 0u; hf[j] = 0.f;
-                for (unsigned c = 0; c < ranks; ++c) {
-                    const unsigned v = sh.slots[hbuf][c][8 * lane + j];
-                    if (MASS) hf[j] += __uint_as_float(v); else hu[j] += v;
-                }
+                const unsigned v = sh.merged[8 * lane + j];
+                hu[j] = MASS ? 0u : v;
+                hf[j] = MASS ? __uint_as_float(v) : 0.f;
                 tu += hu[j]; tf += hf[j];
             }
             unsigned su = tu;                 // sums over this lane and the lanes above it
