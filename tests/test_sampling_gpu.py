@@ -135,6 +135,26 @@ def test_draws_lie_in_their_interval_of_the_cdf_with_several_ctas_a_row(V, limit
     assert len(owners) > 2 or V < 1000          # the tokens came from several parts of the row
 
 
+@pytest.mark.parametrize("V,limit", [(5000, -1), (300, 40), (49152, -1)])
+def test_equal_values_at_a_threshold_are_all_kept(V, limit, stage_limit):
+    """Logits on a grid of quarter steps (hundreds of equal values): the k-th largest value and the value at which
+    the cumulative probability passes p are shared by many entries, all of which stay (the radix passes end early
+    when a whole bin is wanted, or run to the last bit: both must give the same set)."""
+    ops = _ops()
+    stage_limit(limit)
+    g = torch.Generator().manual_seed(V)
+    settings = [(1.0, 3, 0.0), (1.0, 40, 0.0), (1.0, 0, 0.5), (1.0, 200, 0.9), (1.0, 1000, 0.0), (1.0, V - 1, 0.0)]
+    k = len(settings)
+    logits = (torch.randn(k, V, generator=g) * 2).mul(4).round().div(4)
+    out, probs, _ = _run(ops, logits, [s[0] for s in settings], [s[1] for s in settings], [s[2] for s in settings],
+                         [1.0] * k, [[]] * k, [1] * k, [0] * k)
+    for r, (t, tk, tp) in enumerate(settings):
+        want = ref.row_probs(logits[r], t, tk, tp, 1.0, []).float()
+        assert int((probs[r] > 0).sum()) == int((want > 0).sum()), settings[r]
+        torch.testing.assert_close(probs[r], want, rtol=1e-4, atol=1e-7)
+        assert probs[r, out[r]] > 0
+
+
 def test_same_seed_same_token_and_seen_bitmap_grows():
     ops = _ops()
     g = torch.Generator().manual_seed(1)

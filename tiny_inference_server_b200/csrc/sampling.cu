@@ -243,6 +243,8 @@ __device__ __forceinline__ uint32_t radix_threshold(Shared& sh, unsigned* lane_h
         prefix |= (sh.picked[0] << shift);
         mask |= (255u << shift);
         if (MASS) above_total = sh.picked_above; else want = sh.picked[1];
+        // every entry of the bin is wanted: the bin's lowest key is the threshold, whatever the bits below say
+        if (!MASS && sh.merged[sh.picked[0]] == want) break;
     }
     return prefix;
 }
