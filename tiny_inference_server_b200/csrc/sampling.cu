@@ -29,7 +29,7 @@
 // drawn number finds the entry.
 //
 // A row whose share per rank is larger than the shared memory (a vocabulary of more than
-// about 400,000 entries) is read from the logits in every pass instead.
+// about 360,000 entries) is read from the logits in every pass instead.
 #include "cluster_reduce.cuh"
 
 #define SAMPLE_THREADS 1024
